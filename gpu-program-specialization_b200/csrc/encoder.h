@@ -1,0 +1,56 @@
+/*
+ * encoder.h - host-side program encoder: postfix bytecode -> accumulator-machine records.
+ *
+ * Plays the role of the reference specializer (projects/secant/s_cubin_specialize.c):
+ * same linear traversal with routine inlining and the same structural error codes, but
+ * the output is a compact record per program (record.h) instead of machine code.
+ */
+#ifndef SECANT_B200_ENCODER_H
+#define SECANT_B200_ENCODER_H
+
+#include "../../include/secant_b200.h"
+#include "record.h"
+
+#include <cstddef>
+#include <vector>
+
+namespace sb {
+
+constexpr unsigned kMaxSlots = 48;       /* spill slots one program may need */
+constexpr unsigned kRoutineDepth = 8;    /* nested routine frames, as in the reference */
+
+struct ProgramRules {
+    size_t num_columns = 0;     /* COLUMN indices must be below this */
+    size_t num_constants = 0;   /* BANK / AFFINE_BANK slots must be below this */
+    bool banks_allowed = false; /* only the toggle shape has banks and toggles */
+    unsigned toggle_bits = 0;   /* toggle bit indices must be below this */
+};
+
+/* Encoded records of a contiguous group of programs, ready to upload as five arrays. */
+struct EncodedBatch {
+    std::vector<SbProgram> programs;
+    std::vector<SbInsn> insns;
+    std::vector<SbPatch> patches;
+    std::vector<SbAffine> affines;
+    std::vector<float> lits;
+    unsigned max_insn = 1;      /* largest n_insn */
+    unsigned max_extra = 0;     /* largest n_affine + n_lits */
+    unsigned max_slots = 0;     /* largest n_slots */
+    unsigned max_patch = 0;
+    void clear();
+};
+
+/* Leaf-range / opcode scan of one program without inlining; mirrors the runner preflight
+ * (projects/secant/s_cubin_runner.c:138-181).  Runs before any output is cleared. */
+SecantResult preflight(const SecantAstInstruction* program, const ProgramRules& rules);
+
+/* Number of ROUTINE_ARG slots each routine uses (projects/secant/s_cpu.c:129-191). */
+SecantResult routine_arities(const SecantAstProgramList& routines, uint8_t* arity /* [255] */);
+
+/* Appends the record of one program to `out`.  On error `out` may hold a partial record. */
+SecantResult encode_program(const SecantAstInstruction* program, const SecantAstProgramList& routines,
+                            const uint8_t* routine_arity, const ProgramRules& rules, EncodedBatch& out);
+
+}  // namespace sb
+
+#endif

@@ -1,0 +1,553 @@
+/*
+ * evaluator.cu - population evaluator for sm_100a.
+ *
+ * Replaces the reference's generated-and-patched kernels
+ * (projects/secant/s_cubin_generate_toggle_sse.c:339-386, s_cubin_generate_sse.c:461-706,
+ * s_cubin_generate_materialize.c:475-540) with one resident kernel family that interprets
+ * the encoder's records (record.h).
+ *
+ * Work decomposition
+ *   CTA    = one group of programs x one range of rows.  The CTA stages a tile of
+ *            (inputs + targets) x tile_rows floats in shared memory once per chunk and all
+ *            its warps read operands from that tile.
+ *   warp   = one program at a time, taken from the CTA's queue, so long and short
+ *            programs balance inside a CTA.  All 32 lanes execute the same instruction
+ *            stream (no divergence); toggles are resolved per permutation by patching
+ *            the warp's private copy of the program, not by per-thread selects.
+ *   thread = a register tile acc[RR rows][RC banks]; one decoded instruction does
+ *            RR*RC FP32 operations.  A column operand costs one 128-bit shared load per
+ *            four rows and is reused for all RC coefficient banks; a bank constant is one
+ *            broadcast load reused for all RR rows.
+ * The squared error is accumulated in registers over the passes of a chunk, reduced
+ * with warp shuffles, and added to the caller's output once per (program, configuration,
+ * chunk): per-row predictions never reach HBM.
+ *
+ * Numerics follow the reference HOST evaluator (projects/secant/s_cpu.c:329-352): IEEE
+ * add/sub/mul/div/sqrt, accurate sin/cos/exp/log, no flush-to-zero, and no contraction of
+ * program-level multiplies and adds (only FMA_F32 fuses).
+ */
+#include "evaluator.cuh"
+
+#include <math_constants.h>
+
+namespace sb {
+
+namespace {
+
+struct Geom {
+    uint32_t tile_rows;      /* floats between consecutive columns of the tile */
+    uint32_t programs_per_cta;
+    uint32_t row_splits;
+    uint32_t exec_bytes;     /* per-warp regions, each a multiple of 16 bytes */
+    uint32_t cst_bytes;
+    uint32_t tacc_bytes;
+    uint32_t warp_bytes;
+    uint32_t tile_bytes;
+    unsigned long long rows_per_split;
+    uint32_t use_atomics;
+};
+
+template <int OP>
+__device__ __forceinline__ float binop(float a, float x) {
+    if (OP == SB_BIN_ADD) return __fadd_rn(a, x);
+    if (OP == SB_BIN_SUB) return __fsub_rn(a, x);
+    if (OP == SB_BIN_RSUB) return __fsub_rn(x, a);
+    if (OP == SB_BIN_MUL) return __fmul_rn(a, x);
+    if (OP == SB_BIN_DIV) return __fdiv_rn(a, x);
+    if (OP == SB_BIN_RDIV) return __fdiv_rn(x, a);
+    if (OP == SB_BIN_MIN) return fminf(a, x);
+    return fmaxf(a, x);
+}
+
+template <int OP>
+__device__ __forceinline__ float unop(float a) {
+    if (OP == SB_UN_NEG) return -a;
+    if (OP == SB_UN_SQRT) return __fsqrt_rn(a);
+    if (OP == SB_UN_RCP) return __frcp_rn(a);
+    if (OP == SB_UN_ABS) return fabsf(a);
+    if (OP == SB_UN_SIN) return sinf(a);
+    if (OP == SB_UN_COS) return cosf(a);
+    if (OP == SB_UN_EX2) return exp2f(a);
+    if (OP == SB_UN_LG2) return log2f(a);
+    if (OP == SB_UN_RSQRT) return __frcp_rn(__fsqrt_rn(a)); /* host: 1 / sqrtf(x), two roundings */
+    if (OP == SB_UN_TANH) return tanhf(a);
+    if (OP == SB_UN_EXP) return expf(a);
+    return logf(a);
+}
+
+template <int RR, int RC>
+struct Machine {
+    static constexpr int V = RR * RC;
+    static constexpr int PASS = 32 * RR;      /* rows one warp covers per pass */
+    static constexpr int GROUPS = RR / 4;     /* float4 row groups per thread */
+    static constexpr int SLOT_BYTES = V * 128;
+
+    float acc[RR][RC];
+
+    __device__ __forceinline__ void fetch_row(const float* rowp, uint32_t tile_ld, uint32_t col, float (&x)[RR]) const {
+        const float* q = rowp + (size_t)col * tile_ld;
+#pragma unroll
+        for (int g = 0; g < GROUPS; ++g) {
+            const float4 v = *reinterpret_cast<const float4*>(q + g * 128);
+            x[4 * g + 0] = v.x; x[4 * g + 1] = v.y; x[4 * g + 2] = v.z; x[4 * g + 3] = v.w;
+        }
+    }
+    __device__ __forceinline__ void fetch_cst(const float* cst, uint32_t entry, float (&x)[RC]) const {
+        const float* q = cst + entry * RC;
+        if (RC == 4) {
+            const float4 v = *reinterpret_cast<const float4*>(q);
+            x[0] = v.x; x[1 % RC] = v.y; x[2 % RC] = v.z; x[3 % RC] = v.w;
+        } else if (RC == 2) {
+            const float2 v = *reinterpret_cast<const float2*>(q);
+            x[0] = v.x; x[1 % RC] = v.y;
+        } else {
+            x[0] = q[0];
+        }
+    }
+    /* Slot s of this warp: V/4 float4 vectors per lane, lane-interleaved (conflict free). */
+    __device__ __forceinline__ void fetch_slot(const float4* slots, uint32_t s, float (&x)[RR][RC]) const {
+        const float4* q = slots + (size_t)s * (V / 4) * 32;
+        float* flat = &x[0][0];
+#pragma unroll
+        for (int j = 0; j < V / 4; ++j) {
+            const float4 v = q[j * 32];
+            flat[4 * j + 0] = v.x; flat[4 * j + 1] = v.y; flat[4 * j + 2] = v.z; flat[4 * j + 3] = v.w;
+        }
+    }
+    __device__ __forceinline__ void store_slot(float4* slots, uint32_t s) const {
+        float4* q = slots + (size_t)s * (V / 4) * 32;
+        const float* flat = &acc[0][0];
+#pragma unroll
+        for (int j = 0; j < V / 4; ++j) q[j * 32] = make_float4(flat[4 * j], flat[4 * j + 1], flat[4 * j + 2], flat[4 * j + 3]);
+    }
+
+    /* Generic operand expansion used by FMA only. */
+    __device__ __forceinline__ void expand(unsigned kind, uint32_t index, const float* rowp, uint32_t tile_ld,
+                                           const float* cst, const float4* slots, float (&out)[RR][RC]) const {
+        if (kind == SB_FMA_ACC) {
+#pragma unroll
+            for (int r = 0; r < RR; ++r)
+#pragma unroll
+                for (int c = 0; c < RC; ++c) out[r][c] = acc[r][c];
+        } else if (kind == SB_KIND_ROW) {
+            float x[RR];
+            fetch_row(rowp, tile_ld, index, x);
+#pragma unroll
+            for (int r = 0; r < RR; ++r)
+#pragma unroll
+                for (int c = 0; c < RC; ++c) out[r][c] = x[r];
+        } else if (kind == SB_KIND_CST) {
+            float x[RC];
+            fetch_cst(cst, index, x);
+#pragma unroll
+            for (int r = 0; r < RR; ++r)
+#pragma unroll
+                for (int c = 0; c < RC; ++c) out[r][c] = x[c];
+        } else {
+            fetch_slot(slots, index, out);
+        }
+    }
+
+#define SB_FOR_TILE _Pragma("unroll") for (int r = 0; r < RR; ++r) _Pragma("unroll") for (int c = 0; c < RC; ++c)
+
+#define SB_BIN_CASES(OP)                                                                             \
+    case SB_CASE_BIN + OP * SB_NUM_KINDS + SB_KIND_ROW: {                                            \
+        float x[RR]; fetch_row(rowp, tile_ld, idx, x);                                               \
+        SB_FOR_TILE acc[r][c] = binop<OP>(acc[r][c], x[r]);                                          \
+        break; }                                                                                     \
+    case SB_CASE_BIN + OP * SB_NUM_KINDS + SB_KIND_CST: {                                            \
+        float x[RC]; fetch_cst(cst, idx, x);                                                         \
+        SB_FOR_TILE acc[r][c] = binop<OP>(acc[r][c], x[c]);                                          \
+        break; }                                                                                     \
+    case SB_CASE_BIN + OP * SB_NUM_KINDS + SB_KIND_SLOT: {                                           \
+        float x[RR][RC]; fetch_slot(slots, idx, x);                                                  \
+        SB_FOR_TILE acc[r][c] = binop<OP>(acc[r][c], x[r][c]);                                       \
+        break; }                                                                                     \
+    case SB_CASE_BIN + OP * SB_NUM_KINDS + SB_KIND_IMM: {                                            \
+        const float x = __uint_as_float(ins.y);                                                      \
+        SB_FOR_TILE acc[r][c] = binop<OP>(acc[r][c], x);                                             \
+        break; }
+
+#define SB_UN_CASE(OP) \
+    case SB_CASE_UN + OP: { SB_FOR_TILE acc[r][c] = unop<OP>(acc[r][c]); break; }
+
+    /* Runs the warp's program once over the RR*32 rows starting at rowp. */
+    __device__ __forceinline__ void run(const SbInsn* exec, const float* rowp, uint32_t tile_ld, const float* cst,
+                                        float4* slots) {
+        const uint2* ip = reinterpret_cast<const uint2*>(exec);
+        SB_FOR_TILE acc[r][c] = 0.0f;
+#pragma unroll 1
+        for (;;) {
+            const uint2 ins = *ip++;
+            const uint32_t idx = ins.x >> 16;
+            switch (ins.x & 0xffu) {
+            case SB_CASE_END:
+                return;
+            case SB_CASE_LOAD + SB_KIND_ROW: {
+                float x[RR]; fetch_row(rowp, tile_ld, idx, x);
+                SB_FOR_TILE acc[r][c] = x[r];
+                break; }
+            case SB_CASE_LOAD + SB_KIND_CST: {
+                float x[RC]; fetch_cst(cst, idx, x);
+                SB_FOR_TILE acc[r][c] = x[c];
+                break; }
+            case SB_CASE_LOAD + SB_KIND_SLOT:
+                fetch_slot(slots, idx, acc);
+                break;
+            case SB_CASE_LOAD + SB_KIND_IMM: {
+                const float x = __uint_as_float(ins.y);
+                SB_FOR_TILE acc[r][c] = x;
+                break; }
+            case SB_CASE_STORE:
+                store_slot(slots, idx);
+                break;
+            SB_BIN_CASES(SB_BIN_ADD)
+            SB_BIN_CASES(SB_BIN_SUB)
+            SB_BIN_CASES(SB_BIN_RSUB)
+            SB_BIN_CASES(SB_BIN_MUL)
+            SB_BIN_CASES(SB_BIN_DIV)
+            SB_BIN_CASES(SB_BIN_RDIV)
+            SB_BIN_CASES(SB_BIN_MIN)
+            SB_BIN_CASES(SB_BIN_MAX)
+            SB_UN_CASE(SB_UN_NEG)
+            SB_UN_CASE(SB_UN_SQRT)
+            SB_UN_CASE(SB_UN_RCP)
+            SB_UN_CASE(SB_UN_ABS)
+            SB_UN_CASE(SB_UN_SIN)
+            SB_UN_CASE(SB_UN_COS)
+            SB_UN_CASE(SB_UN_EX2)
+            SB_UN_CASE(SB_UN_LG2)
+            SB_UN_CASE(SB_UN_RSQRT)
+            SB_UN_CASE(SB_UN_TANH)
+            SB_UN_CASE(SB_UN_EXP)
+            SB_UN_CASE(SB_UN_LOG)
+            case SB_CASE_FMA: {
+                const unsigned kinds = (ins.x >> 8) & 0x3fu;
+                float a[RR][RC], b[RR][RC], d[RR][RC];
+                expand(kinds & 3u, ins.y & 1023u, rowp, tile_ld, cst, slots, a);
+                expand((kinds >> 2) & 3u, (ins.y >> 10) & 1023u, rowp, tile_ld, cst, slots, b);
+                expand((kinds >> 4) & 3u, (ins.y >> 20) & 1023u, rowp, tile_ld, cst, slots, d);
+                SB_FOR_TILE acc[r][c] = __fmaf_rn(a[r][c], b[r][c], d[r][c]);
+                break; }
+            default:
+                return; /* unreachable for records produced by the encoder */
+            }
+        }
+    }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <int RR, int RC>
+__global__ void __launch_bounds__(512, 1)
+eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
+    using M = Machine<RR, RC>;
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* const tile = reinterpret_cast<float*>(smem);
+    unsigned int* const queue = reinterpret_cast<unsigned int*>(smem + geom.tile_bytes);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned char* const warea = smem + geom.tile_bytes + 16 + (size_t)warp * geom.warp_bytes;
+    SbInsn* const exec = reinterpret_cast<SbInsn*>(warea);
+    float* const cst = reinterpret_cast<float*>(warea + geom.exec_bytes);
+    float* const tacc = reinterpret_cast<float*>(warea + geom.exec_bytes + geom.cst_bytes);
+    float4* const slots = reinterpret_cast<float4*>(warea + geom.exec_bytes + geom.cst_bytes + geom.tacc_bytes) + lane;
+
+    const uint32_t group = blockIdx.x / geom.row_splits, split = blockIdx.x % geom.row_splits;
+    const uint32_t prog_begin = group * geom.programs_per_cta;
+    const uint32_t prog_count = min(geom.programs_per_cta, batch.num_programs - prog_begin);
+    const size_t row_begin = (size_t)split * geom.rows_per_split;
+    const size_t row_end = min(prob.num_rows, row_begin + (size_t)geom.rows_per_split);
+    const uint32_t ncols = prob.num_inputs + (prob.mode == EVAL_MATERIALIZE ? 0u : prob.num_targets);
+    const uint32_t tile_ld = geom.tile_rows;
+    const uint32_t K = prob.num_constants;
+    const uint32_t T = prob.num_targets;
+    const unsigned long long nperm = prob.mode == EVAL_MATERIALIZE ? 1ull : (1ull << prob.toggle_bits);
+    const uint32_t ngroups = prob.mode == EVAL_MATERIALIZE ? 1u : (prob.num_banks + RC - 1) / RC;
+
+    for (size_t c0 = row_begin; c0 < row_end; c0 += geom.tile_rows) {
+        const uint32_t chunk_rows = (uint32_t)min((size_t)geom.tile_rows, row_end - c0);
+        const uint32_t padded = (chunk_rows + M::PASS - 1) / M::PASS * M::PASS;
+        const uint32_t npass = padded / M::PASS;
+        __syncthreads();
+        for (uint32_t col = 0; col < ncols; ++col) {
+            const float* src = col < prob.num_inputs ? prob.input + (size_t)col * prob.input_ld
+                                                     : prob.targets + (size_t)(col - prob.num_inputs) * prob.targets_ld;
+            float* dst = tile + (size_t)col * tile_ld;
+            for (uint32_t i = threadIdx.x; i < padded; i += blockDim.x) dst[i] = i < chunk_rows ? __ldg(src + c0 + i) : 0.0f;
+        }
+        if (threadIdx.x == 0) *queue = 0u;
+        __syncthreads();
+
+        for (;;) {
+            unsigned int pi = 0;
+            if (lane == 0) pi = atomicAdd(queue, 1u);
+            pi = __shfl_sync(0xffffffffu, pi, 0);
+            if (pi >= prog_count) break;
+            const uint32_t lp = prog_begin + pi;           /* index inside the batch */
+            const size_t gp = prob.first_program + lp;     /* index inside the run */
+            const SbProgram pr = batch.programs[lp];
+            __syncwarp();
+            for (uint32_t i = lane; i < pr.n_insn; i += 32) exec[i] = batch.insns[pr.insn_off + i];
+            for (uint32_t i = lane; i < (uint32_t)pr.n_lits * RC; i += 32)
+                cst[(K + pr.n_affine) * RC + i] = batch.lits[pr.lit_off + i / RC];
+            const float* bank_base = prob.banks ? prob.banks + gp * prob.program_bank_stride : nullptr;
+
+            for (unsigned long long perm = 0; perm < nperm; ++perm) {
+                const unsigned long long permutation = prob.mode == EVAL_MATERIALIZE ? prob.fixed_permutation : perm;
+                if (pr.n_patch) {
+                    __syncwarp();
+                    for (uint32_t i = lane; i < pr.n_patch; i += 32) {
+                        const SbPatch* p = batch.patches + pr.patch_off + i;
+                        unsigned choice = (unsigned)(permutation >> p->bit0) & 1u;
+                        if (p->bit1 != 0xffu) choice |= ((unsigned)(permutation >> p->bit1) & 1u) << 1;
+                        exec[p->insn] = p->alt[choice];
+                    }
+                }
+                for (uint32_t bg = 0; bg < ngroups; ++bg) {
+                    __syncwarp();
+                    for (uint32_t e = lane; e < (K + pr.n_affine) * RC; e += 32) {
+                        const uint32_t entry = e / RC, c = e % RC, bank = bg * RC + c;
+                        float v = 0.0f;
+                        if (bank < prob.num_banks) {
+                            if (entry < K) {
+                                v = __ldg(bank_base + (size_t)bank * prob.bank_stride + entry);
+                            } else {
+                                const SbAffine a = batch.affines[pr.affine_off + entry - K];
+                                v = __fadd_rn(__fmul_rn(__ldg(bank_base + (size_t)bank * prob.bank_stride + a.slot), a.scale), a.offset);
+                            }
+                        }
+                        cst[e] = v;
+                    }
+                    if (T > 1 || prob.mode == EVAL_AFFINE_STATS)
+                        for (uint32_t e = lane; e < (T + 2) * RC; e += 32) tacc[e] = 0.0f;
+                    __syncwarp();
+
+                    M m;
+                    float part[RC];
+#pragma unroll
+                    for (int c = 0; c < RC; ++c) part[c] = 0.0f;
+
+#pragma unroll 1
+                    for (uint32_t pass = 0; pass < npass; ++pass) {
+                        const float* rowp = tile + pass * M::PASS + lane * 4;
+                        m.run(exec, rowp, tile_ld, cst, slots);
+                        const uint32_t row0 = pass * M::PASS + lane * 4; /* first row of this thread in the chunk */
+                        const bool full = (pass + 1) * M::PASS <= chunk_rows;
+                        if (prob.mode == EVAL_MATERIALIZE) {
+                            float* out = prob.output + gp * prob.out_program_stride + c0;
+#pragma unroll
+                            for (int r = 0; r < RR; ++r) {
+                                const uint32_t row = row0 + (r / 4) * 128 + (r % 4);
+                                if (row < chunk_rows) out[row] = m.acc[r][0];
+                            }
+                        } else if (prob.mode == EVAL_SSE && T == 1) {
+                            float t[RR];
+                            m.fetch_row(rowp, tile_ld, prob.num_inputs, t);
+                            if (full) {
+#pragma unroll
+                                for (int r = 0; r < RR; ++r)
+#pragma unroll
+                                    for (int c = 0; c < RC; ++c) {
+                                        const float e = __fsub_rn(m.acc[r][c], t[r]);
+                                        part[c] = __fmaf_rn(e, e, part[c]);
+                                    }
+                            } else {
+#pragma unroll
+                                for (int r = 0; r < RR; ++r) {
+                                    const bool ok = row0 + (r / 4) * 128 + (r % 4) < chunk_rows;
+#pragma unroll
+                                    for (int c = 0; c < RC; ++c) {
+                                        const float e = ok ? __fsub_rn(m.acc[r][c], t[r]) : 0.0f;
+                                        part[c] = __fmaf_rn(e, e, part[c]);
+                                    }
+                                }
+                            }
+                        } else {
+                            /* several targets, or affine statistics: per-pass warp reduction into
+                             * the warp's shared accumulators tacc[quantity][bank] */
+                            const uint32_t nq = prob.mode == EVAL_AFFINE_STATS ? T + 2 : T;
+                            for (uint32_t q = 0; q < nq; ++q) {
+                                float t[RR];
+                                const bool is_target = prob.mode == EVAL_SSE || q >= 2;
+                                const uint32_t tcol = prob.num_inputs + (prob.mode == EVAL_SSE ? q : q - 2);
+                                if (is_target) m.fetch_row(rowp, tile_ld, tcol, t);
+                                float s[RC];
+#pragma unroll
+                                for (int c = 0; c < RC; ++c) s[c] = 0.0f;
+#pragma unroll
+                                for (int r = 0; r < RR; ++r) {
+                                    const bool ok = full || row0 + (r / 4) * 128 + (r % 4) < chunk_rows;
+#pragma unroll
+                                    for (int c = 0; c < RC; ++c) {
+                                        const float p = m.acc[r][c];
+                                        float term;
+                                        if (prob.mode == EVAL_SSE) { const float e = __fsub_rn(p, t[r]); term = __fmul_rn(e, e); }
+                                        else if (q == 0) term = p;
+                                        else if (q == 1) term = __fmul_rn(p, p);
+                                        else term = __fmul_rn(p, t[r]);
+                                        s[c] = __fadd_rn(s[c], ok ? term : 0.0f);
+                                    }
+                                }
+#pragma unroll
+                                for (int c = 0; c < RC; ++c) {
+                                    const float total = warp_sum(s[c]);
+                                    if (lane == 0) tacc[q * RC + c] += total;
+                                }
+                            }
+                        }
+                    }
+
+                    if (prob.mode == EVAL_SSE && T == 1) {
+                        float mine = 0.0f;
+#pragma unroll
+                        for (int c = 0; c < RC; ++c) {
+                            const float total = warp_sum(part[c]);
+                            if (lane == c) mine = total;
+                        }
+                        const uint32_t bank = bg * RC + lane;
+                        if (lane < RC && bank < prob.num_banks) {
+                            float* dst = prob.output + gp * prob.out_program_stride + ((size_t)bank << prob.toggle_bits) + perm;
+                            if (geom.use_atomics) atomicAdd(dst, mine);
+                            else *dst += mine;
+                        }
+                    } else if (prob.mode != EVAL_MATERIALIZE) {
+                        __syncwarp();
+                        const uint32_t nq = prob.mode == EVAL_AFFINE_STATS ? T + 2 : T;
+                        for (uint32_t e = lane; e < nq * RC; e += 32) {
+                            const uint32_t q = e / RC, c = e % RC, bank = bg * RC + c;
+                            if (bank < prob.num_banks) {
+                                float* dst = prob.output + gp * prob.out_program_stride + (size_t)q * prob.out_target_stride +
+                                             ((size_t)bank << prob.toggle_bits) + perm;
+                                if (geom.use_atomics) atomicAdd(dst, tacc[e]);
+                                else *dst += tacc[e];
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <int RR, int RC>
+cudaError_t launch_variant(const DeviceBatch& batch, const EvalProblem& prob, const Geom& geom, const LaunchPlan& plan,
+                           cudaStream_t stream) {
+    eval_kernel<RR, RC><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom);
+    return cudaGetLastError();
+}
+
+constexpr int kVariantRows[3] = {4, 8, 16};
+constexpr int kVariantBanks[3] = {4, 2, 1};
+
+uint32_t round16(size_t v) { return (uint32_t)((v + 15) / 16 * 16); }
+
+Geom make_geom(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPlan& plan) {
+    const int rr = kVariantRows[plan.variant], rc = kVariantBanks[plan.variant];
+    const uint32_t ncols = prob.num_inputs + (prob.mode == EVAL_MATERIALIZE ? 0u : prob.num_targets);
+    Geom g;
+    g.tile_rows = plan.tile_rows;
+    g.programs_per_cta = plan.programs_per_cta;
+    g.row_splits = plan.row_splits;
+    g.exec_bytes = round16((size_t)batch.max_insn * sizeof(SbInsn));
+    g.cst_bytes = round16(((size_t)prob.num_constants + batch.max_extra) * rc * 4 + 16);
+    g.tacc_bytes = round16(((size_t)prob.num_targets + 2) * rc * 4);
+    g.warp_bytes = g.exec_bytes + g.cst_bytes + g.tacc_bytes + (uint32_t)batch.max_slots * rr * rc * 128u;
+    g.tile_bytes = round16((size_t)ncols * plan.tile_rows * 4);
+    g.rows_per_split = plan.rows_per_split;
+    g.use_atomics = plan.row_splits > 1 ? 1u : 0u;
+    return g;
+}
+
+}  // namespace
+
+LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm_count, size_t smem_limit, int forced_variant) {
+    LaunchPlan plan;
+    plan.ok = false;
+    int variant = prob.num_banks >= 4 ? 0 : prob.num_banks >= 2 ? 1 : 2;
+    if (prob.mode == EVAL_MATERIALIZE) variant = 2;
+    if (forced_variant >= 0 && forced_variant < 3 && prob.mode != EVAL_MATERIALIZE) variant = forced_variant;
+    plan.variant = variant;
+    const int rr = kVariantRows[variant], rc = kVariantBanks[variant];
+    const uint32_t pass = 32u * rr;
+    const uint32_t ncols = prob.num_inputs + (prob.mode == EVAL_MATERIALIZE ? 0u : prob.num_targets);
+
+    /* rows staged per chunk: as many passes as fit in about a third of shared memory,
+     * never more than the data has */
+    const size_t rows_padded = (prob.num_rows + pass - 1) / pass * pass;
+    size_t tile_rows = ncols ? (smem_limit / 3) / ((size_t)ncols * 4) / pass * pass : rows_padded;
+    if (tile_rows > 4096) tile_rows = 4096 / pass * pass;
+    if (tile_rows < pass) tile_rows = pass;
+    if (tile_rows > rows_padded) tile_rows = rows_padded;
+
+    for (uint32_t warps = 16; warps >= 1; warps /= 2) {
+        LaunchPlan trial = plan;
+        trial.warps = warps;
+        trial.tile_rows = (uint32_t)tile_rows;
+        trial.programs_per_cta = 1;
+        trial.row_splits = 1;
+        trial.rows_per_split = prob.num_rows;
+        Geom g = make_geom(batch, prob, trial);
+        size_t need = (size_t)g.tile_bytes + 16 + (size_t)g.warp_bytes * warps;
+        while (need > smem_limit && trial.tile_rows > pass) {
+            trial.tile_rows = (trial.tile_rows / 2 + pass - 1) / pass * pass;
+            g = make_geom(batch, prob, trial);
+            need = (size_t)g.tile_bytes + 16 + (size_t)g.warp_bytes * warps;
+        }
+        if (need > smem_limit) continue;
+        plan = trial;
+        plan.smem_bytes = need;
+        plan.ok = true;
+        break;
+    }
+    if (!plan.ok) return plan;
+
+    /* Programs per CTA: enough CTAs to fill the machine several times over, but several
+     * programs per warp where the population allows so that a staged tile is reused. */
+    const uint32_t P = batch.num_programs;
+    const uint32_t target_ctas = (uint32_t)sm_count * 8u;
+    uint32_t ppc = (P + target_ctas - 1) / target_ctas;
+    const uint32_t min_ppc = plan.warps * 2;
+    if (ppc < min_ppc) ppc = min_ppc;
+    if (ppc > P) ppc = P;
+    const uint32_t groups = (P + ppc - 1) / ppc;
+    plan.programs_per_cta = ppc;
+    /* Too few program groups to occupy the GPU: split the rows across CTAs as well. */
+    uint32_t splits = 1;
+    const size_t chunks = (prob.num_rows + plan.tile_rows - 1) / plan.tile_rows;
+    if (groups < (uint32_t)sm_count && prob.mode != EVAL_MATERIALIZE) {
+        splits = ((uint32_t)sm_count * 2 + groups - 1) / groups;
+        if (splits > chunks) splits = (uint32_t)chunks;
+        if (splits < 1) splits = 1;
+    }
+    const size_t chunks_per_split = (chunks + splits - 1) / splits;
+    plan.rows_per_split = chunks_per_split * plan.tile_rows;
+    plan.row_splits = (uint32_t)((prob.num_rows + plan.rows_per_split - 1) / plan.rows_per_split);
+    plan.grid_x = groups * plan.row_splits;
+    return plan;
+}
+
+cudaError_t configure_kernels() {
+    cudaError_t e;
+    int dev = 0, limit = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+    if ((e = cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(eval_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(eval_kernel<8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(eval_kernel<16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
+    return cudaSuccess;
+}
+
+cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPlan& plan, cudaStream_t stream) {
+    const Geom geom = make_geom(batch, prob, plan);
+    switch (plan.variant) {
+    case 0: return launch_variant<4, 4>(batch, prob, geom, plan, stream);
+    case 1: return launch_variant<8, 2>(batch, prob, geom, plan, stream);
+    default: return launch_variant<16, 1>(batch, prob, geom, plan, stream);
+    }
+}
+
+}  // namespace sb

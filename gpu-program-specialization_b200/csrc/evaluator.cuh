@@ -1,0 +1,81 @@
+/*
+ * evaluator.cuh - launch interface of the population evaluator kernels (evaluator.cu).
+ */
+#ifndef SECANT_B200_EVALUATOR_CUH
+#define SECANT_B200_EVALUATOR_CUH
+
+#include "record.h"
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace sb {
+
+enum EvalMode : int {
+    EVAL_SSE = 0,          /* sum over rows of (prediction - target)^2 per (program, target, configuration) */
+    EVAL_MATERIALIZE = 1,  /* prediction per (program, row), one configuration */
+    EVAL_AFFINE_STATS = 2  /* sum p, sum p*p, sum p*t per program */
+};
+
+/* Device-resident records of one program batch. */
+struct DeviceBatch {
+    const SbProgram* programs;
+    const SbInsn* insns;
+    const SbPatch* patches;
+    const SbAffine* affines;
+    const float* lits;
+    uint32_t num_programs;
+    uint32_t max_insn;    /* largest instruction count in the batch */
+    uint32_t max_extra;   /* largest n_affine + n_lits */
+    uint32_t max_slots;   /* largest spill-slot count */
+};
+
+struct EvalProblem {
+    int mode;
+    const float* input;       /* [column][row] */
+    size_t input_ld;
+    uint32_t num_inputs;
+    const float* targets;     /* [target][row] */
+    size_t targets_ld;
+    uint32_t num_targets;
+    const float* banks;       /* [bank][slot] (+ program * program_bank_stride) */
+    size_t bank_stride;
+    size_t program_bank_stride;
+    size_t first_program;     /* index of the batch's first program within the run */
+    uint32_t num_constants;
+    uint32_t num_banks;       /* >= 1 */
+    uint32_t toggle_bits;
+    uint32_t fixed_permutation; /* materialize: the single permutation evaluated */
+    size_t num_rows;
+    float* output;
+    size_t out_program_stride; /* elements between consecutive programs */
+    size_t out_target_stride;  /* elements between consecutive targets  */
+};
+
+/* Launch geometry chosen by plan_launch(). */
+struct LaunchPlan {
+    int variant;              /* 0: 4 rows x 4 banks, 1: 8 x 2, 2: 16 x 1 per thread */
+    uint32_t warps;           /* per CTA */
+    uint32_t tile_rows;       /* rows staged per chunk, multiple of the pass size */
+    uint32_t programs_per_cta;
+    uint32_t row_splits;      /* CTAs sharing one program group, each with a row range */
+    size_t rows_per_split;
+    size_t smem_bytes;
+    uint32_t grid_x;
+    bool ok;
+};
+
+LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& problem, int sm_count, size_t smem_limit,
+                       int forced_variant /* -1 = automatic */);
+
+/* Enqueues the evaluation of one batch on `stream`.  The output range must have been
+ * cleared beforehand for the accumulating modes.  Returns the CUDA status of the launch. */
+cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem& problem, const LaunchPlan& plan, cudaStream_t stream);
+
+/* One-time per-device kernel attribute setup (dynamic shared memory opt-in). */
+cudaError_t configure_kernels();
+
+}  // namespace sb
+
+#endif

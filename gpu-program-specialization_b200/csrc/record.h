@@ -1,0 +1,90 @@
+/*
+ * record.h - the compact program record shared by the host encoder and the device
+ * evaluator.
+ *
+ * The reference turns every postfix program into machine code patched into a compiled
+ * kernel template (projects/secant/s_cubin_specialize.c:1203-1368).  Here the same
+ * traversal produces a short list of 8-byte instructions for an accumulator machine
+ * that one warp interprets:
+ *
+ *   - every thread owns a register tile acc[rows][banks];
+ *   - an instruction combines acc with ONE operand X (a dataset column of the staged
+ *     row tile, an entry of the per-warp constant area, a spill slot, or an immediate),
+ *     or applies a unary function to acc, or stores acc into a spill slot;
+ *   - spill slots and the order of evaluation are fixed by the encoder, so the device
+ *     never manipulates a stack.
+ *
+ * Instruction word 0:  bits 0..7 case id (SB_CASE_*), bits 8..15 aux, bits 16..31 operand index.
+ * Instruction word 1:  immediate f32 bits (IMM kind) or packed FMA operand indices.
+ */
+#ifndef SECANT_B200_RECORD_H
+#define SECANT_B200_RECORD_H
+
+#include <stdint.h>
+
+/* Operand kinds. */
+enum { SB_KIND_ROW = 0, SB_KIND_CST = 1, SB_KIND_SLOT = 2, SB_KIND_IMM = 3, SB_NUM_KINDS = 4 };
+/* For FMA operand descriptors kind 3 means "the accumulator". */
+enum { SB_FMA_ACC = 3 };
+
+/* Binary operations; R* = operand on the left, accumulator on the right. */
+enum { SB_BIN_ADD = 0, SB_BIN_SUB, SB_BIN_RSUB, SB_BIN_MUL, SB_BIN_DIV, SB_BIN_RDIV, SB_BIN_MIN, SB_BIN_MAX, SB_NUM_BIN };
+/* Unary operations, in the order of the reference opcodes they implement. */
+enum { SB_UN_NEG = 0, SB_UN_SQRT, SB_UN_RCP, SB_UN_ABS, SB_UN_SIN, SB_UN_COS, SB_UN_EX2, SB_UN_LG2, SB_UN_RSQRT,
+       SB_UN_TANH, SB_UN_EXP, SB_UN_LOG, SB_NUM_UN };
+
+enum {
+    SB_CASE_END = 0,
+    SB_CASE_LOAD = 1,                                  /* + kind           : acc = X            */
+    SB_CASE_STORE = SB_CASE_LOAD + SB_NUM_KINDS,       /* slot[index] = acc                     */
+    SB_CASE_BIN = SB_CASE_STORE + 1,                   /* + op * 4 + kind  : acc = acc (op) X   */
+    SB_CASE_UN = SB_CASE_BIN + SB_NUM_BIN * SB_NUM_KINDS, /* + op          : acc = f(acc)       */
+    SB_CASE_FMA = SB_CASE_UN + SB_NUM_UN,              /* acc = fma(A, B, C), generic operands  */
+    SB_NUM_CASES
+};
+
+typedef struct SbInsn {
+    uint32_t w0;
+    uint32_t w1;
+} SbInsn;
+
+static inline uint32_t sb_w0(unsigned case_id, unsigned aux, unsigned index) {
+    return (uint32_t)case_id | ((uint32_t)aux << 8) | ((uint32_t)index << 16);
+}
+/* FMA: aux = kindA | kindB << 2 | kindC << 4 ; w1 = idxA | idxB << 10 | idxC << 20. */
+
+/* One toggle site: instruction `insn` is replaced by alt[choice] for every permutation,
+ * choice = bit(bit0) + 2 * bit(bit1); bit1 == 0xff marks a two-way toggle. */
+typedef struct SbPatch {
+    uint16_t insn;
+    uint8_t bit0;
+    uint8_t bit1;
+    uint32_t pad;
+    SbInsn alt[4];
+} SbPatch;
+
+/* A derived constant-area entry: bank[slot] * scale + offset, both operations rounded. */
+typedef struct SbAffine {
+    uint32_t slot;
+    float scale;
+    float offset;
+} SbAffine;
+
+/* Per-program header; offsets index the pools of the batch the program belongs to.
+ * Constant-area entries are laid out [0, K) bank slots, [K, K + n_affine) derived
+ * entries, [K + n_affine, K + n_affine + n_lits) literals (only FMA operands use them). */
+typedef struct SbProgram {
+    uint32_t insn_off;
+    uint32_t patch_off;
+    uint32_t affine_off;
+    uint32_t lit_off;
+    uint16_t n_insn; /* including the END instruction */
+    uint16_t n_patch;
+    uint16_t n_affine;
+    uint16_t n_lits;
+    uint16_t n_slots;
+    uint16_t n_ops; /* arithmetic nodes after routine inlining, for work accounting */
+    uint32_t reserved;
+} SbProgram;
+
+#endif

@@ -1,0 +1,202 @@
+"""Runner: the reference's create / run / destroy call sequence over torch device memory.
+
+torch is used for device allocations, streams and (in the benchmark) torch.distributed
+only; every evaluation goes through the C-ABI of libsecant_b200.so.  Method names and
+argument meaning follow the reference run descriptors (projects/secant/secant.h:418-540):
+matrices are [column][row] float32, outputs are caller-visible tensors the library clears
+and writes.
+"""
+import ctypes as C
+
+import torch
+
+from . import abi
+
+_SHAPE_RECIPE = {
+    abi.SHAPE_MATERIALIZE: abi.MaterializeRecipe,
+    abi.SHAPE_SSE: abi.TiledRecipe,
+    abi.SHAPE_AFFINE_STATS: abi.TiledRecipe,
+    abi.SHAPE_TOGGLE_SSE: abi.ToggleRecipe,
+}
+
+
+def make_recipe(shape, num_inputs, num_targets=1, num_constants=0):
+    r = abi.init_header(_SHAPE_RECIPE[shape](), abi.RECIPE_VERSION, shape)
+    r.num_kernels = 8
+    r.asts_per_kernel = 8 if shape == abi.SHAPE_TOGGLE_SSE else 4
+    r.num_inputs = num_inputs
+    r.patch_capacity_instructions = 2048
+    if shape != abi.SHAPE_MATERIALIZE:
+        r.num_targets = num_targets
+        r.tile_rows = 128
+        r.threads_per_block = 128
+    if shape == abi.SHAPE_TOGGLE_SSE:
+        r.num_constants = num_constants
+    return r
+
+
+def _matrix(t, leading_dimension=None):
+    m = abi.DeviceMatrix()
+    if t is not None:
+        m.address = t.data_ptr()
+        m.num_elements = t.numel()
+        m.leading_dimension = leading_dimension if leading_dimension is not None else (t.shape[-1] if t.dim() else 1)
+    return m
+
+
+class Runner:
+    """One runner handle for one kernel shape, bound to torch's current CUDA context."""
+
+    def __init__(self, shape, num_inputs, num_targets=1, num_constants=0, workers=1, streams=1, via_plan=False):
+        if not torch.cuda.is_available():
+            raise RuntimeError("a CUDA device is required: this library has no CPU fallback")
+        torch.cuda.init()
+        torch.zeros(1, device="cuda")  # make sure torch's primary context is current on this thread
+        self.lib = abi.load()
+        self.shape = shape
+        self.num_inputs, self.num_targets, self.num_constants = num_inputs, num_targets, num_constants
+        self.recipe = make_recipe(shape, num_inputs, num_targets, num_constants)
+        self.handle = C.c_void_p()
+        options = abi.runner_options(workers, streams)
+        if via_plan:
+            # the reference sequence: source -> (caller compiles) -> plan -> runner
+            size = C.c_size_t()
+            abi.check(self.lib.secant_cubin_source_size(C.byref(self.recipe), C.byref(size)), "source_size")
+            self._source = C.create_string_buffer(size.value)
+            abi.check(self.lib.secant_cubin_source_write(C.byref(self.recipe), self._source, size.value), "source_write")
+            self._cubin = C.create_string_buffer(self._source.raw, size.value)  # stands in for the compiled binary
+            need = C.c_size_t()
+            abi.check(self.lib.secant_cubin_plan_storage_size(C.byref(self.recipe), self._cubin, size.value, C.byref(need)),
+                      "plan_storage_size")
+            self._plan_storage = C.create_string_buffer(need.value)
+            self._plan = C.c_void_p()
+            abi.check(self.lib.secant_cubin_plan_init(C.byref(self.recipe), self._cubin, size.value, self._plan_storage,
+                                                      need.value, C.byref(self._plan)), "plan_init")
+            abi.check(self.lib.secant_cubin_runner_create(self._plan, self._cubin, size.value, C.byref(options),
+                                                          C.byref(self.handle)), "runner_create")
+        else:
+            abi.check(self.lib.secant_b200_runner_create(C.byref(self.recipe), C.byref(options), C.byref(self.handle)),
+                      "secant_b200_runner_create")
+        self.stats = abi.runner_stats()
+
+    # -- request builders -------------------------------------------------------
+    def toggle_request(self, packed, x, y, banks, num_banks, toggle_bits, out, out_ld=None, bank_stride=None,
+                       program_bank_stride=0, first_program_index=0):
+        ext = abi.ToggleRunExt()
+        run = ext.base
+        abi.init_header(run, abi.RUN_VERSION, abi.SHAPE_TOGGLE_SSE)
+        run.header.struct_size = C.sizeof(ext)
+        packed.fill(run.programs)
+        run.input = _matrix(x)
+        run.targets = _matrix(y)
+        if banks is not None and self.num_constants:
+            run.constants.address = banks.data_ptr()
+            run.constants.num_elements = banks.numel()
+            run.constants.bank_stride = bank_stride if bank_stride is not None else banks.shape[-1]
+        run.num_rows = y.shape[-1]
+        run.num_targets = y.shape[0]
+        run.num_banks = num_banks
+        run.toggle_bits = toggle_bits
+        run.output = _matrix(out, out_ld if out_ld is not None else out.shape[-1])
+        ext.program_bank_stride = program_bank_stride
+        ext.first_program_index = first_program_index
+        return ext
+
+    def static_request(self, packed, x, y, out, out_ld=None):
+        run = abi.init_header(abi.StaticRun(), abi.RUN_VERSION, self.shape)
+        packed.fill(run.programs)
+        run.input = _matrix(x)
+        run.targets = _matrix(y)
+        run.num_rows = x.shape[-1]
+        run.num_targets = y.shape[0]
+        run.output = _matrix(out, out_ld if out_ld is not None else out.shape[-1])
+        return run
+
+    def materialize_request(self, packed, x, out, out_ld=None):
+        run = abi.init_header(abi.MaterializeRun(), abi.RUN_VERSION, abi.SHAPE_MATERIALIZE)
+        packed.fill(run.programs)
+        run.input = _matrix(x)
+        run.num_rows = x.shape[-1]
+        run.output = _matrix(out, out_ld if out_ld is not None else out.shape[-1])
+        return run
+
+    # -- execution --------------------------------------------------------------
+    def run(self, request, check=True):
+        code = self.lib.secant_cubin_runner_run(self.handle, C.byref(request), C.byref(self.stats))
+        if check:
+            abi.check(code, "secant_cubin_runner_run: " + self.last_error())
+        return code
+
+    def run_batch(self, requests, check=True):
+        ptrs = (C.c_void_p * len(requests))(*[C.addressof(r) for r in requests])
+        code = self.lib.secant_cubin_runner_run_batch(self.handle, ptrs, len(requests), C.byref(self.stats))
+        if check:
+            abi.check(code, "secant_cubin_runner_run_batch: " + self.last_error())
+        return code
+
+    def last_error(self):
+        return (self.lib.secant_b200_runner_last_error(self.handle) or b"").decode()
+
+    # -- conveniences -------------------------------------------------------------
+    def toggle_sse(self, packed, x, y, banks, num_banks, toggle_bits, **kw):
+        configs = num_banks << toggle_bits
+        out = torch.empty((len(packed.asts), y.shape[0], configs), dtype=torch.float32, device=y.device)
+        self.run(self.toggle_request(packed, x, y, banks, num_banks, toggle_bits, out, **kw))
+        return out
+
+    def sse(self, packed, x, y):
+        out = torch.empty((len(packed.asts), y.shape[0]), dtype=torch.float32, device=x.device)
+        self.run(self.static_request(packed, x, y, out))
+        return out
+
+    def affine_stats(self, packed, x, y):
+        out = torch.empty((len(packed.asts), 2 + y.shape[0]), dtype=torch.float32, device=x.device)
+        self.run(self.static_request(packed, x, y, out))
+        return out
+
+    def materialize(self, packed, x):
+        out = torch.empty((len(packed.asts), x.shape[-1]), dtype=torch.float32, device=x.device)
+        self.run(self.materialize_request(packed, x, out))
+        return out
+
+    def force_variant(self, variant):
+        self.lib.secant_b200_runner_force_variant(self.handle, variant)
+
+    def population(self, packed, toggle_bits=0):
+        return Population(self, packed, toggle_bits)
+
+    def destroy(self):
+        if self.handle:
+            abi.check(self.lib.secant_cubin_runner_destroy(self.handle), "runner_destroy")
+            self.handle = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.destroy()
+
+
+class Population:
+    """Programs validated, encoded and uploaded once; scored many times (extension API)."""
+
+    def __init__(self, runner, packed, toggle_bits=0):
+        self.runner = runner
+        self.packed = packed
+        self.handle = C.c_void_p()
+        pset = abi.ProgramSet()
+        packed.fill(pset)
+        abi.check(runner.lib.secant_b200_population_create(runner.handle, C.byref(pset), toggle_bits, C.byref(self.handle)),
+                  "secant_b200_population_create")
+        self.num_ops = runner.lib.secant_b200_population_num_ops(self.handle)
+
+    def run(self, request, check=True):
+        code = self.runner.lib.secant_b200_population_run(self.handle, C.byref(request), C.byref(self.runner.stats))
+        if check:
+            abi.check(code, "secant_b200_population_run: " + self.runner.last_error())
+        return code
+
+    def destroy(self):
+        if self.handle:
+            abi.check(self.runner.lib.secant_b200_population_destroy(self.handle), "population_destroy")
+            self.handle = C.c_void_p()

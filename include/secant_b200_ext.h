@@ -1,0 +1,85 @@
+/*
+ * secant_b200_ext.h - entry points and descriptor fields this library adds to the
+ * reference C API.  Included by secant_b200.h; do not include it on its own.
+ *
+ * None of these has a counterpart in the reference header.  They exist because the
+ * population-scoring workloads this library is built for need things the reference API
+ * cannot express (per-program coefficient banks, a runner without the NVRTC round trip,
+ * device-side best-configuration and top-k reductions, RK4 rollout scoring).
+ */
+#ifndef SECANT_B200_EXT_H_INCLUDED
+#define SECANT_B200_EXT_H_INCLUDED
+
+/*
+ * Toggle-SSE run with appended optional fields.  The reference descriptor rule
+ * (secant.h:49-56) allows a larger struct_size whose extra fields default to zero, so this
+ * struct is passed to secant_cubin_runner_run()/run_batch() like the plain one, with
+ * base.header.struct_size = sizeof(SecantB200ToggleSSERun).
+ *
+ *  program_bank_stride  elements between the coefficient tables of consecutive programs.
+ *                       0 (default) = one [bank][slot] table shared by every program,
+ *                       which is the reference behaviour (secant.h:506-514).  Non-zero =
+ *                       program a reads bank b, slot k at
+ *                       constants.address[a*program_bank_stride + b*bank_stride + k].
+ *  first_program_index  added to the program index when addressing per-program banks,
+ *                       so that a rank holding a slice of a population can point at the
+ *                       whole table.  Ignored when program_bank_stride is 0.
+ */
+typedef struct SecantB200ToggleSSERun {
+    SecantCubinToggleSSERun base;
+    size_t program_bank_stride;
+    size_t first_program_index;
+} SecantB200ToggleSSERun;
+
+static inline SecantB200ToggleSSERun secant_b200_toggle_sse_run_init(void) {
+    SECANT_B200_ZERO_INIT(SecantB200ToggleSSERun, v);
+    v.base = secant_cubin_toggle_sse_run_init();
+    v.base.header.struct_size = (uint32_t)sizeof(v);
+    return v;
+}
+
+/*
+ * Creates a runner straight from a recipe, without generating source, compiling it and
+ * inspecting a binary first.  Equivalent to the reference sequence source_write -> NVRTC ->
+ * plan_init -> runner_create (projects/secant/tests/toggle_cuda_test.c:65-115) with the
+ * compile step removed; the runner owns its plan.  Same context rules as
+ * secant_cubin_runner_create: the CUDA context current at creation must be current for
+ * every run and for destroy.
+ */
+SECANT_DEC SecantResult secant_b200_runner_create(const SecantCubinRecipeHeader* recipe,
+                                                  const SecantCubinRunnerOptions* options,
+                                                  SecantCubinRunner* runner_ret);
+
+/*
+ * Device-resident populations.  secant_b200_population_create() validates, encodes and
+ * uploads a program set once; secant_b200_population_run() then scores it against any
+ * run request of the runner's shape (the request's `programs` field is ignored) without
+ * re-reading, re-encoding or re-uploading the programs -- the case of a search loop that
+ * refits coefficient banks or swaps data for an unchanged population
+ * (projects/secant-sr/toggle/src/cuda.c:368-477 scores the same programs with new banks).
+ * toggle_bits is the smallest toggle_bits any later run will use.  A population belongs
+ * to the runner it was created from and must be destroyed before that runner.
+ */
+typedef struct SecantB200PopulationImpl* SecantB200Population;
+SECANT_DEC SecantResult secant_b200_population_create(SecantCubinRunner runner, const SecantAstProgramSet* programs,
+                                                      uint32_t toggle_bits, SecantB200Population* population_ret);
+SECANT_DEC SecantResult secant_b200_population_run(SecantB200Population population, const SecantCubinRunHeader* run,
+                                                   SecantRunnerStats* stats_ret);
+SECANT_DEC SecantResult secant_b200_population_run_batch(SecantB200Population population,
+                                                         const SecantCubinRunHeader* const* runs, size_t num_runs,
+                                                         SecantRunnerStats* stats_ret);
+/* Arithmetic nodes (after routine inlining) summed over the population, for work accounting. */
+SECANT_DEC uint64_t secant_b200_population_num_ops(SecantB200Population population);
+SECANT_DEC SecantResult secant_b200_population_destroy(SecantB200Population population);
+
+/* Pins the per-thread register tile used by the evaluator: 0 = 4 rows x 4 banks,
+ * 1 = 8 x 2, 2 = 16 x 1, -1 = automatic.  Every variant computes the same values. */
+SECANT_DEC void secant_b200_runner_force_variant(SecantCubinRunner runner, int variant);
+
+/* Human-readable description of the last CUDA error seen by a runner (empty when none). */
+SECANT_DEC const char* secant_b200_runner_last_error(SecantCubinRunner runner);
+
+/* Number of kernels this library has launched in the calling process so far. */
+SECANT_DEC uint64_t secant_b200_kernel_launch_count(void);
+
+#endif /* SECANT_B200_EXT_H_INCLUDED */
