@@ -27,6 +27,7 @@
  * program-level multiplies and adds (only FMA_F32 fuses).
  */
 #include "evaluator.cuh"
+#include "sbmath.cuh"
 
 #include <math_constants.h>
 
@@ -45,6 +46,8 @@ struct Geom {
     uint32_t tile_bytes;
     unsigned long long rows_per_split;
     uint32_t use_atomics;
+    uint32_t groups_per_item; /* configuration groups one queue item covers */
+    uint32_t scratch_slot;    /* spill slot reserved for the out-of-line unary functions */
 };
 
 template <int OP>
@@ -62,17 +65,61 @@ __device__ __forceinline__ float binop(float a, float x) {
 template <int OP>
 __device__ __forceinline__ float unop(float a) {
     if (OP == SB_UN_NEG) return -a;
-    if (OP == SB_UN_SQRT) return __fsqrt_rn(a);
-    if (OP == SB_UN_RCP) return __frcp_rn(a);
-    if (OP == SB_UN_ABS) return fabsf(a);
-    if (OP == SB_UN_SIN) return sinf(a);
-    if (OP == SB_UN_COS) return cosf(a);
-    if (OP == SB_UN_EX2) return exp2f(a);
-    if (OP == SB_UN_LG2) return log2f(a);
-    if (OP == SB_UN_RSQRT) return __frcp_rn(__fsqrt_rn(a)); /* host: 1 / sqrtf(x), two roundings */
-    if (OP == SB_UN_TANH) return tanhf(a);
-    if (OP == SB_UN_EXP) return expf(a);
-    return logf(a);
+    return fabsf(a);
+}
+
+/* Unary functions that are rare in scoring workloads and bulky when unrolled over the whole
+ * register tile.  They run element by element over a copy of the tile in shared memory,
+ * so their bodies exist once in the kernel. */
+__device__ __noinline__ float rare_unop(unsigned op, float a) {
+    switch (op) {
+    case SB_UN_SQRT: return __fsqrt_rn(a);
+    case SB_UN_RCP: return __frcp_rn(a);
+    case SB_UN_RSQRT: return __frcp_rn(__fsqrt_rn(a)); /* host: 1 / sqrtf(x), two roundings */
+    case SB_UN_LG2: return log2f(a);
+    default: return tanhf(a);
+    }
+}
+
+/* FMA_F32 takes three arbitrary operands.  It is rare in scoring workloads, so it runs
+ * element by element over shared memory (the caller parks the accumulator in the scratch
+ * slot first and reloads it afterwards) instead of being unrolled for every combination of
+ * operand kinds.  Nothing here touches the register tile, which therefore stays in
+ * registers. */
+template <int RR, int RC>
+__device__ __noinline__ void fma_over_scratch(uint2 ins, const float* rowp, uint32_t tile_ld, const float* cst,
+                                              float4* slots, uint32_t scratch_slot) {
+    constexpr int V = RR * RC;
+    const unsigned kinds = (ins.x >> 8) & 0x3fu;
+    float* out = reinterpret_cast<float*>(slots + (size_t)scratch_slot * (V / 4) * 32);
+#pragma unroll 1
+    for (int k = 0; k < V; ++k) {
+        float v[3];
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            const unsigned kind = (kinds >> (2 * i)) & 3u;
+            const uint32_t index = (ins.y >> (10 * i)) & 1023u;
+            const int r = k / RC, c = k % RC;
+            if (kind == SB_KIND_ROW) v[i] = rowp[(size_t)index * tile_ld + (r / 4) * 128 + (r % 4)];
+            else if (kind == SB_KIND_CST) v[i] = cst[index * RC + c];
+            else {
+                const uint32_t slot = kind == SB_FMA_ACC ? scratch_slot : index;
+                v[i] = reinterpret_cast<const float*>(slots + (size_t)slot * (V / 4) * 32)[(k >> 2) * 128 + (k & 3)];
+            }
+        }
+        out[(k >> 2) * 128 + (k & 3)] = __fmaf_rn(v[0], v[1], v[2]);
+    }
+}
+
+/* Applies a rare unary function to every element of the tile parked in the scratch slot. */
+template <int V>
+__device__ __noinline__ void rare_over_scratch(unsigned op, float4* slots, uint32_t scratch_slot) {
+    float* flat = reinterpret_cast<float*>(slots + (size_t)scratch_slot * (V / 4) * 32);
+#pragma unroll 1
+    for (int k = 0; k < V; ++k) {
+        float* p = flat + (k >> 2) * 128 + (k & 3);
+        *p = rare_unop(op, *p);
+    }
 }
 
 template <int RR, int RC>
@@ -121,33 +168,6 @@ struct Machine {
         for (int j = 0; j < V / 4; ++j) q[j * 32] = make_float4(flat[4 * j], flat[4 * j + 1], flat[4 * j + 2], flat[4 * j + 3]);
     }
 
-    /* Generic operand expansion used by FMA only. */
-    __device__ __forceinline__ void expand(unsigned kind, uint32_t index, const float* rowp, uint32_t tile_ld,
-                                           const float* cst, const float4* slots, float (&out)[RR][RC]) const {
-        if (kind == SB_FMA_ACC) {
-#pragma unroll
-            for (int r = 0; r < RR; ++r)
-#pragma unroll
-                for (int c = 0; c < RC; ++c) out[r][c] = acc[r][c];
-        } else if (kind == SB_KIND_ROW) {
-            float x[RR];
-            fetch_row(rowp, tile_ld, index, x);
-#pragma unroll
-            for (int r = 0; r < RR; ++r)
-#pragma unroll
-                for (int c = 0; c < RC; ++c) out[r][c] = x[r];
-        } else if (kind == SB_KIND_CST) {
-            float x[RC];
-            fetch_cst(cst, index, x);
-#pragma unroll
-            for (int r = 0; r < RR; ++r)
-#pragma unroll
-                for (int c = 0; c < RC; ++c) out[r][c] = x[c];
-        } else {
-            fetch_slot(slots, index, out);
-        }
-    }
-
 #define SB_FOR_TILE _Pragma("unroll") for (int r = 0; r < RR; ++r) _Pragma("unroll") for (int c = 0; c < RC; ++c)
 
 #define SB_BIN_CASES(OP)                                                                             \
@@ -171,14 +191,26 @@ struct Machine {
 #define SB_UN_CASE(OP) \
     case SB_CASE_UN + OP: { SB_FOR_TILE acc[r][c] = unop<OP>(acc[r][c]); break; }
 
+/* applies an out-of-line four-element function to the whole tile */
+#define SB_FOR_QUADS(CALL)                                                                           \
+    {                                                                                                \
+        float* flat = &acc[0][0];                                                                    \
+        _Pragma("unroll") for (int j = 0; j < V / 4; ++j) {                                          \
+            const float4 in = make_float4(flat[4 * j], flat[4 * j + 1], flat[4 * j + 2], flat[4 * j + 3]); \
+            const float4 o = CALL;                                                                   \
+            flat[4 * j] = o.x; flat[4 * j + 1] = o.y; flat[4 * j + 2] = o.z; flat[4 * j + 3] = o.w;  \
+        }                                                                                            \
+    }
+
     /* Runs the warp's program once over the RR*32 rows starting at rowp. */
     __device__ __forceinline__ void run(const SbInsn* exec, const float* rowp, uint32_t tile_ld, const float* cst,
-                                        float4* slots) {
+                                        float4* slots, uint32_t scratch_slot) {
         const uint2* ip = reinterpret_cast<const uint2*>(exec);
-        SB_FOR_TILE acc[r][c] = 0.0f;
+        uint2 next = *ip++; /* the buffer holds one padding entry after END */
 #pragma unroll 1
         for (;;) {
-            const uint2 ins = *ip++;
+            const uint2 ins = next;
+            next = *ip++;
             const uint32_t idx = ins.x >> 16;
             switch (ins.x & 0xffu) {
             case SB_CASE_END:
@@ -205,30 +237,71 @@ struct Machine {
             SB_BIN_CASES(SB_BIN_SUB)
             SB_BIN_CASES(SB_BIN_RSUB)
             SB_BIN_CASES(SB_BIN_MUL)
-            SB_BIN_CASES(SB_BIN_DIV)
-            SB_BIN_CASES(SB_BIN_RDIV)
+            /* IEEE division is ~10 instructions per element: the eight operand-kind cases
+             * only expand the operand, then share one body per direction. */
+            case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_ROW:
+            case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_ROW:
+            case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_CST:
+            case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_CST:
+            case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_SLOT:
+            case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_SLOT:
+            case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_IMM:
+            case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_IMM: {
+                const unsigned rel = (ins.x & 0xffu) - SB_CASE_BIN;
+                const unsigned kind = rel % SB_NUM_KINDS;
+                float xv[RR][RC];
+                if (kind == SB_KIND_ROW) {
+                    float x[RR]; fetch_row(rowp, tile_ld, idx, x);
+                    SB_FOR_TILE xv[r][c] = x[r];
+                } else if (kind == SB_KIND_CST) {
+                    float x[RC]; fetch_cst(cst, idx, x);
+                    SB_FOR_TILE xv[r][c] = x[c];
+                } else if (kind == SB_KIND_SLOT) {
+                    fetch_slot(slots, idx, xv);
+                } else {
+                    const float x = __uint_as_float(ins.y);
+                    SB_FOR_TILE xv[r][c] = x;
+                }
+                if (rel / SB_NUM_KINDS == SB_BIN_RDIV) { /* operand / acc: swap so that one body divides acc by xv */
+                    SB_FOR_TILE { const float t = acc[r][c]; acc[r][c] = xv[r][c]; xv[r][c] = t; }
+                }
+                {
+                    float* fa = &acc[0][0];
+                    const float* fx = &xv[0][0];
+#pragma unroll
+                    for (int j = 0; j < V / 4; ++j) {
+                        const float4 o = sbm::div4(make_float4(fa[4 * j], fa[4 * j + 1], fa[4 * j + 2], fa[4 * j + 3]),
+                                                   make_float4(fx[4 * j], fx[4 * j + 1], fx[4 * j + 2], fx[4 * j + 3]));
+                        fa[4 * j] = o.x; fa[4 * j + 1] = o.y; fa[4 * j + 2] = o.z; fa[4 * j + 3] = o.w;
+                    }
+                }
+                break; }
             SB_BIN_CASES(SB_BIN_MIN)
             SB_BIN_CASES(SB_BIN_MAX)
             SB_UN_CASE(SB_UN_NEG)
-            SB_UN_CASE(SB_UN_SQRT)
-            SB_UN_CASE(SB_UN_RCP)
             SB_UN_CASE(SB_UN_ABS)
-            SB_UN_CASE(SB_UN_SIN)
-            SB_UN_CASE(SB_UN_COS)
-            SB_UN_CASE(SB_UN_EX2)
-            SB_UN_CASE(SB_UN_LG2)
-            SB_UN_CASE(SB_UN_RSQRT)
-            SB_UN_CASE(SB_UN_TANH)
-            SB_UN_CASE(SB_UN_EXP)
-            SB_UN_CASE(SB_UN_LOG)
-            case SB_CASE_FMA: {
-                const unsigned kinds = (ins.x >> 8) & 0x3fu;
-                float a[RR][RC], b[RR][RC], d[RR][RC];
-                expand(kinds & 3u, ins.y & 1023u, rowp, tile_ld, cst, slots, a);
-                expand((kinds >> 2) & 3u, (ins.y >> 10) & 1023u, rowp, tile_ld, cst, slots, b);
-                expand((kinds >> 4) & 3u, (ins.y >> 20) & 1023u, rowp, tile_ld, cst, slots, d);
-                SB_FOR_TILE acc[r][c] = __fmaf_rn(a[r][c], b[r][c], d[r][c]);
+            case SB_CASE_UN + SB_UN_EX2: SB_FOR_QUADS(sbm::exp2_4(in)) break;
+            case SB_CASE_UN + SB_UN_EXP: SB_FOR_QUADS(sbm::exp4(in)) break;
+            case SB_CASE_UN + SB_UN_LOG: SB_FOR_QUADS(sbm::log4(in)) break;
+            case SB_CASE_UN + SB_UN_SIN:
+            case SB_CASE_UN + SB_UN_COS: { /* cos x = sin(x + pi/2): one body, shifted quadrant */
+                const int shift = (int)(ins.x & 0xffu) - (SB_CASE_UN + SB_UN_SIN);
+                SB_FOR_QUADS(sbm::sincos4(in, shift))
                 break; }
+            case SB_CASE_UN + SB_UN_SQRT:
+            case SB_CASE_UN + SB_UN_RCP:
+            case SB_CASE_UN + SB_UN_LG2:
+            case SB_CASE_UN + SB_UN_RSQRT:
+            case SB_CASE_UN + SB_UN_TANH:
+                store_slot(slots, scratch_slot);
+                rare_over_scratch<V>((ins.x & 0xffu) - SB_CASE_UN, slots, scratch_slot);
+                fetch_slot(slots, scratch_slot, acc);
+                break;
+            case SB_CASE_FMA:
+                store_slot(slots, scratch_slot);
+                fma_over_scratch<RR, RC>(ins, rowp, tile_ld, cst, slots, scratch_slot);
+                fetch_slot(slots, scratch_slot, acc);
+                break;
             default:
                 return; /* unreachable for records produced by the encoder */
             }
@@ -242,8 +315,10 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+/* 16-value tiles run 16 warps per CTA within 128 registers; 32-value tiles need more
+ * registers per thread and run 12 warps. */
 template <int RR, int RC>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(RR * RC > 16 ? 384 : 512, 1)
 eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
     using M = Machine<RR, RC>;
     extern __shared__ __align__(16) unsigned char smem[];
@@ -261,12 +336,16 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
     const uint32_t prog_count = min(geom.programs_per_cta, batch.num_programs - prog_begin);
     const size_t row_begin = (size_t)split * geom.rows_per_split;
     const size_t row_end = min(prob.num_rows, row_begin + (size_t)geom.rows_per_split);
-    const uint32_t ncols = prob.num_inputs + (prob.mode == EVAL_MATERIALIZE ? 0u : prob.num_targets);
+    const bool materialize = prob.mode == EVAL_MATERIALIZE;
+    const uint32_t ncols = prob.num_inputs + (materialize ? 0u : prob.num_targets);
     const uint32_t tile_ld = geom.tile_rows;
     const uint32_t K = prob.num_constants;
     const uint32_t T = prob.num_targets;
-    const unsigned long long nperm = prob.mode == EVAL_MATERIALIZE ? 1ull : (1ull << prob.toggle_bits);
-    const uint32_t ngroups = prob.mode == EVAL_MATERIALIZE ? 1u : (prob.num_banks + RC - 1) / RC;
+    /* configuration groups of one program: permutation-major, RC banks per group */
+    const uint32_t bank_groups = materialize ? 1u : (prob.num_banks + RC - 1) / RC;
+    const unsigned long long cfg_groups = materialize ? 1ull : ((unsigned long long)bank_groups << prob.toggle_bits);
+    const unsigned long long items_per_program = (cfg_groups + geom.groups_per_item - 1) / geom.groups_per_item;
+    const unsigned long long num_items = items_per_program * prog_count;
 
     for (size_t c0 = row_begin; c0 < row_end; c0 += geom.tile_rows) {
         const uint32_t chunk_rows = (uint32_t)min((size_t)geom.tile_rows, row_end - c0);
@@ -282,149 +361,158 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
         if (threadIdx.x == 0) *queue = 0u;
         __syncthreads();
 
+        uint32_t loaded = 0xffffffffu; /* program currently held in this warp's exec buffer */
+        SbProgram pr;
         for (;;) {
-            unsigned int pi = 0;
-            if (lane == 0) pi = atomicAdd(queue, 1u);
-            pi = __shfl_sync(0xffffffffu, pi, 0);
-            if (pi >= prog_count) break;
+            unsigned int item = 0;
+            if (lane == 0) item = atomicAdd(queue, 1u);
+            item = __shfl_sync(0xffffffffu, item, 0);
+            if (item >= num_items) break;
+            const uint32_t pi = (uint32_t)(item / items_per_program);
+            const unsigned long long first_group = (item % items_per_program) * geom.groups_per_item;
+            const unsigned long long last_group = min(cfg_groups, first_group + geom.groups_per_item);
             const uint32_t lp = prog_begin + pi;           /* index inside the batch */
             const size_t gp = prob.first_program + lp;     /* index inside the run */
-            const SbProgram pr = batch.programs[lp];
             __syncwarp();
-            for (uint32_t i = lane; i < pr.n_insn; i += 32) exec[i] = batch.insns[pr.insn_off + i];
-            for (uint32_t i = lane; i < (uint32_t)pr.n_lits * RC; i += 32)
-                cst[(K + pr.n_affine) * RC + i] = batch.lits[pr.lit_off + i / RC];
+            if (lp != loaded) {
+                pr = batch.programs[lp];
+                for (uint32_t i = lane; i < pr.n_insn; i += 32) exec[i] = batch.insns[pr.insn_off + i];
+                if (lane == 0) exec[pr.n_insn] = SbInsn{0u, 0u}; /* padding read by the instruction prefetch */
+                for (uint32_t i = lane; i < (uint32_t)pr.n_lits * RC; i += 32)
+                    cst[(K + pr.n_affine) * RC + i] = batch.lits[pr.lit_off + i / RC];
+                loaded = lp;
+            }
             const float* bank_base = prob.banks ? prob.banks + gp * prob.program_bank_stride : nullptr;
+            unsigned long long patched_for = ~0ull;
 
-            for (unsigned long long perm = 0; perm < nperm; ++perm) {
-                const unsigned long long permutation = prob.mode == EVAL_MATERIALIZE ? prob.fixed_permutation : perm;
-                if (pr.n_patch) {
-                    __syncwarp();
+            for (unsigned long long cg = first_group; cg < last_group; ++cg) {
+                const unsigned long long perm = materialize ? prob.fixed_permutation : cg / bank_groups;
+                const uint32_t bg = (uint32_t)(cg % bank_groups);
+                __syncwarp();
+                if (pr.n_patch && perm != patched_for) {
                     for (uint32_t i = lane; i < pr.n_patch; i += 32) {
                         const SbPatch* p = batch.patches + pr.patch_off + i;
-                        unsigned choice = (unsigned)(permutation >> p->bit0) & 1u;
-                        if (p->bit1 != 0xffu) choice |= ((unsigned)(permutation >> p->bit1) & 1u) << 1;
+                        unsigned choice = (unsigned)(perm >> p->bit0) & 1u;
+                        if (p->bit1 != 0xffu) choice |= ((unsigned)(perm >> p->bit1) & 1u) << 1;
                         exec[p->insn] = p->alt[choice];
                     }
+                    patched_for = perm;
                 }
-                for (uint32_t bg = 0; bg < ngroups; ++bg) {
-                    __syncwarp();
-                    for (uint32_t e = lane; e < (K + pr.n_affine) * RC; e += 32) {
-                        const uint32_t entry = e / RC, c = e % RC, bank = bg * RC + c;
-                        float v = 0.0f;
-                        if (bank < prob.num_banks) {
-                            if (entry < K) {
-                                v = __ldg(bank_base + (size_t)bank * prob.bank_stride + entry);
-                            } else {
-                                const SbAffine a = batch.affines[pr.affine_off + entry - K];
-                                v = __fadd_rn(__fmul_rn(__ldg(bank_base + (size_t)bank * prob.bank_stride + a.slot), a.scale), a.offset);
-                            }
+                for (uint32_t e = lane; e < (K + pr.n_affine) * RC; e += 32) {
+                    const uint32_t entry = e / RC, c = e % RC, bank = bg * RC + c;
+                    float v = 0.0f;
+                    if (bank < prob.num_banks) {
+                        if (entry < K) {
+                            v = __ldg(bank_base + (size_t)bank * prob.bank_stride + entry);
+                        } else {
+                            const SbAffine a = batch.affines[pr.affine_off + entry - K];
+                            v = __fadd_rn(__fmul_rn(__ldg(bank_base + (size_t)bank * prob.bank_stride + a.slot), a.scale), a.offset);
                         }
-                        cst[e] = v;
                     }
-                    if (T > 1 || prob.mode == EVAL_AFFINE_STATS)
-                        for (uint32_t e = lane; e < (T + 2) * RC; e += 32) tacc[e] = 0.0f;
-                    __syncwarp();
+                    cst[e] = v;
+                }
+                if (T > 1 || prob.mode == EVAL_AFFINE_STATS)
+                    for (uint32_t e = lane; e < (T + 2) * RC; e += 32) tacc[e] = 0.0f;
+                __syncwarp();
 
-                    M m;
-                    float part[RC];
+                M m;
+                float part[RC];
 #pragma unroll
-                    for (int c = 0; c < RC; ++c) part[c] = 0.0f;
+                for (int c = 0; c < RC; ++c) part[c] = 0.0f;
 
 #pragma unroll 1
-                    for (uint32_t pass = 0; pass < npass; ++pass) {
-                        const float* rowp = tile + pass * M::PASS + lane * 4;
-                        m.run(exec, rowp, tile_ld, cst, slots);
-                        const uint32_t row0 = pass * M::PASS + lane * 4; /* first row of this thread in the chunk */
-                        const bool full = (pass + 1) * M::PASS <= chunk_rows;
-                        if (prob.mode == EVAL_MATERIALIZE) {
-                            float* out = prob.output + gp * prob.out_program_stride + c0;
+                for (uint32_t pass = 0; pass < npass; ++pass) {
+                    const float* rowp = tile + pass * M::PASS + lane * 4;
+                    m.run(exec, rowp, tile_ld, cst, slots, geom.scratch_slot);
+                    const uint32_t row0 = pass * M::PASS + lane * 4; /* first row of this thread in the chunk */
+                    const bool full = (pass + 1) * M::PASS <= chunk_rows;
+                    if (materialize) {
+                        float* out = prob.output + gp * prob.out_program_stride + c0;
 #pragma unroll
-                            for (int r = 0; r < RR; ++r) {
-                                const uint32_t row = row0 + (r / 4) * 128 + (r % 4);
-                                if (row < chunk_rows) out[row] = m.acc[r][0];
-                            }
-                        } else if (prob.mode == EVAL_SSE && T == 1) {
-                            float t[RR];
-                            m.fetch_row(rowp, tile_ld, prob.num_inputs, t);
-                            if (full) {
+                        for (int r = 0; r < RR; ++r) {
+                            const uint32_t row = row0 + (r / 4) * 128 + (r % 4);
+                            if (row < chunk_rows) out[row] = m.acc[r][0];
+                        }
+                    } else if (prob.mode == EVAL_SSE && T == 1) {
+                        float t[RR];
+                        m.fetch_row(rowp, tile_ld, prob.num_inputs, t);
+                        if (full) {
 #pragma unroll
-                                for (int r = 0; r < RR; ++r)
-#pragma unroll
-                                    for (int c = 0; c < RC; ++c) {
-                                        const float e = __fsub_rn(m.acc[r][c], t[r]);
-                                        part[c] = __fmaf_rn(e, e, part[c]);
-                                    }
-                            } else {
-#pragma unroll
-                                for (int r = 0; r < RR; ++r) {
-                                    const bool ok = row0 + (r / 4) * 128 + (r % 4) < chunk_rows;
-#pragma unroll
-                                    for (int c = 0; c < RC; ++c) {
-                                        const float e = ok ? __fsub_rn(m.acc[r][c], t[r]) : 0.0f;
-                                        part[c] = __fmaf_rn(e, e, part[c]);
-                                    }
-                                }
-                            }
-                        } else {
-                            /* several targets, or affine statistics: per-pass warp reduction into
-                             * the warp's shared accumulators tacc[quantity][bank] */
-                            const uint32_t nq = prob.mode == EVAL_AFFINE_STATS ? T + 2 : T;
-                            for (uint32_t q = 0; q < nq; ++q) {
-                                float t[RR];
-                                const bool is_target = prob.mode == EVAL_SSE || q >= 2;
-                                const uint32_t tcol = prob.num_inputs + (prob.mode == EVAL_SSE ? q : q - 2);
-                                if (is_target) m.fetch_row(rowp, tile_ld, tcol, t);
-                                float s[RC];
-#pragma unroll
-                                for (int c = 0; c < RC; ++c) s[c] = 0.0f;
-#pragma unroll
-                                for (int r = 0; r < RR; ++r) {
-                                    const bool ok = full || row0 + (r / 4) * 128 + (r % 4) < chunk_rows;
-#pragma unroll
-                                    for (int c = 0; c < RC; ++c) {
-                                        const float p = m.acc[r][c];
-                                        float term;
-                                        if (prob.mode == EVAL_SSE) { const float e = __fsub_rn(p, t[r]); term = __fmul_rn(e, e); }
-                                        else if (q == 0) term = p;
-                                        else if (q == 1) term = __fmul_rn(p, p);
-                                        else term = __fmul_rn(p, t[r]);
-                                        s[c] = __fadd_rn(s[c], ok ? term : 0.0f);
-                                    }
-                                }
+                            for (int r = 0; r < RR; ++r)
 #pragma unroll
                                 for (int c = 0; c < RC; ++c) {
-                                    const float total = warp_sum(s[c]);
-                                    if (lane == 0) tacc[q * RC + c] += total;
+                                    const float e = __fsub_rn(m.acc[r][c], t[r]);
+                                    part[c] = __fmaf_rn(e, e, part[c]);
                                 }
+                        } else {
+#pragma unroll
+                            for (int r = 0; r < RR; ++r) {
+                                const bool ok = row0 + (r / 4) * 128 + (r % 4) < chunk_rows;
+#pragma unroll
+                                for (int c = 0; c < RC; ++c) {
+                                    const float e = ok ? __fsub_rn(m.acc[r][c], t[r]) : 0.0f;
+                                    part[c] = __fmaf_rn(e, e, part[c]);
+                                }
+                            }
+                        }
+                    } else {
+                        /* several targets, or affine statistics: per-pass warp reduction into
+                         * the warp's shared accumulators tacc[quantity][bank] */
+                        const uint32_t nq = prob.mode == EVAL_AFFINE_STATS ? T + 2 : T;
+                        for (uint32_t q = 0; q < nq; ++q) {
+                            float t[RR];
+                            const bool is_target = prob.mode == EVAL_SSE || q >= 2;
+                            const uint32_t tcol = prob.num_inputs + (prob.mode == EVAL_SSE ? q : q - 2);
+                            if (is_target) m.fetch_row(rowp, tile_ld, tcol, t);
+                            float s[RC];
+#pragma unroll
+                            for (int c = 0; c < RC; ++c) s[c] = 0.0f;
+#pragma unroll
+                            for (int r = 0; r < RR; ++r) {
+                                const bool ok = full || row0 + (r / 4) * 128 + (r % 4) < chunk_rows;
+#pragma unroll
+                                for (int c = 0; c < RC; ++c) {
+                                    const float p = m.acc[r][c];
+                                    float term;
+                                    if (prob.mode == EVAL_SSE) { const float e = __fsub_rn(p, t[r]); term = __fmul_rn(e, e); }
+                                    else if (q == 0) term = p;
+                                    else if (q == 1) term = __fmul_rn(p, p);
+                                    else term = __fmul_rn(p, t[r]);
+                                    s[c] = __fadd_rn(s[c], ok ? term : 0.0f);
+                                }
+                            }
+#pragma unroll
+                            for (int c = 0; c < RC; ++c) {
+                                const float total = warp_sum(s[c]);
+                                if (lane == 0) tacc[q * RC + c] += total;
                             }
                         }
                     }
+                }
 
-                    if (prob.mode == EVAL_SSE && T == 1) {
-                        float mine = 0.0f;
+                if (prob.mode == EVAL_SSE && T == 1) {
+                    float mine = 0.0f;
 #pragma unroll
-                        for (int c = 0; c < RC; ++c) {
-                            const float total = warp_sum(part[c]);
-                            if (lane == c) mine = total;
-                        }
-                        const uint32_t bank = bg * RC + lane;
-                        if (lane < RC && bank < prob.num_banks) {
-                            float* dst = prob.output + gp * prob.out_program_stride + ((size_t)bank << prob.toggle_bits) + perm;
-                            if (geom.use_atomics) atomicAdd(dst, mine);
-                            else *dst += mine;
-                        }
-                    } else if (prob.mode != EVAL_MATERIALIZE) {
-                        __syncwarp();
-                        const uint32_t nq = prob.mode == EVAL_AFFINE_STATS ? T + 2 : T;
-                        for (uint32_t e = lane; e < nq * RC; e += 32) {
-                            const uint32_t q = e / RC, c = e % RC, bank = bg * RC + c;
-                            if (bank < prob.num_banks) {
-                                float* dst = prob.output + gp * prob.out_program_stride + (size_t)q * prob.out_target_stride +
-                                             ((size_t)bank << prob.toggle_bits) + perm;
-                                if (geom.use_atomics) atomicAdd(dst, tacc[e]);
-                                else *dst += tacc[e];
-                            }
+                    for (int c = 0; c < RC; ++c) {
+                        const float total = warp_sum(part[c]);
+                        if (lane == c) mine = total;
+                    }
+                    const uint32_t bank = bg * RC + lane;
+                    if (lane < RC && bank < prob.num_banks) {
+                        float* dst = prob.output + gp * prob.out_program_stride + ((size_t)bank << prob.toggle_bits) + perm;
+                        if (geom.use_atomics) atomicAdd(dst, mine);
+                        else *dst += mine;
+                    }
+                } else if (!materialize) {
+                    __syncwarp();
+                    const uint32_t nq = prob.mode == EVAL_AFFINE_STATS ? T + 2 : T;
+                    for (uint32_t e = lane; e < nq * RC; e += 32) {
+                        const uint32_t q = e / RC, c = e % RC, bank = bg * RC + c;
+                        if (bank < prob.num_banks) {
+                            float* dst = prob.output + gp * prob.out_program_stride + (size_t)q * prob.out_target_stride +
+                                         ((size_t)bank << prob.toggle_bits) + perm;
+                            if (geom.use_atomics) atomicAdd(dst, tacc[e]);
+                            else *dst += tacc[e];
                         }
                     }
                 }
@@ -440,8 +528,10 @@ cudaError_t launch_variant(const DeviceBatch& batch, const EvalProblem& prob, co
     return cudaGetLastError();
 }
 
-constexpr int kVariantRows[3] = {4, 8, 16};
-constexpr int kVariantBanks[3] = {4, 2, 1};
+/* register-tile variants: rows x banks per thread */
+constexpr int kNumVariants = 6;
+constexpr int kVariantRows[kNumVariants] = {4, 8, 16, 8, 16, 32};
+constexpr int kVariantBanks[kNumVariants] = {4, 2, 1, 4, 2, 1};
 
 uint32_t round16(size_t v) { return (uint32_t)((v + 15) / 16 * 16); }
 
@@ -452,13 +542,15 @@ Geom make_geom(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPl
     g.tile_rows = plan.tile_rows;
     g.programs_per_cta = plan.programs_per_cta;
     g.row_splits = plan.row_splits;
-    g.exec_bytes = round16((size_t)batch.max_insn * sizeof(SbInsn));
+    g.exec_bytes = round16(((size_t)batch.max_insn + 1) * sizeof(SbInsn));
     g.cst_bytes = round16(((size_t)prob.num_constants + batch.max_extra) * rc * 4 + 16);
     g.tacc_bytes = round16(((size_t)prob.num_targets + 2) * rc * 4);
-    g.warp_bytes = g.exec_bytes + g.cst_bytes + g.tacc_bytes + (uint32_t)batch.max_slots * rr * rc * 128u;
+    g.scratch_slot = batch.max_slots; /* one slot beyond what the programs use */
+    g.warp_bytes = g.exec_bytes + g.cst_bytes + g.tacc_bytes + ((uint32_t)batch.max_slots + 1u) * rr * rc * 128u;
     g.tile_bytes = round16((size_t)ncols * plan.tile_rows * 4);
     g.rows_per_split = plan.rows_per_split;
     g.use_atomics = plan.row_splits > 1 ? 1u : 0u;
+    g.groups_per_item = plan.groups_per_item ? plan.groups_per_item : 1u;
     return g;
 }
 
@@ -467,9 +559,10 @@ Geom make_geom(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPl
 LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm_count, size_t smem_limit, int forced_variant) {
     LaunchPlan plan;
     plan.ok = false;
+    plan.groups_per_item = 1;
     int variant = prob.num_banks >= 4 ? 0 : prob.num_banks >= 2 ? 1 : 2;
+    if (forced_variant >= 0 && forced_variant < kNumVariants) variant = forced_variant;
     if (prob.mode == EVAL_MATERIALIZE) variant = 2;
-    if (forced_variant >= 0 && forced_variant < 3 && prob.mode != EVAL_MATERIALIZE) variant = forced_variant;
     plan.variant = variant;
     const int rr = kVariantRows[variant], rc = kVariantBanks[variant];
     const uint32_t pass = 32u * rr;
@@ -483,7 +576,7 @@ LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm
     if (tile_rows < pass) tile_rows = pass;
     if (tile_rows > rows_padded) tile_rows = rows_padded;
 
-    for (uint32_t warps = 16; warps >= 1; warps /= 2) {
+    for (uint32_t warps = rr * rc > 16 ? 12 : 16; warps >= 1; warps = warps == 12 ? 8 : warps / 2) {
         LaunchPlan trial = plan;
         trial.warps = warps;
         trial.tile_rows = (uint32_t)tile_rows;
@@ -515,6 +608,22 @@ LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm
     if (ppc > P) ppc = P;
     const uint32_t groups = (P + ppc - 1) / ppc;
     plan.programs_per_cta = ppc;
+    /* Queue items: a program's configuration groups are dealt out in pieces so that the
+     * warps of a CTA finish a chunk together; each piece still amortises the program copy
+     * over a few thousand row evaluations. */
+    if (prob.mode != EVAL_MATERIALIZE) {
+        const unsigned long long bank_groups = (prob.num_banks + rc - 1) / rc;
+        const unsigned long long cfg_groups = bank_groups << prob.toggle_bits;
+        const unsigned long long passes = (plan.tile_rows + pass - 1) / pass;
+        unsigned long long gpi = (32 + passes - 1) / passes; /* at least ~32 program executions per item */
+        const unsigned long long want_items = (unsigned long long)plan.warps * 8;
+        const unsigned long long have = cfg_groups * ppc;
+        if (have / want_items > gpi) gpi = have / want_items;    /* no finer than eight items per warp */
+        if (gpi < 1) gpi = 1;
+        if (gpi > cfg_groups) gpi = cfg_groups;
+        while ((cfg_groups + gpi - 1) / gpi * ppc > 0xfffffff0ull) gpi *= 2; /* item ids are 32-bit */
+        plan.groups_per_item = (uint32_t)(gpi > 0xffffffffull ? 0xffffffffull : gpi);
+    }
     /* Too few program groups to occupy the GPU: split the rows across CTAs as well. */
     uint32_t splits = 1;
     const size_t chunks = (prob.num_rows + plan.tile_rows - 1) / plan.tile_rows;
@@ -530,14 +639,17 @@ LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm
     return plan;
 }
 
+#define SB_FOR_VARIANTS(X) X(4, 4) X(8, 2) X(16, 1) X(8, 4) X(16, 2) X(32, 1)
+
 cudaError_t configure_kernels() {
     cudaError_t e;
     int dev = 0, limit = 0;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
     if ((e = cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(eval_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(eval_kernel<8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(eval_kernel<16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
+#define SB_CONFIGURE(RR, RC) \
+    if ((e = cudaFuncSetAttribute(eval_kernel<RR, RC>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
+    SB_FOR_VARIANTS(SB_CONFIGURE)
+#undef SB_CONFIGURE
     return cudaSuccess;
 }
 
@@ -546,7 +658,10 @@ cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem& prob, const
     switch (plan.variant) {
     case 0: return launch_variant<4, 4>(batch, prob, geom, plan, stream);
     case 1: return launch_variant<8, 2>(batch, prob, geom, plan, stream);
-    default: return launch_variant<16, 1>(batch, prob, geom, plan, stream);
+    case 2: return launch_variant<16, 1>(batch, prob, geom, plan, stream);
+    case 3: return launch_variant<8, 4>(batch, prob, geom, plan, stream);
+    case 4: return launch_variant<16, 2>(batch, prob, geom, plan, stream);
+    default: return launch_variant<32, 1>(batch, prob, geom, plan, stream);
     }
 }
 

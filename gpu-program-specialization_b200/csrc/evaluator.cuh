@@ -55,10 +55,11 @@ struct EvalProblem {
 
 /* Launch geometry chosen by plan_launch(). */
 struct LaunchPlan {
-    int variant;              /* 0: 4 rows x 4 banks, 1: 8 x 2, 2: 16 x 1 per thread */
+    int variant;              /* rows x banks per thread: 0: 4x4, 1: 8x2, 2: 16x1, 3: 8x4, 4: 16x2, 5: 32x1 */
     uint32_t warps;           /* per CTA */
     uint32_t tile_rows;       /* rows staged per chunk, multiple of the pass size */
     uint32_t programs_per_cta;
+    uint32_t groups_per_item; /* configuration groups handed to a warp at a time */
     uint32_t row_splits;      /* CTAs sharing one program group, each with a row range */
     size_t rows_per_split;
     size_t smem_bytes;
