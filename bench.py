@@ -1,0 +1,362 @@
+#!/usr/bin/env python
+"""Benchmark of the population-scoring hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE.json configs[1], "Secant-SR population scoring"): P = 65,536 seeded
+random postfix programs of at most 32 tokens over {+, -, *, protected /, sin, cos, exp,
+protected log}, 16 coefficient slots, 64 coefficient sets per program (per-program bank
+tables), N = 1,048,576 rows of F = 8 float32 features ~U[-3, 3], target = a hidden seeded
+depth-6 expression plus N(0, 0.05) noise, fused squared-error score per (program, set).
+One step scores the whole population once.  With N GPUs every rank scores its own
+65,536-program shard of an N x 65,536 population against the replicated dataset (weak
+scaling); per-program best scores are combined with one all-gather and every rank takes the
+same top-1024.
+
+The line printed by rank 0:
+  value       scored program-rows per second (programs x rows / time; each program-row
+              covers all 64 coefficient sets), programs resident on the device, timed with
+              the library's CUDA events on its launch streams, max over ranks
+  e2e         the same metric through the reference-facing call secant_cubin_runner_run with
+              host programs, including host->device copies of data, banks and programs and
+              the device->host copy of all scores, every step
+  roofline    FP32-pipe roofline of the evaluator kernel: algorithmic
+              lane-operations per second over the probed FFMA rate of this device
+  cpu_baseline the CPU evaluator timed on this box's cores on a bounded sample
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(ROOT, "gpu-program-specialization_b200"), os.path.join(ROOT, "tests")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+from secant_b200 import abi, programs as P  # noqa: E402
+
+WORKLOAD = dict(name="configs[1] Secant-SR population scoring", programs=65536, max_tokens=32, slots=16, banks=64,
+                rows=1 << 20, features=8, seed=2)
+METRIC = "scored program-rows/sec"
+
+
+def hidden_target(x, seed, depth=6):
+    """Seeded random expression of the given depth over the feature columns, in float32."""
+    words = iter(P._stream(seed, 777, 4096).tolist())
+
+    def nxt(n):
+        return int(next(words) % n)
+
+    def build(d):
+        if d == 0 or (d < depth - 2 and nxt(5) == 0):
+            return x[nxt(x.shape[0])] if nxt(4) else np.float32((nxt(2001) - 1000) / 500.0)
+        k = nxt(7)
+        a = build(d - 1)
+        if k == 4:
+            return np.sin(a)
+        if k == 5:
+            return np.cos(a)
+        if k == 6:
+            return np.tanh(a)
+        b = build(d - 1)
+        return (a + b, a - b, a * b, a * b / (b * b + np.float32(0.01)))[k]
+    with np.errstate(all="ignore"):
+        y = np.asarray(build(depth), dtype=np.float32) * np.ones(x.shape[1], dtype=np.float32)
+    return np.nan_to_num(y, nan=0.0, posinf=0.0, neginf=0.0).astype(np.float32)
+
+
+def make_workload(w, rank):
+    """Programs and banks of this rank's shard, and the (replicated) dataset."""
+    pop = P.random_population(w["seed"], w["programs"], w["max_tokens"], w["features"], w["slots"], 3.0,
+                              first_index=rank * w["programs"])
+    x = np.stack([P.uniform(w["seed"] + 100, c, w["rows"], -3.0, 3.0) for c in range(w["features"])])
+    y = (hidden_target(x, w["seed"]) + P.normal(w["seed"] + 200, 0, w["rows"], 0.05))[None, :].astype(np.float32)
+    rng = np.random.Generator(np.random.Philox(key=w["seed"] * 1000 + rank))
+    banks = rng.standard_normal((w["programs"], w["banks"], w["slots"]), dtype=np.float32)
+    return pop, x, y, banks
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        busy = [v for v in sm if v > 0.5 * max(sm)]
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": float(self.rows[0][1]), "reasons": reasons,
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ CPU evaluator legs ----
+
+def cpu_evaluator():
+    """(callable, kind): the reference's own host evaluator when its library was built on
+    a machine with the reference checkout (oracle/_ref), else this repository's CPU port."""
+    import support as S
+    ref = S.reference_lib()
+    if ref is not None:
+        def run(pop, x, y, banks_shared):
+            code, _ = S.reference_toggle_sse(ref, pop, x, y, banks_shared, banks_shared.shape[1], 0)
+            assert code == 0
+        return run, "reference"
+
+    def run(pop, x, y, banks_shared):
+        code, _, _ = S.oracle_toggle_sse(pop, x, y, banks_shared, banks_shared.shape[1], 0)
+        assert code == 0
+    return run, "port"
+
+
+def cpu_throughput(w, programs_per_thread, rows, threads, repeats=1):
+    """Scored program-rows/s of the CPU evaluator on `threads` host threads, each scoring its
+    own slice of a seeded sample of the workload (all 64 coefficient sets, `rows` rows)."""
+    run, kind = cpu_evaluator()
+    total = programs_per_thread * threads
+    pop = P.random_population(w["seed"], total, w["max_tokens"], w["features"], w["slots"], 3.0)
+    x = np.stack([P.uniform(w["seed"] + 100, c, rows, -3.0, 3.0) for c in range(w["features"])])
+    y = (hidden_target(x, w["seed"]) + P.normal(w["seed"] + 200, 0, rows, 0.05))[None, :].astype(np.float32)
+    banks = np.random.Generator(np.random.Philox(key=w["seed"])).standard_normal((w["banks"], w["slots"]), dtype=np.float32)
+    parts = [pop.subset(range(t * programs_per_thread, (t + 1) * programs_per_thread)) for t in range(threads)]
+    best = None
+    for _ in range(repeats):
+        workers = [threading.Thread(target=run, args=(parts[t], x, y, banks)) for t in range(threads)]
+        t0 = time.perf_counter()
+        for th in workers:
+            th.start()
+        for th in workers:
+            th.join()
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return total * rows / best, kind, best, f"{total} programs x {w['banks']} sets x {rows} rows"
+
+
+def reference_arm(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rows, per_thread = 4096, 8
+    # size one step to a few seconds from a quick calibration
+    rate, kind, dt, _ = cpu_throughput(w, 1, 1024, threads)
+    per_thread = max(1, int(rate * 4.0 / (rows * threads)))
+    samples = []
+    for _ in range(args.warmup):
+        cpu_throughput(w, per_thread, rows, threads)
+    t_all = time.perf_counter()
+    for _ in range(args.steps):
+        rate, kind, dt, sample = cpu_throughput(w, per_thread, rows, threads)
+        samples.append(dt)
+    ms = 1e3 * (time.perf_counter() - t_all) / args.steps
+    value = per_thread * threads * rows / (sum(samples) / len(samples))
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "program-rows/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w["name"], "programs": w["programs"], "rows": w["rows"], "features": w["features"],
+                       "coefficient_sets": w["banks"], "max_tokens": w["max_tokens"]},
+            "cpu_baseline": {"value": value, "unit": "program-rows/s", "cores": threads, "kind": kind,
+                             "sample": f"each step: {sample}, {threads} host threads"},
+            "e2e": {"value": value, "unit": "program-rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------- GPU arm ----
+
+def gpu_arm(args, w):
+    import torch
+    import torch.distributed as dist
+    from secant_b200 import sharding
+    from secant_b200.runner import Runner
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the evaluator has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    lib = abi.load()
+    Pn, NB, K, F, N = w["programs"], w["banks"], w["slots"], w["features"], w["rows"]
+    pop, x_h, y_h, banks_h = make_workload(w, rank)
+    ops = P.count_ops(pop)
+    lane_ops_per_step = float((ops + 2).sum()) * NB * N          # W = n_ops + 2 per (program, set, row)
+    pin = lambda a: torch.from_numpy(a).pin_memory()
+    x_pin, y_pin, banks_pin = pin(x_h), pin(y_h), pin(banks_h)
+    scores_pin = torch.empty((Pn, 1, NB), dtype=torch.float32).pin_memory()
+    x_d, y_d, banks_d = x_pin.to(dev), y_pin.to(dev), banks_pin.to(dev)
+    out = torch.empty((Pn, 1, NB), dtype=torch.float32, device=dev)
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)   # larger than the 126 MB L2
+
+    def combine(scores):
+        """Per-program best set, one all-gather, the same top-1024 on every rank."""
+        valid = torch.isfinite(scores) & (scores >= 0)
+        best = torch.where(valid, scores, torch.full_like(scores, float("inf"))).amin(dim=(1, 2))
+        best = torch.where(torch.isinf(best), torch.full_like(best, float("nan")), best)
+        allbest = sharding.all_gather_scores(best, Pn * world, world) if world > 1 else best
+        return sharding.topk_indices(allbest, 1024)
+
+    runner = Runner(abi.SHAPE_TOGGLE_SSE, F, 1, K, workers=min(8, max(2, (os.cpu_count() or 2) // max(1, world))), streams=2)
+    req = runner.toggle_request(pop, x_d, y_d, banks_d, NB, 0, out, bank_stride=K, program_bank_stride=NB * K)
+    launches0 = lib.secant_b200_kernel_launch_count()
+
+    # ---- value: programs, banks and data resident; kernel time from the library's events ----
+    resident = runner.population(pop, 0)
+    kernel_s = []
+    for _ in range(args.warmup):
+        flush.fill_(1)
+        resident.run(req)
+        combine(out)
+    barrier()
+    with ClockSampler(local) as clocks:
+        t0 = time.perf_counter()
+        launches_before = lib.secant_b200_kernel_launch_count()
+        for _ in range(args.steps):
+            flush.fill_(1)
+            resident.run(req)
+            kernel_s.append(runner.stats.runtime_seconds)
+            top = combine(out)
+        barrier()
+        wall = time.perf_counter() - t0
+        launches = lib.secant_b200_kernel_launch_count() - launches_before
+    clock_summary = clocks.summary()
+    resident.destroy()
+    step_s = torch.tensor([wall / args.steps, sum(kernel_s) / len(kernel_s)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(step_s, op=dist.ReduceOp.MAX)
+    step_wall, step_kernel = step_s.tolist()
+
+    # ---- e2e: host programs and host buffers through the reference-facing call ----
+    def e2e_step():
+        x_d.copy_(x_pin, non_blocking=True)
+        y_d.copy_(y_pin, non_blocking=True)
+        banks_d.copy_(banks_pin, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        runner.run(req)                       # encodes and uploads the programs, evaluates, blocks
+        combine(out)
+        scores_pin.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    e2e_t = torch.tensor([(time.perf_counter() - t0) / args.steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_s = float(e2e_t.item())
+    encode_s, upload_s = runner.stats.compile_work_seconds, runner.stats.module_load_seconds
+    h2d = x_h.nbytes + y_h.nbytes + banks_h.nbytes + len(pop.ast_blob)
+    d2h = scores_pin.numel() * 4
+
+    # ---- roofline denominator and CPU baseline (rank 0 only) ----
+    line = None
+    if rank == 0:
+        peak = C.c_double()
+        abi.check(lib.secant_b200_fp32_peak_probe(0.5, C.byref(peak)), "fp32 peak probe")
+        achieved = lane_ops_per_step / step_kernel
+        cpu = None
+        if world == 1 or True:
+            threads = os.cpu_count() or 1
+            rate, kind, dt, sample = cpu_throughput(w, 1, 1024, threads)
+            per_thread = max(1, int(rate * 12.0 / (4096 * threads)))
+            rate, kind, dt, sample = cpu_throughput(w, per_thread, 4096, threads)
+            cpu = {"value": rate, "unit": "program-rows/s", "cores": threads, "kind": kind,
+                   "sample": f"{sample}, {dt:.1f} s on {threads} host threads"}
+        total_program_rows = float(Pn) * N * world
+        line = {
+            "metric": METRIC, "value": total_program_rows / step_wall, "unit": "program-rows/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_wall * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w["name"], "programs_per_gpu": Pn, "rows": N, "features": F, "coefficient_slots": K,
+                       "coefficient_sets": NB, "banks": "per-program", "max_tokens": w["max_tokens"],
+                       "row_evals_per_step_per_gpu": float(Pn) * NB * N, "mean_ops_per_program": float(ops.mean()),
+                       "l2": "192 MiB flush between steps", "combine": "best set per program, all-gather, top-1024",
+                       "kernel_ms_per_step": step_kernel * 1e3},
+            "row_evals_per_s": float(Pn) * NB * N * world / step_wall,
+            "node_evals_per_s": lane_ops_per_step * world / step_wall,
+            "e2e": {"value": total_program_rows / e2e_s, "unit": "program-rows/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3, "encode_ms": encode_s * 1e3,
+                    "program_upload_ms": upload_s * 1e3},
+            "gpu_launches": int(launches),
+            "clocks": clock_summary,
+            "roofline": {"bound": "fp32", "achieved": achieved / 1e12, "peak": peak.value / 1e12, "unit": "TFLOP/s",
+                         "frac": achieved / peak.value, "traffic": None,
+                         "note": "achieved = sum over programs of (ops + 2) x sets x rows / kernel time, one per "
+                                 "algorithmic operation; peak = FFMA lane-instructions/s probed on this device in this run"},
+            "cpu_baseline": cpu,
+            "top1024_head": [int(i) for i in top[:4].tolist()],
+        }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    runner.destroy()
+    if line is not None:
+        print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--programs", type=int, default=None, help="development only: shrink the population")
+    ap.add_argument("--rows", type=int, default=None, help="development only: shrink the dataset")
+    args = ap.parse_args()
+    w = dict(WORKLOAD)
+    if args.programs:
+        w["programs"] = args.programs
+        w["name"] += f" (reduced: {args.programs} programs)"
+    if args.rows:
+        w["rows"] = args.rows
+        w["name"] += f" (reduced: {args.rows} rows)"
+    args.warmup = max(args.warmup, 0)
+    if args.impl == "reference":
+        reference_arm(args, w)
+    else:
+        gpu_arm(args, w)
+
+
+if __name__ == "__main__":
+    main()

@@ -76,6 +76,11 @@ SECANT_DEC SecantResult secant_b200_population_destroy(SecantB200Population popu
  * 1 = 8 x 2, 2 = 16 x 1, -1 = automatic.  Every variant computes the same values. */
 SECANT_DEC void secant_b200_runner_force_variant(SecantCubinRunner runner, int variant);
 
+/* Sustained FP32 rate of the current device in lane-instructions per second (one FFMA on
+ * one lane = 1), measured with independent FFMA chains for about seconds_budget seconds.
+ * This is the denominator of the evaluator's FP32 roofline.  Allocates a small buffer. */
+SECANT_DEC SecantResult secant_b200_fp32_peak_probe(double seconds_budget, double* lane_instructions_per_second);
+
 /* Human-readable description of the last CUDA error seen by a runner (empty when none). */
 SECANT_DEC const char* secant_b200_runner_last_error(SecantCubinRunner runner);
 
