@@ -197,7 +197,7 @@ def reference_arm(args, w):
 def gpu_arm(args, w):
     import torch
     import torch.distributed as dist
-    from secant_b200 import sharding
+    from secant_b200 import runner as R
     from secant_b200.runner import Runner
 
     rank = int(os.environ.get("RANK", "0"))
@@ -227,13 +227,16 @@ def gpu_arm(args, w):
     out = torch.empty((Pn, 1, NB), dtype=torch.float32, device=dev)
     flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)   # larger than the 126 MB L2
 
+    records = torch.empty(Pn * R.SCORE_BYTES, dtype=torch.uint8, device=dev)          # all-gather send buffer
+    gathered = torch.empty(world * Pn * R.SCORE_BYTES, dtype=torch.uint8, device=dev) if world > 1 else records
+
     def combine(scores):
-        """Per-program best set, one all-gather, the same top-1024 on every rank."""
-        valid = torch.isfinite(scores) & (scores >= 0)
-        best = torch.where(valid, scores, torch.full_like(scores, float("inf"))).amin(dim=(1, 2))
-        best = torch.where(torch.isinf(best), torch.full_like(best, float("nan")), best)
-        allbest = sharding.all_gather_scores(best, Pn * world, world) if world > 1 else best
-        return sharding.topk_indices(allbest, 1024)
+        """Best set per program (device kernel writing straight into the all-gather send
+        buffer), one all-gather of the 24-byte records, the same top-1024 on every rank."""
+        R.best_config(scores.view(Pn, NB), out=records)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, records)
+        return R.topk(R.score_fields(gathered)[0], 1024)[0]
 
     runner = Runner(abi.SHAPE_TOGGLE_SSE, F, 1, K, workers=min(8, max(2, (os.cpu_count() or 2) // max(1, world))), streams=2)
     req = runner.toggle_request(pop, x_d, y_d, banks_d, NB, 0, out, bank_stride=K, program_bank_stride=NB * K)
@@ -311,7 +314,7 @@ def gpu_arm(args, w):
             "config": {"workload": w["name"], "programs_per_gpu": Pn, "rows": N, "features": F, "coefficient_slots": K,
                        "coefficient_sets": NB, "banks": "per-program", "max_tokens": w["max_tokens"],
                        "row_evals_per_step_per_gpu": float(Pn) * NB * N, "mean_ops_per_program": float(ops.mean()),
-                       "l2": "192 MiB flush between steps", "combine": "best set per program, all-gather, top-1024",
+                       "l2": "192 MiB flush between steps", "combine": "best-set kernel, all-gather of 24-byte records, top-1024 kernel",
                        "kernel_ms_per_step": step_kernel * 1e3},
             "row_evals_per_s": float(Pn) * NB * N * world / step_wall,
             "node_evals_per_s": lane_ops_per_step * world / step_wall,

@@ -1,0 +1,185 @@
+/*
+ * reduce.cu - what happens to the score grid after evaluation, on the device:
+ * the best configuration of every program and the global top-k of per-program scores.
+ *
+ * Rules restated from the reference:
+ *   - a score is valid when it is finite and >= 0; the best configuration of a program is
+ *     its smallest valid score, the lowest configuration index on ties; no valid score
+ *     gives {+inf, UINT64_MAX, 0}   (projects/secant-sr/toggle/src/cpu.c:45-67, the NVRTC
+ *     `best` kernel of projects/secant-sr/toggle/src/cuda.c:62-88, SRScore layout
+ *     projects/secant-sr/secant_sr.h:68-76);
+ *   - ranking across programs orders by (score, index) ascending and an invalid score never
+ *     beats a valid one (projects/odezza/core/o_score_reduce.cu:36-39).  The reference's
+ *     ranking stops at k = 256 and is built on CUB; this one is a tiled bitonic selection
+ *     written for any k up to 2048.
+ */
+#include "../../include/secant_b200.h"
+
+#include <cuda_runtime.h>
+#include <math_constants.h>
+
+namespace {
+
+constexpr int kBestThreads = 128;
+
+struct Candidate {
+    float score;
+    unsigned long long index;
+    unsigned long long valid;
+};
+
+__device__ __forceinline__ bool wins(float s, unsigned long long i, float t, unsigned long long j) {
+    return s < t || (s == t && i < j);
+}
+
+/* one CTA per score vector */
+__global__ void __launch_bounds__(kBestThreads)
+best_config_kernel(const float* __restrict__ grid, unsigned long long configs, unsigned long long ld, SecantB200Score* out) {
+    const float* row = grid + (size_t)blockIdx.x * ld;
+    Candidate c{CUDART_INF_F, ~0ull, 0ull};
+    for (unsigned long long i = threadIdx.x; i < configs; i += kBestThreads) {
+        const float v = row[i];
+        if (v >= 0.0f && v < CUDART_INF_F) { /* finite and non-negative; NaN fails both */
+            ++c.valid;
+            if (wins(v, i, c.score, c.index)) { c.score = v; c.index = i; }
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float s = __shfl_down_sync(0xffffffffu, c.score, o);
+        const unsigned long long i = __shfl_down_sync(0xffffffffu, c.index, o);
+        c.valid += __shfl_down_sync(0xffffffffu, c.valid, o);
+        if (wins(s, i, c.score, c.index)) { c.score = s; c.index = i; }
+    }
+    __shared__ Candidate partial[kBestThreads / 32];
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kBestThreads / 32; ++w) {
+            c.valid += partial[w].valid;
+            if (wins(partial[w].score, partial[w].index, c.score, c.index)) { c.score = partial[w].score; c.index = partial[w].index; }
+        }
+        SecantB200Score r;
+        r.sse = c.score; r.reserved = 0; r.configuration = c.index; r.valid_configurations = c.valid;
+        out[blockIdx.x] = r;
+    }
+}
+
+/* ---- top-k --------------------------------------------------------------------------
+ * Every score becomes a 64-bit key: high word = the float's bit pattern (monotonic for
+ * non-negative floats; invalid scores map to 0xffffffff), low word = the index.  Smaller
+ * key = better rank, and keys are unique.  A CTA sorts a tile of 4096 keys in shared memory
+ * (bitonic network) and keeps the k smallest; rounds shrink the candidate list by
+ * 4096 / k until one tile is left. */
+constexpr int kTile = 4096;
+constexpr int kSortThreads = 512;
+
+__device__ __forceinline__ unsigned long long score_key(float v, unsigned long long index) {
+    unsigned int hi = 0xffffffffu;
+    if (v >= 0.0f && v < CUDART_INF_F) hi = v == 0.0f ? 0u : __float_as_uint(v);
+    return ((unsigned long long)hi << 32) | (index & 0xffffffffull);
+}
+
+__device__ void sort_tile(unsigned long long* keys) {
+    for (int size = 2; size <= kTile; size <<= 1)
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (int t = threadIdx.x; t < kTile / 2; t += kSortThreads) {
+                const int lo = 2 * t - (t & (stride - 1));
+                const int hi = lo + stride;
+                const bool ascending = (lo & size) == 0;
+                const unsigned long long a = keys[lo], b = keys[hi];
+                if ((a > b) == ascending) { keys[lo] = b; keys[hi] = a; }
+            }
+        }
+    __syncthreads();
+}
+
+/* first round: tiles of raw scores -> k best keys per tile */
+__global__ void __launch_bounds__(kSortThreads)
+topk_first_kernel(const float* __restrict__ scores, unsigned long long count, unsigned int k, unsigned long long* out) {
+    __shared__ unsigned long long keys[kTile];
+    const unsigned long long base = (unsigned long long)blockIdx.x * kTile;
+    for (int t = threadIdx.x; t < kTile; t += kSortThreads) {
+        const unsigned long long i = base + t;
+        keys[t] = i < count ? score_key(scores[i], i) : ~0ull;
+    }
+    sort_tile(keys);
+    for (unsigned int t = threadIdx.x; t < k; t += kSortThreads) out[(size_t)blockIdx.x * k + t] = keys[t];
+}
+
+/* later rounds: tiles of candidate keys -> k best keys per tile */
+__global__ void __launch_bounds__(kSortThreads)
+topk_merge_kernel(const unsigned long long* __restrict__ in, unsigned long long count, unsigned int k, unsigned long long* out) {
+    __shared__ unsigned long long keys[kTile];
+    const unsigned long long base = (unsigned long long)blockIdx.x * kTile;
+    for (int t = threadIdx.x; t < kTile; t += kSortThreads) keys[t] = base + t < count ? in[base + t] : ~0ull;
+    sort_tile(keys);
+    for (unsigned int t = threadIdx.x; t < k; t += kSortThreads) out[(size_t)blockIdx.x * k + t] = keys[t];
+}
+
+__global__ void topk_emit_kernel(const unsigned long long* __restrict__ keys, const float* __restrict__ scores,
+                                 unsigned long long count, unsigned int k, unsigned long long* indices, float* values) {
+    const unsigned int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= k) return;
+    const unsigned long long key = keys[t];
+    const bool present = t < count && key != ~0ull;
+    const unsigned long long index = key & 0xffffffffull;
+    indices[t] = present ? index : ~0ull;
+    if (values) values[t] = present ? scores[index] : CUDART_NAN_F;
+}
+
+size_t tiles_of(unsigned long long count) { return (size_t)((count + kTile - 1) / kTile); }
+
+}  // namespace
+
+/* Runs the selection rounds; `scratch` must hold secant_b200_topk_scratch_elements(count, k)
+ * 64-bit words.  Shared by the allocating and the caller-provided-scratch entry points. */
+static cudaError_t topk_rounds(const float* scores, unsigned long long count, unsigned int k, unsigned long long* scratch,
+                               unsigned long long* indices, float* values, cudaStream_t stream) {
+    size_t tiles = tiles_of(count);
+    unsigned long long* cur = scratch;
+    unsigned long long* nxt = scratch + tiles * k;
+    topk_first_kernel<<<(unsigned)tiles, kSortThreads, 0, stream>>>(scores, count, k, cur);
+    unsigned long long have = (unsigned long long)tiles * k;
+    while (tiles > 1) {
+        tiles = tiles_of(have);
+        topk_merge_kernel<<<(unsigned)tiles, kSortThreads, 0, stream>>>(cur, have, k, nxt);
+        have = (unsigned long long)tiles * k;
+        unsigned long long* t = cur; cur = nxt; nxt = t;
+    }
+    topk_emit_kernel<<<(k + 255) / 256, 256, 0, stream>>>(cur, scores, count, k, indices, values);
+    return cudaGetLastError();
+}
+
+extern "C" {
+
+size_t secant_b200_topk_scratch_elements(size_t count, size_t k) {
+    const size_t first = tiles_of(count) * k;
+    return first + tiles_of(first) * k; /* ping + pong; later rounds only shrink */
+}
+
+SecantResult secant_b200_best_config(uintptr_t scores, size_t num_vectors, size_t num_configurations, size_t leading_dimension,
+                                     uintptr_t best_out, void* stream) {
+    if (!scores || !best_out || !num_vectors || !num_configurations || leading_dimension < num_configurations ||
+        num_vectors > 0x7fffffffull || scores % 4 || best_out % 8)
+        return SECANT_ERROR_INVALID_VALUE;
+    best_config_kernel<<<(unsigned)num_vectors, kBestThreads, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const float*>(scores), num_configurations, leading_dimension, reinterpret_cast<SecantB200Score*>(best_out));
+    return cudaGetLastError() == cudaSuccess ? SECANT_SUCCESS : SECANT_ERROR_DRIVER_FAILED;
+}
+
+SecantResult secant_b200_topk(uintptr_t scores, size_t count, size_t k, uintptr_t indices_out, uintptr_t scores_out, void* stream) {
+    if (!scores || !indices_out || !count || !k || k > 2048 || count > 0xffffffffull || scores % 4 || indices_out % 8 || scores_out % 4)
+        return SECANT_ERROR_INVALID_VALUE;
+    unsigned long long* scratch = nullptr;
+    const size_t words = secant_b200_topk_scratch_elements(count, k);
+    if (cudaMallocAsync(&scratch, words * sizeof(unsigned long long), (cudaStream_t)stream) != cudaSuccess) return SECANT_ERROR_ALLOCATION_FAILED;
+    cudaError_t e = topk_rounds(reinterpret_cast<const float*>(scores), count, (unsigned)k, scratch,
+                                reinterpret_cast<unsigned long long*>(indices_out), reinterpret_cast<float*>(scores_out),
+                                (cudaStream_t)stream);
+    const cudaError_t f = cudaFreeAsync(scratch, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = f;
+    return e == cudaSuccess ? SECANT_SUCCESS : SECANT_ERROR_DRIVER_FAILED;
+}
+
+}  // extern "C"

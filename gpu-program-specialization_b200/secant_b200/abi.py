@@ -136,6 +136,10 @@ class RunnerStats(C.Structure):
                 ("module_unload_seconds", C.c_double), ("runtime_seconds", C.c_double), ("total_seconds", C.c_double)]
 
 
+class Score(C.Structure):  # SecantB200Score, layout of the reference consumer's SRScore
+    _fields_ = [("sse", C.c_float), ("reserved", _u32), ("configuration", C.c_uint64), ("valid_configurations", C.c_uint64)]
+
+
 def init_header(struct, version, shape):
     struct.header.struct_size = C.sizeof(struct)
     struct.header.version = version
@@ -184,6 +188,9 @@ EXPORTED = {
     "secant_b200_population_num_ops": (C.c_uint64, [C.c_void_p]),
     "secant_b200_population_destroy": (C.c_int32, [C.c_void_p]),
     "secant_b200_runner_force_variant": (None, [C.c_void_p, C.c_int]),
+    "secant_b200_best_config": (C.c_int32, [C.c_size_t, _sz, _sz, _sz, C.c_size_t, C.c_void_p]),
+    "secant_b200_topk": (C.c_int32, [C.c_size_t, _sz, _sz, C.c_size_t, C.c_size_t, C.c_void_p]),
+    "secant_b200_topk_scratch_elements": (_sz, [_sz, _sz]),
     "secant_b200_fp32_peak_probe": (C.c_int32, [C.c_double, C.POINTER(C.c_double)]),
     "secant_b200_runner_last_error": (C.c_char_p, [C.c_void_p]),
     "secant_b200_kernel_launch_count": (C.c_uint64, []),

@@ -200,3 +200,43 @@ class Population:
         if self.handle:
             abi.check(self.runner.lib.secant_b200_population_destroy(self.handle), "population_destroy")
             self.handle = C.c_void_p()
+
+
+# ---- device-side reductions over score grids (extension API) -----------------------------
+
+SCORE_BYTES = C.sizeof(abi.Score)
+
+
+def best_config(scores, out=None):
+    """Best configuration of every vector of a [vectors][configurations] float32 CUDA tensor.
+    Returns a uint8 tensor of SecantB200Score records (24 bytes each); score_fields() views it."""
+    lib = abi.load()
+    flat = scores.reshape(-1, scores.shape[-1])
+    assert flat.is_cuda and flat.dtype == torch.float32 and flat.stride(-1) == 1
+    if out is None:
+        out = torch.empty(flat.shape[0] * SCORE_BYTES, dtype=torch.uint8, device=scores.device)
+    stream = torch.cuda.current_stream().cuda_stream
+    abi.check(lib.secant_b200_best_config(flat.data_ptr(), flat.shape[0], flat.shape[1], flat.stride(0), out.data_ptr(),
+                                          C.c_void_p(stream)), "secant_b200_best_config")
+    return out
+
+
+def score_fields(records):
+    """(sse float32 view, configuration int64 view, valid int64 view) of a record buffer."""
+    n = records.numel() // SCORE_BYTES
+    sse = records.view(torch.float32).view(n, 6)[:, 0]
+    words = records.view(torch.int64).view(n, 3)
+    return sse, words[:, 1], words[:, 2]
+
+
+def topk(scores, k):
+    """Indices (int64, UINT64_MAX shows as -1) and values of the k best scores of a 1-D float32
+    CUDA tensor under (valid first, score ascending, index ascending)."""
+    lib = abi.load()
+    scores = scores.contiguous()
+    idx = torch.empty(k, dtype=torch.int64, device=scores.device)
+    val = torch.empty(k, dtype=torch.float32, device=scores.device)
+    stream = torch.cuda.current_stream().cuda_stream
+    abi.check(lib.secant_b200_topk(scores.data_ptr(), scores.numel(), k, idx.data_ptr(), val.data_ptr(), C.c_void_p(stream)),
+              "secant_b200_topk")
+    return idx, val

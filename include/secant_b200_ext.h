@@ -76,6 +76,36 @@ SECANT_DEC SecantResult secant_b200_population_destroy(SecantB200Population popu
  * 1 = 8 x 2, 2 = 16 x 1, -1 = automatic.  Every variant computes the same values. */
 SECANT_DEC void secant_b200_runner_force_variant(SecantCubinRunner runner, int variant);
 
+/*
+ * Best configuration of every score vector, on the device.  `scores` is [vector][configuration]
+ * float32 with `leading_dimension` elements between vectors (for a toggle-SSE grid with one
+ * target: vector = program).  A score is valid when finite and >= 0; the winner is the
+ * smallest valid score, lowest configuration on ties; no valid score gives
+ * {+inf, UINT64_MAX, 0}.  Layout and rule of the reference consumer's SRScore
+ * (projects/secant-sr/secant_sr.h:68-76, projects/secant-sr/toggle/src/cpu.c:45-67).
+ * Asynchronous on `stream` (a cudaStream_t, NULL = default stream).
+ */
+typedef struct SecantB200Score {
+    float sse;
+    uint32_t reserved;
+    uint64_t configuration;
+    uint64_t valid_configurations;
+} SecantB200Score;
+SECANT_DEC SecantResult secant_b200_best_config(uintptr_t scores, size_t num_vectors, size_t num_configurations,
+                                                size_t leading_dimension, uintptr_t best_out, void* stream);
+
+/*
+ * Global top-k of `count` float32 scores (count < 2^32, k <= 2048): writes the indices of the
+ * k best scores to indices_out (uint64[k]) and, when scores_out is non-zero, their values
+ * (float[k]).  Order: valid scores (finite, >= 0) before invalid ones, score ascending,
+ * index ascending (projects/odezza/core/o_score_reduce.cu:36-39).  Slots beyond `count`
+ * receive UINT64_MAX / NaN.  Uses a stream-ordered temporary allocation of
+ * secant_b200_topk_scratch_elements(count, k) 64-bit words.  Asynchronous on `stream`.
+ */
+SECANT_DEC SecantResult secant_b200_topk(uintptr_t scores, size_t count, size_t k, uintptr_t indices_out,
+                                         uintptr_t scores_out, void* stream);
+SECANT_DEC size_t secant_b200_topk_scratch_elements(size_t count, size_t k);
+
 /* Sustained FP32 rate of the current device in lane-instructions per second (one FFMA on
  * one lane = 1), measured with independent FFMA chains for about seconds_budget seconds.
  * This is the denominator of the evaluator's FP32 roofline.  Allocates a small buffer. */
