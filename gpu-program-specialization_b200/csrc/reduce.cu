@@ -130,6 +130,14 @@ __global__ void topk_emit_kernel(const unsigned long long* __restrict__ keys, co
 
 size_t tiles_of(unsigned long long count) { return (size_t)((count + kTile - 1) / kTile); }
 
+/* Fixed scratch of secant_b200_topk_static(): enough for 1,048,576 scores and k = 1024
+ * (256 first-round tiles x 1024 keys, plus 64 x 1024 for the second round), 2.5 MiB.  The
+ * array lives in every device that loads this library, for the life of the process. */
+constexpr size_t kStaticMaxCount = 1u << 20;
+constexpr size_t kStaticMaxK = 1024;
+constexpr size_t kStaticWords = (kStaticMaxCount / kTile) * kStaticMaxK + ((kStaticMaxCount / kTile) * kStaticMaxK / kTile) * kStaticMaxK;
+static __device__ __align__(256) unsigned long long g_topk_static_scratch[kStaticWords];
+
 }  // namespace
 
 /* Runs the selection rounds; `scratch` must hold secant_b200_topk_scratch_elements(count, k)
@@ -166,6 +174,42 @@ SecantResult secant_b200_best_config(uintptr_t scores, size_t num_vectors, size_
     best_config_kernel<<<(unsigned)num_vectors, kBestThreads, 0, (cudaStream_t)stream>>>(
         reinterpret_cast<const float*>(scores), num_configurations, leading_dimension, reinterpret_cast<SecantB200Score*>(best_out));
     return cudaGetLastError() == cudaSuccess ? SECANT_SUCCESS : SECANT_ERROR_DRIVER_FAILED;
+}
+
+/* Device address of the static scratch on the current device.  The symbol name is only a
+ * host-side handle; the address a kernel may use has to be asked for once per device, with
+ * that device current. */
+static cudaError_t static_scratch_address(unsigned long long** address) {
+    constexpr int kMaxDevices = 64;
+    static unsigned long long* table[kMaxDevices] = {nullptr};
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+    unsigned long long* known = __atomic_load_n(&table[device], __ATOMIC_ACQUIRE);
+    if (!known) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_topk_static_scratch);
+        if (e != cudaSuccess) return e;
+        known = static_cast<unsigned long long*>(p);
+        __atomic_store_n(&table[device], known, __ATOMIC_RELEASE); /* every thread resolves the same address */
+    }
+    *address = known;
+    return cudaSuccess;
+}
+
+SecantResult secant_b200_topk_static(uintptr_t scores, size_t count, size_t k, uintptr_t indices_out, uintptr_t scores_out,
+                                     void* stream) {
+    if (!scores || !indices_out || !count || !k || scores % 4 || indices_out % 8 || scores_out % 4) return SECANT_ERROR_INVALID_VALUE;
+    if (count > kStaticMaxCount || k > kStaticMaxK) return SECANT_ERROR_INSUFFICIENT_BUFFER; /* beyond the fixed scratch */
+    if (secant_b200_topk_scratch_elements(count, k) > kStaticWords) return SECANT_ERROR_INSUFFICIENT_BUFFER;
+    unsigned long long* scratch = nullptr;
+    if (static_scratch_address(&scratch) != cudaSuccess) return SECANT_ERROR_DRIVER_FAILED;
+    /* every round writes the keys it later reads, so nothing in the shared array needs clearing */
+    const cudaError_t e = topk_rounds(reinterpret_cast<const float*>(scores), count, (unsigned)k, scratch,
+                                      reinterpret_cast<unsigned long long*>(indices_out), reinterpret_cast<float*>(scores_out),
+                                      (cudaStream_t)stream);
+    return e == cudaSuccess ? SECANT_SUCCESS : SECANT_ERROR_DRIVER_FAILED;
 }
 
 SecantResult secant_b200_topk(uintptr_t scores, size_t count, size_t k, uintptr_t indices_out, uintptr_t scores_out, void* stream) {

@@ -191,6 +191,7 @@ EXPORTED = {
     "secant_b200_best_config": (C.c_int32, [C.c_size_t, _sz, _sz, _sz, C.c_size_t, C.c_void_p]),
     "secant_b200_topk": (C.c_int32, [C.c_size_t, _sz, _sz, C.c_size_t, C.c_size_t, C.c_void_p]),
     "secant_b200_topk_scratch_elements": (_sz, [_sz, _sz]),
+    "secant_b200_topk_static": (C.c_int32, [C.c_size_t, _sz, _sz, C.c_size_t, C.c_size_t, C.c_void_p]),
     "secant_b200_fp32_peak_probe": (C.c_int32, [C.c_double, C.POINTER(C.c_double)]),
     "secant_b200_runner_last_error": (C.c_char_p, [C.c_void_p]),
     "secant_b200_kernel_launch_count": (C.c_uint64, []),

@@ -106,6 +106,29 @@ SECANT_DEC SecantResult secant_b200_topk(uintptr_t scores, size_t count, size_t 
                                          uintptr_t scores_out, void* stream);
 SECANT_DEC size_t secant_b200_topk_scratch_elements(size_t count, size_t k);
 
+/*
+ * secant_b200_topk() for callers that must not allocate.  No counterpart in the reference.
+ *
+ * Some hosts cannot let a library call cudaMalloc: a process that has handed all device
+ * memory to its own pool (a further allocation fails or fragments the pool), or a steady-
+ * state scoring loop that cannot afford the device-wide synchronisation and latency an
+ * allocation or free may cost.  This variant runs the same kernels as secant_b200_topk()
+ * but keeps its intermediate keys in a fixed 2.5 MiB array compiled into the library, so
+ * it calls no cudaMalloc, cudaFree or other allocating routine; inputs and outputs are
+ * still the caller's.
+ *
+ * Limits: count <= 1,048,576 scores and k <= 1,024; anything larger returns
+ * SECANT_ERROR_INSUFFICIENT_BUFFER and nothing is launched (use secant_b200_topk()).
+ * The array exists once per device and is held until the process exits.  All calls on a
+ * device share it: two calls whose kernels overlap on the GPU (different streams, or
+ * different host threads) race on the intermediate keys and return garbage, so serialise
+ * them.  The first call on each device looks up the array's device address (with that
+ * device current); make that first call outside any stream capture.  Results are identical
+ * to secant_b200_topk().  Asynchronous on `stream`.
+ */
+SECANT_DEC SecantResult secant_b200_topk_static(uintptr_t scores, size_t count, size_t k, uintptr_t indices_out,
+                                                uintptr_t scores_out, void* stream);
+
 /* Sustained FP32 rate of the current device in lane-instructions per second (one FFMA on
  * one lane = 1), measured with independent FFMA chains for about seconds_budget seconds.
  * This is the denominator of the evaluator's FP32 roofline.  Allocates a small buffer. */
