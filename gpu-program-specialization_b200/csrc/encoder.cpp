@@ -254,7 +254,7 @@ struct Emitter {
         const Node& n = nodes[id];
         if (n.slot >= 0) return Operand{SB_KIND_SLOT, (unsigned)n.slot, 0};
         switch (n.type) {
-        case N_COL: return Operand{SB_KIND_ROW, n.index, 0};
+        case N_COL: return rules.columns_are_slots ? Operand{SB_KIND_SLOT, n.index, 0} : Operand{SB_KIND_ROW, n.index, 0};
         case N_BANK: return Operand{SB_KIND_CST, n.index, 0};
         case N_AFFINE: return Operand{SB_KIND_CST, (unsigned)rules.num_constants + n.index, 0};
         default: break;
@@ -459,6 +459,8 @@ SecantResult encode_program(const SecantAstInstruction* program, const SecantAst
     rec.lit_off = (uint32_t)out.lits.size();
 
     Emitter em{nodes, rules, out, out.insns.size(), out.lits.size(), (unsigned)affines.size(), {}, 0, SECANT_SUCCESS};
+    em.slot_busy.assign(rules.reserved_slots, 1);
+    em.slots_high = rules.reserved_slots;
     em.prepare(root); /* counts the RETURN as the root's first use */
     for (auto& n : nodes) n.pending = n.uses;
     em.gen(root);

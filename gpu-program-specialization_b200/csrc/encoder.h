@@ -24,6 +24,11 @@ struct ProgramRules {
     size_t num_constants = 0;   /* BANK / AFFINE_BANK slots must be below this */
     bool banks_allowed = false; /* only the toggle shape has banks and toggles */
     unsigned toggle_bits = 0;   /* toggle bit indices must be below this */
+    /* Rollout scoring: COLUMN i is not a dataset column but state i of the trajectory being
+     * integrated, which the kernel keeps in spill slot i; the first `reserved_slots` slots
+     * belong to the integrator and program temporaries start after them. */
+    bool columns_are_slots = false;
+    unsigned reserved_slots = 0;
 };
 
 /* Encoded records of a contiguous group of programs, ready to upload as five arrays. */

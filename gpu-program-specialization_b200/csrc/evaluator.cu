@@ -521,6 +521,162 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
     }
 }
 
+/* ---- RK4 rollout scoring ---------------------------------------------------------------
+ * Restates the integration loop of the reference's generated scoring kernel
+ * (projects/odezza/core/o_generate_scoring_cuda.c:494-588): per observation interval
+ * h = interval / substeps; per substep base = stage = state, sum = 0, four stages with
+ * sum = fma(w, rhs, sum) (w = 1,2,2,1), stage = fma(h/2 or h, rhs, base), then
+ * state = fma(h/6, sum, base); after every interval all states must be finite and
+ * sq = fma(err, err, sq).  Score = sq / residuals, or FLT_MAX when anything was not finite.
+ *
+ * Mapping (different from the reference, which gives a thread one configuration and loops all
+ * trajectories inside it): one warp per (system, configuration), lanes = trajectories, four
+ * per lane.  The integrator's vectors live in the warp's spill slots: slot s = stage state s
+ * (what COLUMN s of a right-hand side reads), then next-stage, base, sum and state vectors. */
+constexpr int kRk4Warps = 8;
+
+__global__ void __launch_bounds__(kRk4Warps * 32)
+rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, uint32_t cst_bytes, uint32_t warp_bytes,
+           uint32_t scratch_slot) {
+    using M = Machine<4, 1>;
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t S = prob.num_states, K = prob.num_constants;
+    unsigned char* const warea = smem + (size_t)warp * warp_bytes;
+    float4* const slots = reinterpret_cast<float4*>(warea + (size_t)S * (exec_bytes + cst_bytes)) + lane;
+    const unsigned long long configs = (unsigned long long)prob.num_banks << prob.toggle_bits;
+    const unsigned long long item = (unsigned long long)blockIdx.x * kRk4Warps + warp;
+    if (item >= configs * prob.num_systems) return;
+    const uint32_t sys = (uint32_t)(item / configs);
+    const unsigned long long cfg = item % configs;
+    const unsigned long long perm = cfg & ((1ull << prob.toggle_bits) - 1ull);
+    const uint32_t bank = (uint32_t)(cfg >> prob.toggle_bits);
+    const float* bank_ptr = prob.banks ? prob.banks + (size_t)sys * prob.system_bank_stride + (size_t)bank * prob.bank_stride : nullptr;
+
+    for (uint32_t s = 0; s < S; ++s) { /* private copy of every right-hand side, toggles resolved, constants staged */
+        const SbProgram pr = batch.programs[sys * S + s];
+        SbInsn* exec = reinterpret_cast<SbInsn*>(warea + (size_t)s * exec_bytes);
+        float* cst = reinterpret_cast<float*>(warea + (size_t)S * exec_bytes + (size_t)s * cst_bytes);
+        for (uint32_t i = lane; i < pr.n_insn; i += 32) exec[i] = batch.insns[pr.insn_off + i];
+        if (lane == 0) exec[pr.n_insn] = SbInsn{0u, 0u};
+        __syncwarp();
+        for (uint32_t i = lane; i < pr.n_patch; i += 32) {
+            const SbPatch* p = batch.patches + pr.patch_off + i;
+            unsigned choice = (unsigned)(perm >> p->bit0) & 1u;
+            if (p->bit1 != 0xffu) choice |= ((unsigned)(perm >> p->bit1) & 1u) << 1;
+            exec[p->insn] = p->alt[choice];
+        }
+        for (uint32_t e = lane; e < K + pr.n_affine + pr.n_lits; e += 32) {
+            float v;
+            if (e < K) v = bank_ptr[e];
+            else if (e < K + pr.n_affine) {
+                const SbAffine a = batch.affines[pr.affine_off + e - K];
+                v = __fadd_rn(__fmul_rn(bank_ptr[a.slot], a.scale), a.offset);
+            } else v = batch.lits[pr.lit_off + e - K - pr.n_affine];
+            cst[e] = v;
+        }
+    }
+    __syncwarp();
+
+    const uint32_t STAGE = 0, NEXT = S, BASE = 2 * S, SUM = 3 * S, STATE = 4 * S;
+    const uint32_t points = prob.points_per_trajectory;
+    M m;
+    float sq = 0.0f;
+    bool ok = true;
+    for (uint32_t t0 = 0; t0 < prob.num_trajectories; t0 += 128) {
+        bool live[4];
+        size_t first[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t traj = t0 + lane * 4 + q;
+            live[q] = traj < prob.num_trajectories;
+            first[q] = (size_t)(live[q] ? traj : 0) * points;
+        }
+        for (uint32_t s = 0; s < S; ++s) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float v = live[q] ? prob.reference[(size_t)s * prob.reference_ld + first[q]] : 0.0f;
+                ok = ok && (!live[q] || (fabsf(v) <= 3.402823466e+38f));
+                m.acc[q][0] = v;
+            }
+            m.store_slot(slots, STATE + s);
+        }
+        for (uint32_t k = 1; k < points; ++k) {
+            const float interval = prob.times[k] - prob.times[k - 1];
+            const float h = interval / (float)prob.substeps;
+            ok = ok && (fabsf(interval) <= 3.402823466e+38f) && interval > 0.0f && h > 0.0f;
+            const float half = 0.5f * h, sixth = h / 6.0f;
+            for (uint32_t sub = 0; sub < prob.substeps; ++sub) {
+                for (uint32_t s = 0; s < S; ++s) {
+                    m.fetch_slot(slots, STATE + s, m.acc);
+                    m.store_slot(slots, BASE + s);
+                    m.store_slot(slots, STAGE + s);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) m.acc[q][0] = 0.0f;
+                    m.store_slot(slots, SUM + s);
+                }
+#pragma unroll 1
+                for (int stage = 0; stage < 4; ++stage) {
+                    const float weight = (stage == 0 || stage == 3) ? 1.0f : 2.0f;
+                    const float stage_h = stage == 2 ? h : half;
+                    for (uint32_t s = 0; s < S; ++s) {
+                        const SbInsn* exec = reinterpret_cast<const SbInsn*>(warea + (size_t)s * exec_bytes);
+                        const float* cst = reinterpret_cast<const float*>(warea + (size_t)S * exec_bytes + (size_t)s * cst_bytes);
+                        m.run(exec, nullptr, 0, cst, slots, scratch_slot); /* acc = rhs of state s at the stage values */
+                        float rhs[4], v[4][1];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) rhs[q] = m.acc[q][0];
+                        m.fetch_slot(slots, SUM + s, v);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) m.acc[q][0] = __fmaf_rn(weight, rhs[q], v[q][0]);
+                        m.store_slot(slots, SUM + s);
+                        if (stage != 3) {
+                            m.fetch_slot(slots, BASE + s, v);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) m.acc[q][0] = __fmaf_rn(stage_h, rhs[q], v[q][0]);
+                            m.store_slot(slots, NEXT + s);
+                        }
+                    }
+                    if (stage != 3)
+                        for (uint32_t s = 0; s < S; ++s) {
+                            m.fetch_slot(slots, NEXT + s, m.acc);
+                            m.store_slot(slots, STAGE + s);
+                        }
+                }
+                for (uint32_t s = 0; s < S; ++s) {
+                    float sum[4][1], base[4][1];
+                    m.fetch_slot(slots, SUM + s, sum);
+                    m.fetch_slot(slots, BASE + s, base);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) m.acc[q][0] = __fmaf_rn(sixth, sum[q][0], base[q][0]);
+                    m.store_slot(slots, STATE + s);
+                }
+            }
+            for (uint32_t s = 0; s < S; ++s) { /* all states must be finite before any residual counts */
+                m.fetch_slot(slots, STATE + s, m.acc);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) ok = ok && (!live[q] || fabsf(m.acc[q][0]) <= 3.402823466e+38f);
+            }
+            for (uint32_t s = 0; s < S; ++s) {
+                m.fetch_slot(slots, STATE + s, m.acc);
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (live[q]) {
+                        const float err = __fsub_rn(m.acc[q][0], prob.reference[(size_t)s * prob.reference_ld + first[q] + k]);
+                        sq = __fmaf_rn(err, err, sq);
+                    }
+            }
+        }
+    }
+    const float total = warp_sum(sq);
+    const bool all_ok = __all_sync(0xffffffffu, ok);
+    if (lane == 0) {
+        const float residuals = (float)((unsigned long long)prob.num_trajectories * (points - 1) * S);
+        const bool finite = fabsf(total) <= 3.402823466e+38f;
+        prob.output[(size_t)sys * prob.output_ld + cfg] = (all_ok && finite) ? total / residuals : 3.402823466e+38f;
+    }
+}
+
 template <int RR, int RC>
 cudaError_t launch_variant(const DeviceBatch& batch, const EvalProblem& prob, const Geom& geom, const LaunchPlan& plan,
                            cudaStream_t stream) {
@@ -651,6 +807,22 @@ cudaError_t configure_kernels() {
     SB_FOR_VARIANTS(SB_CONFIGURE)
 #undef SB_CONFIGURE
     return cudaSuccess;
+}
+
+cudaError_t launch_rk4(const DeviceBatch& batch, const Rk4Problem& prob, size_t smem_limit, cudaStream_t stream) {
+    const uint32_t exec_bytes = round16(((size_t)batch.max_insn + 1) * sizeof(SbInsn));
+    const uint32_t cst_bytes = round16(((size_t)prob.num_constants + batch.max_extra) * 4 + 16);
+    const uint32_t scratch_slot = batch.max_slots; /* max_slots already includes the integrator's reserved slots */
+    const uint32_t warp_bytes = prob.num_states * (exec_bytes + cst_bytes) + (batch.max_slots + 1u) * 4u * 128u;
+    const size_t smem = (size_t)warp_bytes * kRk4Warps;
+    if (smem > smem_limit) return cudaErrorInvalidConfiguration;
+    cudaError_t e = cudaFuncSetAttribute(rk4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
+    if (e != cudaSuccess) return e;
+    const unsigned long long items = ((unsigned long long)prob.num_banks << prob.toggle_bits) * prob.num_systems;
+    const unsigned long long blocks = (items + kRk4Warps - 1) / kRk4Warps;
+    if (blocks > 0x7fffffffull) return cudaErrorInvalidConfiguration;
+    rk4_kernel<<<(unsigned)blocks, kRk4Warps * 32, smem, stream>>>(batch, prob, exec_bytes, cst_bytes, warp_bytes, scratch_slot);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPlan& plan, cudaStream_t stream) {

@@ -74,6 +74,22 @@ LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& problem, int
  * cleared beforehand for the accumulating modes.  Returns the CUDA status of the launch. */
 cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem& problem, const LaunchPlan& plan, cudaStream_t stream);
 
+/* Fixed-step RK4 rollout scoring of S-state systems whose right-hand sides are programs. */
+struct Rk4Problem {
+    uint32_t num_systems, num_states, num_constants, num_banks, toggle_bits;
+    const float* banks;            /* [system][bank][slot] */
+    size_t bank_stride, system_bank_stride;
+    const float* reference;        /* [state][total_points]; a trajectory starts at its first point */
+    size_t reference_ld;
+    uint32_t num_trajectories, points_per_trajectory, substeps;
+    const float* times;            /* [points_per_trajectory] */
+    float* output;                 /* [system][configuration] */
+    size_t output_ld;
+};
+/* batch.programs holds num_systems * num_states records, system-major, encoded with
+ * columns_are_slots and 5 * num_states reserved slots. */
+cudaError_t launch_rk4(const DeviceBatch& batch, const Rk4Problem& problem, size_t smem_limit, cudaStream_t stream);
+
 /* One-time per-device kernel attribute setup (dynamic shared memory opt-in). */
 cudaError_t configure_kernels();
 

@@ -136,6 +136,14 @@ class RunnerStats(C.Structure):
                 ("module_unload_seconds", C.c_double), ("runtime_seconds", C.c_double), ("total_seconds", C.c_double)]
 
 
+class Rk4Run(C.Structure):  # SecantB200Rk4Run
+    _fields_ = [("struct_size", _u32), ("version", _u32), ("flags", _u32), ("reserved", _u32), ("programs", ProgramSet),
+                ("num_systems", _sz), ("num_states", _sz), ("num_constants", _sz), ("constants", DeviceBanks),
+                ("system_bank_stride", _sz), ("num_banks", _sz), ("toggle_bits", _u32), ("reserved2", _u32),
+                ("reference", DeviceMatrix), ("num_trajectories", _sz), ("points_per_trajectory", _sz),
+                ("times", C.c_size_t), ("steps_per_observation", _sz), ("output", DeviceMatrix)]
+
+
 class Score(C.Structure):  # SecantB200Score, layout of the reference consumer's SRScore
     _fields_ = [("sse", C.c_float), ("reserved", _u32), ("configuration", C.c_uint64), ("valid_configurations", C.c_uint64)]
 
@@ -188,6 +196,7 @@ EXPORTED = {
     "secant_b200_population_num_ops": (C.c_uint64, [C.c_void_p]),
     "secant_b200_population_destroy": (C.c_int32, [C.c_void_p]),
     "secant_b200_runner_force_variant": (None, [C.c_void_p, C.c_int]),
+    "secant_b200_rk4_score": (C.c_int32, [C.c_void_p]),
     "secant_b200_best_config": (C.c_int32, [C.c_size_t, _sz, _sz, _sz, C.c_size_t, C.c_void_p]),
     "secant_b200_topk": (C.c_int32, [C.c_size_t, _sz, _sz, C.c_size_t, C.c_size_t, C.c_void_p]),
     "secant_b200_topk_scratch_elements": (_sz, [_sz, _sz]),

@@ -240,3 +240,32 @@ def topk(scores, k):
     abi.check(lib.secant_b200_topk(scores.data_ptr(), scores.numel(), k, idx.data_ptr(), val.data_ptr(), C.c_void_p(stream)),
               "secant_b200_topk")
     return idx, val
+
+
+def rk4_score(packed, num_states, reference, times, constants=None, num_constants=0, num_banks=1, toggle_bits=0,
+              steps_per_observation=1, points_per_trajectory=None):
+    """Fixed-step RK4 rollout scores [system][configuration] (extension API).
+
+    packed: num_systems * num_states right-hand-side programs, system-major.
+    reference: CUDA tensor [state][trajectories * points]; times: CUDA tensor [points];
+    constants: CUDA tensor [system][bank][slot] or None."""
+    lib = abi.load()
+    run = abi.Rk4Run()
+    run.struct_size, run.version = C.sizeof(run), abi.RUN_VERSION
+    packed.fill(run.programs)
+    points = points_per_trajectory or times.numel()
+    systems = len(packed.asts) // num_states
+    run.num_systems, run.num_states, run.num_constants = systems, num_states, num_constants
+    if constants is not None and num_constants:
+        run.constants.address, run.constants.num_elements, run.constants.bank_stride = (
+            constants.data_ptr(), constants.numel(), constants.shape[-1])
+    run.num_banks, run.toggle_bits = num_banks, toggle_bits
+    run.reference = _matrix(reference)
+    run.num_trajectories = reference.shape[-1] // points
+    run.points_per_trajectory = points
+    run.times = times.data_ptr()
+    run.steps_per_observation = steps_per_observation
+    out = torch.empty((systems, num_banks << toggle_bits), dtype=torch.float32, device=reference.device)
+    run.output = _matrix(out)
+    abi.check(lib.secant_b200_rk4_score(C.byref(run)), "secant_b200_rk4_score")
+    return out

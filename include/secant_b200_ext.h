@@ -77,6 +77,39 @@ SECANT_DEC SecantResult secant_b200_population_destroy(SecantB200Population popu
 SECANT_DEC void secant_b200_runner_force_variant(SecantCubinRunner runner, int variant);
 
 /*
+ * RK4 rollout scoring: the population-evaluation path with the program inside an integration
+ * loop.  num_systems candidate systems of num_states (<= 8) right-hand-side programs each
+ * (programs.asts is system-major: system i, state s at index i*num_states + s; COLUMN s reads
+ * state s, BANK_CONSTANT k coefficient k) are integrated with fixed-step RK4 from the first
+ * point of every reference trajectory and scored by mean squared error against it.
+ * Semantics of the reference engine's scoring kernel
+ * (projects/odezza/core/o_generate_scoring_cuda.c:494-588): h = (times[k]-times[k-1]) /
+ * steps_per_observation, explicit fmaf in every stage update, score = FLT_MAX (never NaN) as
+ * soon as a time step, an initial state, an integrated state or the error sum is not finite.
+ *   reference   [state][trajectory * points_per_trajectory + point], device, f32
+ *   times       device float[points_per_trajectory], shared by all trajectories
+ *   constants   [system][bank][slot]; system_bank_stride 0 = num_banks * bank_stride
+ *   output      [system][configuration], configuration = bank * 2^toggle_bits + permutation
+ * Blocking; uses the current CUDA device and context.  Transcendental opcodes are allowed in
+ * right-hand sides, but only exactly rounded operations (add, sub, mul, div, fma, sqrt, neg,
+ * abs, min, max) reproduce a host rollout bit for bit, which chaotic systems need.
+ */
+typedef struct SecantB200Rk4Run {
+    uint32_t struct_size, version, flags, reserved;   /* version = SECANT_CUBIN_RUN_VERSION_3 */
+    SecantAstProgramSet programs;
+    size_t num_systems, num_states, num_constants;
+    SecantDeviceConstantBanks constants;
+    size_t system_bank_stride, num_banks;
+    uint32_t toggle_bits, reserved2;
+    SecantDeviceMatrixF32 reference;
+    size_t num_trajectories, points_per_trajectory;
+    uintptr_t times;
+    size_t steps_per_observation;
+    SecantDeviceMatrixF32 output;
+} SecantB200Rk4Run;
+SECANT_DEC SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run);
+
+/*
  * Best configuration of every score vector, on the device.  `scores` is [vector][configuration]
  * float32 with `leading_dimension` elements between vectors (for a toggle-SSE grid with one
  * target: vector = program).  A score is valid when finite and >= 0; the winner is the

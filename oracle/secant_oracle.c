@@ -573,7 +573,9 @@ SO_EXPORT size_t so_topk(const float* scores, size_t count, size_t k, uint64_t* 
  * sq = fmaf(err, err, sq).  Score = sq / residual_count when everything stayed finite and
  * intervals are positive, else FLT_MAX (3.402823466e+38F), never NaN.
  * Residuals are accumulated trajectory by trajectory in one binary32 accumulator, like
- * the reference thread does.
+ * the reference thread does; with ~2e5 residuals that sum alone is only good to ~1e-4
+ * relative (small terms fall below the accumulator's ulp), so scores64 optionally returns the
+ * same residuals accumulated in binary64.
  * Transcendental opcodes are evaluated with libm here; a device implementation that
  * wants bit-identical chaotic rollouts must restrict right-hand sides to exactly
  * rounded operations (add, sub, mul, div, fma, sqrt, rcp, neg, abs, min, max).
@@ -583,7 +585,8 @@ SO_EXPORT SecantResult so_rk4_score(const uint8_t* routine_blob, const uint64_t*
                                     const uint8_t* rhs_blob, const uint64_t* rhs_off, size_t num_systems,
                                     size_t num_states, size_t num_constants, const float* constants,
                                     size_t system_constant_stride, const float* reference, size_t num_trajectories,
-                                    size_t points_per_trajectory, const float* times, size_t substeps, float* scores) {
+                                    size_t points_per_trajectory, const float* times, size_t substeps, uint32_t toggle_bits,
+                                    uint32_t permutation, float* scores, double* scores64) {
     SoPrograms p;
     SoEnv env;
     const size_t total_points = num_trajectories * points_per_trajectory;
@@ -597,8 +600,10 @@ SO_EXPORT SecantResult so_rk4_score(const uint8_t* routine_blob, const uint64_t*
     memset(&env, 0, sizeof(env));
     env.routines = p.routines; env.num_routines = num_routines; env.arity = p.arity;
     env.num_columns = num_states; env.num_constants = num_constants; env.input_ld = 1; env.row = 0;
+    env.toggle_bits = toggle_bits; env.permutation = permutation;
     for (sys = 0; r == SECANT_SUCCESS && sys < num_systems; ++sys) {
         float sq = 0.0f;
+        double sq64 = 0.0; /* same residuals accumulated in binary64, free of summation-order error */
         size_t residuals = 0;
         int valid = 1;
         env.constants = num_constants ? constants + sys * system_constant_stride : NULL;
@@ -630,12 +635,14 @@ SO_EXPORT SecantResult so_rk4_score(const uint8_t* routine_blob, const uint64_t*
                 for (s = 0; s < num_states; ++s) {
                     const float err = state[s] - reference[s * total_points + first + k];
                     sq = fmaf(err, err, sq);
+                    sq64 += (double)err * (double)err;
                     ++residuals;
                 }
             }
         }
         if (r != SECANT_SUCCESS) break;
         scores[sys] = (valid && residuals && isfinite(sq)) ? sq / (float)residuals : FLT_MAX;
+        if (scores64) scores64[sys] = (valid && residuals && isfinite(sq)) ? sq64 / (double)residuals : (double)FLT_MAX;
     }
     so_programs_close(&p);
     return r;

@@ -248,3 +248,19 @@ def sse_slack(packed, x, y, banks, num_constants, toggle_bits, program_bank_stri
             term[sens == 0] = 0.0
             slack[:, t, cfg] = term.sum(axis=1)
     return slack
+
+
+def oracle_rk4(packed, num_states, reference, num_trajectories, times, constants=None, substeps=1, toggle_bits=0,
+               permutation=0, want64=False):
+    """RK4 rollout scores of the CPU restatement, one per system (single bank per system)."""
+    systems = len(packed.asts) // num_states
+    K = constants.shape[1] if constants is not None else 0
+    scores = np.zeros(systems, dtype=np.float32)
+    scores64 = np.zeros(systems, dtype=np.float64)
+    code = oracle().so_rk4_score(*blob_args(packed)[:5], C.c_size_t(systems), C.c_size_t(num_states), C.c_size_t(K),
+                                 fptr(constants) if K else None, C.c_size_t(K), fptr(reference), C.c_size_t(num_trajectories),
+                                 C.c_size_t(len(times)), fptr(times), C.c_size_t(substeps), C.c_uint32(toggle_bits),
+                                 C.c_uint32(permutation), fptr(scores), scores64.ctypes.data_as(F64P))
+    if want64:
+        return code, scores, scores64
+    return code, scores

@@ -1,0 +1,101 @@
+"""GPU RK4 rollout scoring against the CPU restatement.
+
+Right-hand sides built from exactly rounded operations integrate bit-identically on both
+sides, so even a chaotic system (Lorenz, 1000 steps) must agree to summation-order precision
+(1e-4 relative).  Right-hand sides with transcendental functions are compared on a short,
+contracting horizon, where a 2-ulp difference of the math library cannot grow."""
+import numpy as np
+import pytest
+import torch
+
+import support as S
+from secant_b200 import programs as P
+from secant_b200.runner import rk4_score
+from test_rk4_cpu import FLT_MAX, slope_case
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.tensor(np.ascontiguousarray(a), device="cuda")
+
+
+def lorenz_programs():
+    col, bank, op = P.col, P.bank, P.op
+    return [col(1) + col(0) + op("SUB") + bank(0) + op("MUL") + P.RET,
+            col(0) + bank(1) + col(2) + op("SUB") + op("MUL") + col(1) + op("SUB") + P.RET,
+            col(0) + col(1) + op("MUL") + bank(2) + col(2) + op("MUL") + op("SUB") + P.RET]
+
+
+def lorenz_reference(num_ics, steps, dt):
+    """Reference rollout: the restated integrator itself on the true Lorenz system, float32."""
+    rng = np.random.default_rng(4)
+    ics = rng.uniform(-10, 10, size=(num_ics, 3)).astype(np.float32)
+    ref = np.zeros((3, num_ics * (steps + 1)), dtype=np.float32)
+    sigma, rho, beta = np.float32(10.0), np.float32(28.0), np.float32(8.0 / 3.0)
+    h = np.float32(dt)
+
+    def rhs(v):
+        x, y, z = v
+        return np.array([(y - x) * sigma, x * (rho - z) - y, x * y - beta * z], dtype=np.float32)
+    for i in range(num_ics):
+        v = ics[i].copy()
+        ref[:, i * (steps + 1)] = v
+        for k in range(1, steps + 1):
+            k1 = rhs(v); k2 = rhs(v + h / 2 * k1); k3 = rhs(v + h / 2 * k2); k4 = rhs(v + h * k3)
+            v = (v + h / 6 * (k1 + 2 * k2 + 2 * k3 + k4)).astype(np.float32)
+            ref[:, i * (steps + 1) + k] = v
+    return ref
+
+
+def test_constant_slope_closed_form_and_invalid_policy(cuda):
+    systems, reference, times, constants = slope_case()
+    got = rk4_score(systems, 1, dev(reference), dev(times), dev(constants[:, None, :]), 1, 1, 0, 4).cpu().numpy()[:, 0]
+    assert np.allclose(got, [0.53125 * e * e for e in range(4)], atol=2e-6)
+    bad = reference.copy(); bad[0, 3] = np.nan
+    got = rk4_score(systems, 1, dev(bad), dev(times), dev(constants[:, None, :]), 1, 1, 0, 1).cpu().numpy()
+    assert np.all(got == FLT_MAX)
+    blow = P.PackedPrograms([P.col(0) + P.col(0) + P.op("MUL") + P.lit(1e30) + P.op("MUL") + P.RET])
+    assert rk4_score(blow, 1, dev(reference), dev(times)).cpu().numpy()[0, 0] == FLT_MAX
+
+
+def test_lorenz_candidates_match_oracle_over_a_chaotic_horizon(cuda):
+    num_ics, steps, dt = 64, 1000, 0.01
+    ref = lorenz_reference(num_ics, steps, dt)
+    times = (np.arange(steps + 1, dtype=np.float32) * np.float32(dt)).astype(np.float32)
+    rng = np.random.default_rng(8)
+    n_sys = 24
+    coeffs = np.tile(np.array([10.0, 28.0, 8.0 / 3.0], dtype=np.float32), (n_sys, 1))
+    coeffs[1:] += rng.normal(0, 0.5, size=(n_sys - 1, 3)).astype(np.float32)
+    coeffs[-1] = [10.0, 2000.0, -5.0]                                    # an explosive candidate
+    pop = P.PackedPrograms(lorenz_programs() * n_sys)
+    code, want, want64 = S.oracle_rk4(pop, 3, ref, num_ics, times, coeffs, want64=True)
+    assert code == 0
+    got = rk4_score(pop, 3, dev(ref), dev(times), dev(coeffs[:, None, :]), 3).cpu().numpy()[:, 0]
+    assert np.array_equal(got == FLT_MAX, want == FLT_MAX)
+    fin = want != FLT_MAX
+    # trajectories are bit-identical; only the 192,000-term residual sum differs.  Against the
+    # float64-accumulated sum the tolerance is 1e-4; the oracle's own sequential float32 sum
+    # (the reference thread's order) is itself ~1e-4 low and is held to 5e-4.
+    assert np.allclose(got[fin], want64[fin], rtol=1e-4, atol=1e-7)
+    assert np.allclose(got[fin], want[fin], rtol=5e-4, atol=1e-7)
+    assert want[0] < 1e-3 and want[1:-1].min() > 1.0                     # the true system wins by a wide margin
+    assert int(np.argmin(got)) == int(np.argmin(want)) == 0
+
+
+def test_banks_toggles_and_random_right_hand_sides(cuda):
+    S_, K, nb, bits = 2, 3, 3, 1
+    ops = [(P.op("ADD"), 2), (P.op("SUB"), 2), (P.op("MUL"), 2), (P.op("SIN"), 1), (P.op("COS"), 1), (P.op("TANH"), 1)]
+    raw = P.random_population(12, 40 * S_, 14, S_, K, 1.0, toggle_bits=bits, ops=ops)
+    # damp every candidate: rhs_s = tanh(program) - state_s keeps trajectories bounded and contracting
+    asts = [a[:-1] + P.op("TANH") + P.col(i % S_) + P.op("SUB") + P.RET for i, a in enumerate(raw.asts)]
+    pop = P.PackedPrograms(asts, raw.routines)
+    points, ntraj = 21, 130                                             # more than one block of 128 trajectories
+    times = (np.arange(points, dtype=np.float32) * np.float32(0.05)).astype(np.float32)
+    ref = np.stack([P.uniform(13, s, ntraj * points, -1, 1) for s in range(S_)])
+    banks = np.stack([np.stack([P.normal(14, sy * 10 + b, K) for b in range(nb)]) for sy in range(40)])
+    got = rk4_score(pop, S_, dev(ref), dev(times), dev(banks), K, nb, bits, 2).cpu().numpy()
+    for cfg in range(nb << bits):
+        code, want = S.oracle_rk4(pop, S_, ref, ntraj, times, np.ascontiguousarray(banks[:, cfg >> bits, :]), 2, bits, cfg & 1)
+        assert code == 0
+        assert np.allclose(got[:, cfg], want, rtol=2e-4, atol=1e-6), cfg
