@@ -21,7 +21,7 @@ namespace sb {
 
 void EncodedBatch::clear() {
     programs.clear(); insns.clear(); patches.clear(); affines.clear(); lits.clear();
-    max_insn = 1; max_extra = 0; max_slots = 0; max_patch = 0;
+    max_insn = 1; max_extra = 0; max_slots = 0; max_patch = 0; max_hoisted = 0;
 }
 
 namespace {
@@ -48,6 +48,9 @@ struct Node {
     int32_t pending = 0;  /* uses not yet emitted */
     int32_t slot = -1;    /* spill slot holding the value, once computed */
     int32_t su = 0;       /* slots needed to compute the node into the accumulator */
+    int8_t varies = -1;   /* depends on a coefficient bank (memoised, -1 = unknown) */
+    int32_t hoisted = -1; /* index of the per-row value the prelude left, once hoisted */
+    int32_t weight = 0;   /* rough instruction cost of the sub-expression */
 };
 
 struct Parser {
@@ -205,7 +208,7 @@ struct Emitter {
     SecantResult error;
 
     static bool leaf_type(const Node& n) { return n.type <= N_TOGGLE; }
-    bool ready(int id) const { return leaf_type(nodes[id]) || nodes[id].slot >= 0; }
+    bool ready(int id) const { return leaf_type(nodes[id]) || nodes[id].slot >= 0 || nodes[id].hoisted >= 0; }
 
     int alloc_slot() {
         for (size_t i = 0; i < slot_busy.size(); ++i)
@@ -216,17 +219,29 @@ struct Emitter {
         return (int)slot_busy.size() - 1;
     }
 
+    /* The prelude expressions and the main part are emitted as separate phases that share
+     * nothing but hoisted values: parent counts, pending uses and slots start afresh, so a
+     * node needed by two phases is simply computed in both (a slot written by the prelude of
+     * one row pass could not be trusted by the main part of every bank group). */
+    void begin_phase(int phase_root) {
+        for (auto& n : nodes) { n.uses = 0; n.pending = 0; n.slot = -1; }
+        std::fill(slot_busy.begin(), slot_busy.end(), 0);
+        for (unsigned i = 0; i < rules.reserved_slots && i < slot_busy.size(); ++i) slot_busy[i] = 1;
+        prepare(phase_root);
+        for (auto& n : nodes) n.pending = n.uses;
+    }
+
     /* Counts parent references of every reachable node and computes how many slots each
      * needs while it is being evaluated (Sethi-Ullman numbers, DAG-agnostic estimate). */
     void prepare(int id) {
         Node& n = nodes[id];
         if (n.uses++ > 0) return;
-        if (leaf_type(n)) { n.su = 0; return; }
+        if (leaf_type(n) || n.hoisted >= 0) { n.su = 0; return; } /* a hoisted value is read like a leaf */
         const unsigned arity = n.type == N_UN ? 1 : n.type == N_BIN ? 2 : 3;
         for (unsigned i = 0; i < arity; ++i) prepare(nodes[id].child[i]);
         int need[3], cnt = 0;
         for (unsigned i = 0; i < arity; ++i)
-            if (!leaf_type(nodes[nodes[id].child[i]])) need[cnt++] = nodes[nodes[id].child[i]].su;
+            if (!leaf_type(nodes[nodes[id].child[i]]) && nodes[nodes[id].child[i]].hoisted < 0) need[cnt++] = nodes[nodes[id].child[i]].su;
         for (int i = 0; i < cnt; ++i)
             for (int j = i + 1; j < cnt; ++j)
                 if (need[j] > need[i]) { int t = need[i]; need[i] = need[j]; need[j] = t; }
@@ -253,6 +268,7 @@ struct Emitter {
     Operand describe(int id, bool allow_imm) {
         const Node& n = nodes[id];
         if (n.slot >= 0) return Operand{SB_KIND_SLOT, (unsigned)n.slot, 0};
+        if (n.hoisted >= 0) return Operand{SB_KIND_HROW, (unsigned)n.hoisted, 0};
         switch (n.type) {
         case N_COL: return rules.columns_are_slots ? Operand{SB_KIND_SLOT, n.index, 0} : Operand{SB_KIND_ROW, n.index, 0};
         case N_BANK: return Operand{SB_KIND_CST, n.index, 0};
@@ -298,6 +314,66 @@ struct Emitter {
     }
     static unsigned bin_case(unsigned op) { return SB_CASE_BIN + op * SB_NUM_KINDS; }
 
+    /* Does the value of `id` depend on the coefficient bank?  Also accumulates a rough cost. */
+    bool varies(int id) {
+        Node& n = nodes[id];
+        if (n.varies >= 0) return n.varies != 0;
+        bool v = false;
+        int w = 0;
+        switch (n.type) {
+        case N_BANK: case N_AFFINE: v = true; break;
+        case N_COL: case N_LIT: break;
+        case N_TOGGLE:
+            for (unsigned i = 0; i < n.ways; ++i) v = varies(n.child[i]) || v;
+            break;
+        default: {
+            const unsigned arity = n.type == N_UN ? 1 : n.type == N_BIN ? 2 : 3;
+            for (unsigned i = 0; i < arity; ++i) { v = varies(nodes[id].child[i]) || v; w += nodes[nodes[id].child[i]].weight; }
+            if (n.type == N_UN) w += (n.op == SB_UN_NEG || n.op == SB_UN_ABS) ? 1 : 20;
+            else if (n.type == N_BIN) w += n.op == SB_BIN_DIV ? 10 : 1;
+            else w += 4;
+        }
+        }
+        nodes[id].varies = v ? 1 : 0;
+        nodes[id].weight = w;
+        return v;
+    }
+    /* Maximal bank-independent computed sub-expressions below `id`. */
+    void collect_invariants(int id, std::vector<int>& found, std::vector<uint8_t>& seen) {
+        if (seen[(size_t)id]) return;
+        seen[(size_t)id] = 1;
+        const Node& n = nodes[id];
+        if (leaf_type(n)) return;
+        if (!varies(id)) { found.push_back(id); return; }
+        const unsigned arity = n.type == N_UN ? 1 : n.type == N_BIN ? 2 : 3;
+        for (unsigned i = 0; i < arity; ++i) collect_invariants(nodes[id].child[i], found, seen);
+    }
+    /* Emits the prelude: every kept invariant sub-expression is computed and parked in a slot
+     * that stays reserved for the rest of the program.  Returns how many were hoisted. */
+    unsigned emit_prelude(int root) {
+        std::vector<int> found;
+        std::vector<uint8_t> seen(nodes.size(), 0);
+        collect_invariants(root, found, seen);
+        if (found.empty()) return 0;
+        for (size_t i = 0; i < found.size(); ++i)          /* heaviest first, then keep the budget */
+            for (size_t j = i + 1; j < found.size(); ++j)
+                if (nodes[found[j]].weight > nodes[found[i]].weight) { int t = found[i]; found[i] = found[j]; found[j] = t; }
+        if (found.size() > rules.max_hoisted) found.resize(rules.max_hoisted);
+        for (size_t i = 0; i < found.size(); ++i)          /* operands before the expressions that use them */
+            for (size_t j = i + 1; j < found.size(); ++j)
+                if (found[j] < found[i]) { int t = found[i]; found[i] = found[j]; found[j] = t; }
+        unsigned h = 0;
+        for (int id : found) {
+            begin_phase(id);
+            gen(id);
+            if (error != SECANT_SUCCESS) return 0;
+            push(sb_w0(SB_CASE_STOREH, 0, h), 0);
+            nodes[id].hoisted = (int32_t)h++;
+        }
+        push(sb_w0(SB_CASE_END, 0, 0), 0);
+        return (unsigned)found.size();
+    }
+
     void gen(int id) {
         if (error != SECANT_SUCCESS) return;
         if (ready(id)) { emit_reading(SB_CASE_LOAD, id); return; }
@@ -332,10 +408,13 @@ struct Emitter {
 
     void gen_fma(const Node& n) {
         int ch[3] = {n.child[0], n.child[1], n.child[2]};
-        /* a toggle operand is selected by a patched LOAD and parked in a private slot */
+        /* a toggle operand (selected by a patched LOAD) or a hoisted per-row value cannot be
+         * named by the FMA instruction: load it and park it in a private slot */
         for (int i = 0; i < 3; ++i) {
             const int id = ch[i];
-            if (nodes[id].type != N_TOGGLE || nodes[id].slot >= 0) continue;
+            const bool toggle = nodes[id].type == N_TOGGLE && nodes[id].slot < 0;
+            const bool hrow = nodes[id].hoisted >= 0 && nodes[id].slot < 0;
+            if (!toggle && !hrow) continue;
             emit_reading(SB_CASE_LOAD, id);
             Node t{N_UN};
             nodes.push_back(t);
@@ -461,8 +540,11 @@ SecantResult encode_program(const SecantAstInstruction* program, const SecantAst
     Emitter em{nodes, rules, out, out.insns.size(), out.lits.size(), (unsigned)affines.size(), {}, 0, SECANT_SUCCESS};
     em.slot_busy.assign(rules.reserved_slots, 1);
     em.slots_high = rules.reserved_slots;
-    em.prepare(root); /* counts the RETURN as the root's first use */
-    for (auto& n : nodes) n.pending = n.uses;
+    unsigned hoisted = 0;
+    if (rules.hoist_invariants && !rules.columns_are_slots) hoisted = em.emit_prelude(root);
+    if (em.error != SECANT_SUCCESS) return em.error;
+    const size_t main_off = hoisted ? out.insns.size() - rec.insn_off : 0;
+    em.begin_phase(root); /* counts the RETURN as the root's first use */
     em.gen(root);
     if (em.error != SECANT_SUCCESS) return em.error;
     em.push(sb_w0(SB_CASE_END, 0, 0), 0);
@@ -480,11 +562,14 @@ SecantResult encode_program(const SecantAstInstruction* program, const SecantAst
     rec.n_lits = (uint16_t)n_lits;
     rec.n_slots = (uint16_t)em.slots_high;
     rec.n_ops = (uint16_t)(parser.n_ops > 0xffffu ? 0xffffu : parser.n_ops);
+    rec.main_off = (uint16_t)main_off;
+    rec.n_hoisted = (uint16_t)hoisted;
     out.programs.push_back(rec);
     if (n_insn > out.max_insn) out.max_insn = (unsigned)n_insn;
     if (affines.size() + n_lits > out.max_extra) out.max_extra = (unsigned)(affines.size() + n_lits);
     if (em.slots_high > out.max_slots) out.max_slots = em.slots_high;
     if (n_patch > out.max_patch) out.max_patch = (unsigned)n_patch;
+    if (hoisted > out.max_hoisted) out.max_hoisted = hoisted;
     return SECANT_SUCCESS;
 }
 

@@ -29,6 +29,11 @@ struct ProgramRules {
      * belong to the integrator and program temporaries start after them. */
     bool columns_are_slots = false;
     unsigned reserved_slots = 0;
+    /* Move bank-independent sub-expressions into a prelude (record.h, SbProgram::main_off);
+     * at most max_hoisted values are parked.  Values and rounding are unchanged: the same
+     * operations run on the same operands, once per row instead of once per (row, bank). */
+    bool hoist_invariants = false;
+    unsigned max_hoisted = 3;
 };
 
 /* Encoded records of a contiguous group of programs, ready to upload as five arrays. */
@@ -42,6 +47,7 @@ struct EncodedBatch {
     unsigned max_extra = 0;     /* largest n_affine + n_lits */
     unsigned max_slots = 0;     /* largest n_slots */
     unsigned max_patch = 0;
+    unsigned max_hoisted = 0;   /* largest n_hoisted */
     void clear();
 };
 

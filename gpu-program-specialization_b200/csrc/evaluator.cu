@@ -42,6 +42,7 @@ struct Geom {
     uint32_t exec_bytes;     /* per-warp regions, each a multiple of 16 bytes */
     uint32_t cst_bytes;
     uint32_t tacc_bytes;
+    uint32_t hoist_bytes;    /* per-row values left by the prelude: max_hoisted x tile_rows floats */
     uint32_t warp_bytes;
     uint32_t tile_bytes;
     unsigned long long rows_per_split;
@@ -186,6 +187,10 @@ struct Machine {
     case SB_CASE_BIN + OP * SB_NUM_KINDS + SB_KIND_IMM: {                                            \
         const float x = __uint_as_float(ins.y);                                                      \
         SB_FOR_TILE acc[r][c] = binop<OP>(acc[r][c], x);                                             \
+        break; }                                                                                     \
+    case SB_CASE_BIN + OP * SB_NUM_KINDS + SB_KIND_HROW: {                                           \
+        float x[RR]; fetch_row(hrowp, tile_ld, idx, x);                                              \
+        SB_FOR_TILE acc[r][c] = binop<OP>(acc[r][c], x[r]);                                          \
         break; }
 
 #define SB_UN_CASE(OP) \
@@ -204,7 +209,7 @@ struct Machine {
 
     /* Runs the warp's program once over the RR*32 rows starting at rowp. */
     __device__ __forceinline__ void run(const SbInsn* exec, const float* rowp, uint32_t tile_ld, const float* cst,
-                                        float4* slots, uint32_t scratch_slot) {
+                                        float4* slots, uint32_t scratch_slot, float* hrowp = nullptr) {
         const uint2* ip = reinterpret_cast<const uint2*>(exec);
         uint2 next = *ip++; /* the buffer holds one padding entry after END */
 #pragma unroll 1
@@ -230,9 +235,19 @@ struct Machine {
                 const float x = __uint_as_float(ins.y);
                 SB_FOR_TILE acc[r][c] = x;
                 break; }
+            case SB_CASE_LOAD + SB_KIND_HROW: {
+                float x[RR]; fetch_row(hrowp, tile_ld, idx, x);
+                SB_FOR_TILE acc[r][c] = x[r];
+                break; }
             case SB_CASE_STORE:
                 store_slot(slots, idx);
                 break;
+            case SB_CASE_STOREH: { /* bank-independent value: every bank column holds the same number */
+                float* q = hrowp + (size_t)idx * tile_ld;
+#pragma unroll
+                for (int g = 0; g < GROUPS; ++g)
+                    *reinterpret_cast<float4*>(q + g * 128) = make_float4(acc[4 * g][0], acc[4 * g + 1][0], acc[4 * g + 2][0], acc[4 * g + 3][0]);
+                break; }
             SB_BIN_CASES(SB_BIN_ADD)
             SB_BIN_CASES(SB_BIN_SUB)
             SB_BIN_CASES(SB_BIN_RSUB)
@@ -246,12 +261,14 @@ struct Machine {
             case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_SLOT:
             case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_SLOT:
             case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_IMM:
-            case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_IMM: {
+            case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_IMM:
+            case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_HROW:
+            case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_HROW: {
                 const unsigned rel = (ins.x & 0xffu) - SB_CASE_BIN;
                 const unsigned kind = rel % SB_NUM_KINDS;
                 float xv[RR][RC];
-                if (kind == SB_KIND_ROW) {
-                    float x[RR]; fetch_row(rowp, tile_ld, idx, x);
+                if (kind == SB_KIND_ROW || kind == SB_KIND_HROW) {
+                    float x[RR]; fetch_row(kind == SB_KIND_ROW ? rowp : hrowp, tile_ld, idx, x);
                     SB_FOR_TILE xv[r][c] = x[r];
                 } else if (kind == SB_KIND_CST) {
                     float x[RC]; fetch_cst(cst, idx, x);
@@ -329,7 +346,8 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
     SbInsn* const exec = reinterpret_cast<SbInsn*>(warea);
     float* const cst = reinterpret_cast<float*>(warea + geom.exec_bytes);
     float* const tacc = reinterpret_cast<float*>(warea + geom.exec_bytes + geom.cst_bytes);
-    float4* const slots = reinterpret_cast<float4*>(warea + geom.exec_bytes + geom.cst_bytes + geom.tacc_bytes) + lane;
+    float* const hoist = reinterpret_cast<float*>(warea + geom.exec_bytes + geom.cst_bytes + geom.tacc_bytes);
+    float4* const slots = reinterpret_cast<float4*>(warea + geom.exec_bytes + geom.cst_bytes + geom.tacc_bytes + geom.hoist_bytes) + lane;
 
     const uint32_t group = blockIdx.x / geom.row_splits, split = blockIdx.x % geom.row_splits;
     const uint32_t prog_begin = group * geom.programs_per_cta;
@@ -372,7 +390,6 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
             const unsigned long long first_group = (item % items_per_program) * geom.groups_per_item;
             const unsigned long long last_group = min(cfg_groups, first_group + geom.groups_per_item);
             const uint32_t lp = prog_begin + pi;           /* index inside the batch */
-            const size_t gp = prob.first_program + lp;     /* index inside the run */
             __syncwarp();
             if (lp != loaded) {
                 pr = batch.programs[lp];
@@ -382,22 +399,27 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
                     cst[(K + pr.n_affine) * RC + i] = batch.lits[pr.lit_off + i / RC];
                 loaded = lp;
             }
+            const size_t gp = prob.first_program + pr.index; /* position in the run: output row, bank table */
             const float* bank_base = prob.banks ? prob.banks + gp * prob.program_bank_stride : nullptr;
-            unsigned long long patched_for = ~0ull;
-
-            for (unsigned long long cg = first_group; cg < last_group; ++cg) {
-                const unsigned long long perm = materialize ? prob.fixed_permutation : cg / bank_groups;
-                const uint32_t bg = (uint32_t)(cg % bank_groups);
-                __syncwarp();
-                if (pr.n_patch && perm != patched_for) {
-                    for (uint32_t i = lane; i < pr.n_patch; i += 32) {
-                        const SbPatch* p = batch.patches + pr.patch_off + i;
-                        unsigned choice = (unsigned)(perm >> p->bit0) & 1u;
-                        if (p->bit1 != 0xffu) choice |= ((unsigned)(perm >> p->bit1) & 1u) << 1;
-                        exec[p->insn] = p->alt[choice];
-                    }
-                    patched_for = perm;
+            /* an item never straddles permutations: toggles are patched once per item */
+            const unsigned long long perm = materialize ? prob.fixed_permutation : first_group / bank_groups;
+            if (pr.n_patch) {
+                __syncwarp(); /* the copy above and the patches below touch the same words from different lanes */
+                for (uint32_t i = lane; i < pr.n_patch; i += 32) {
+                    const SbPatch* p = batch.patches + pr.patch_off + i;
+                    unsigned choice = (unsigned)(perm >> p->bit0) & 1u;
+                    if (p->bit1 != 0xffu) choice |= ((unsigned)(perm >> p->bit1) & 1u) << 1;
+                    exec[p->insn] = p->alt[choice];
                 }
+            }
+            /* iteration -1 (only when the program has a prelude) evaluates the bank-independent
+             * sub-expressions once per row; iterations 0.. evaluate the main part per bank group */
+            const long long steps = (long long)(last_group - first_group);
+            for (long long step = pr.main_off ? -1 : 0; step < steps; ++step) {
+                const bool prelude = step < 0;
+                const uint32_t bg = prelude ? 0u : (uint32_t)((first_group + (unsigned long long)step) % bank_groups);
+                __syncwarp();
+                if (!prelude)
                 for (uint32_t e = lane; e < (K + pr.n_affine) * RC; e += 32) {
                     const uint32_t entry = e / RC, c = e % RC, bank = bg * RC + c;
                     float v = 0.0f;
@@ -411,7 +433,7 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
                     }
                     cst[e] = v;
                 }
-                if (T > 1 || prob.mode == EVAL_AFFINE_STATS)
+                if (!prelude && (T > 1 || prob.mode == EVAL_AFFINE_STATS))
                     for (uint32_t e = lane; e < (T + 2) * RC; e += 32) tacc[e] = 0.0f;
                 __syncwarp();
 
@@ -423,7 +445,9 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
 #pragma unroll 1
                 for (uint32_t pass = 0; pass < npass; ++pass) {
                     const float* rowp = tile + pass * M::PASS + lane * 4;
-                    m.run(exec, rowp, tile_ld, cst, slots, geom.scratch_slot);
+                    m.run(exec + (prelude ? 0u : (uint32_t)pr.main_off), rowp, tile_ld, cst, slots, geom.scratch_slot,
+                          hoist + pass * M::PASS + lane * 4);
+                    if (prelude) continue;
                     const uint32_t row0 = pass * M::PASS + lane * 4; /* first row of this thread in the chunk */
                     const bool full = (pass + 1) * M::PASS <= chunk_rows;
                     if (materialize) {
@@ -490,6 +514,7 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
                     }
                 }
 
+                if (prelude) continue;
                 if (prob.mode == EVAL_SSE && T == 1) {
                     float mine = 0.0f;
 #pragma unroll
@@ -500,8 +525,7 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
                     const uint32_t bank = bg * RC + lane;
                     if (lane < RC && bank < prob.num_banks) {
                         float* dst = prob.output + gp * prob.out_program_stride + ((size_t)bank << prob.toggle_bits) + perm;
-                        if (geom.use_atomics) atomicAdd(dst, mine);
-                        else *dst += mine;
+                        atomicAdd(dst, mine); /* result unused: a reduction that never stalls the warp */
                     }
                 } else if (!materialize) {
                     __syncwarp();
@@ -511,8 +535,7 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
                         if (bank < prob.num_banks) {
                             float* dst = prob.output + gp * prob.out_program_stride + (size_t)q * prob.out_target_stride +
                                          ((size_t)bank << prob.toggle_bits) + perm;
-                            if (geom.use_atomics) atomicAdd(dst, tacc[e]);
-                            else *dst += tacc[e];
+                            atomicAdd(dst, tacc[e]);
                         }
                     }
                 }
@@ -702,7 +725,8 @@ Geom make_geom(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPl
     g.cst_bytes = round16(((size_t)prob.num_constants + batch.max_extra) * rc * 4 + 16);
     g.tacc_bytes = round16(((size_t)prob.num_targets + 2) * rc * 4);
     g.scratch_slot = batch.max_slots; /* one slot beyond what the programs use */
-    g.warp_bytes = g.exec_bytes + g.cst_bytes + g.tacc_bytes + ((uint32_t)batch.max_slots + 1u) * rr * rc * 128u;
+    g.hoist_bytes = round16((size_t)batch.max_hoisted * plan.tile_rows * 4);
+    g.warp_bytes = g.exec_bytes + g.cst_bytes + g.tacc_bytes + g.hoist_bytes + ((uint32_t)batch.max_slots + 1u) * rr * rc * 128u;
     g.tile_bytes = round16((size_t)ncols * plan.tile_rows * 4);
     g.rows_per_split = plan.rows_per_split;
     g.use_atomics = plan.row_splits > 1 ? 1u : 0u;
@@ -717,6 +741,8 @@ LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm
     plan.ok = false;
     plan.groups_per_item = 1;
     int variant = prob.num_banks >= 4 ? 0 : prob.num_banks >= 2 ? 1 : 2;
+    uint32_t forced_warps = 0;
+    if (forced_variant >= 0) { forced_warps = (uint32_t)forced_variant >> 8; forced_variant &= 0xff; } /* tuning hook */
     if (forced_variant >= 0 && forced_variant < kNumVariants) variant = forced_variant;
     if (prob.mode == EVAL_MATERIALIZE) variant = 2;
     plan.variant = variant;
@@ -732,7 +758,7 @@ LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm
     if (tile_rows < pass) tile_rows = pass;
     if (tile_rows > rows_padded) tile_rows = rows_padded;
 
-    for (uint32_t warps = rr * rc > 16 ? 12 : 16; warps >= 1; warps = warps == 12 ? 8 : warps / 2) {
+    for (uint32_t warps = forced_warps ? forced_warps : (rr * rc > 16 ? 12 : 16); warps >= 1; warps = (warps % 2 || warps == 12) ? (warps > 8 ? 8 : warps - 1) : warps / 2) {
         LaunchPlan trial = plan;
         trial.warps = warps;
         trial.tile_rows = (uint32_t)tile_rows;
@@ -754,32 +780,30 @@ LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm
     }
     if (!plan.ok) return plan;
 
-    /* Programs per CTA: enough CTAs to fill the machine several times over, but several
-     * programs per warp where the population allows so that a staged tile is reused. */
-    const uint32_t P = batch.num_programs;
-    const uint32_t target_ctas = (uint32_t)sm_count * 8u;
-    uint32_t ppc = (P + target_ctas - 1) / target_ctas;
-    const uint32_t min_ppc = plan.warps * 2;
-    if (ppc < min_ppc) ppc = min_ppc;
-    if (ppc > P) ppc = P;
-    const uint32_t groups = (P + ppc - 1) / ppc;
-    plan.programs_per_cta = ppc;
-    /* Queue items: a program's configuration groups are dealt out in pieces so that the
-     * warps of a CTA finish a chunk together; each piece still amortises the program copy
-     * over a few thousand row evaluations. */
+    /* Queue items: an item covers up to eight bank groups of one permutation, so the prelude of
+     * a program is amortised over them, and never straddles permutations (toggles are patched
+     * per item). */
+    unsigned long long items_per_program = 1;
     if (prob.mode != EVAL_MATERIALIZE) {
         const unsigned long long bank_groups = (prob.num_banks + rc - 1) / rc;
         const unsigned long long cfg_groups = bank_groups << prob.toggle_bits;
-        const unsigned long long passes = (plan.tile_rows + pass - 1) / pass;
-        unsigned long long gpi = (32 + passes - 1) / passes; /* at least ~32 program executions per item */
-        const unsigned long long want_items = (unsigned long long)plan.warps * 8;
-        const unsigned long long have = cfg_groups * ppc;
-        if (have / want_items > gpi) gpi = have / want_items;    /* no finer than eight items per warp */
-        if (gpi < 1) gpi = 1;
-        if (gpi > cfg_groups) gpi = cfg_groups;
-        while ((cfg_groups + gpi - 1) / gpi * ppc > 0xfffffff0ull) gpi *= 2; /* item ids are 32-bit */
-        plan.groups_per_item = (uint32_t)(gpi > 0xffffffffull ? 0xffffffffull : gpi);
+        unsigned long long gpi = bank_groups < 8 ? bank_groups : 8;
+        while (bank_groups % gpi) --gpi;
+        plan.groups_per_item = (uint32_t)gpi;
+        items_per_program = cfg_groups / gpi;
     }
+    /* Programs per CTA: enough CTAs to fill the machine several times over, and at least
+     * eight queue items per warp so that the warps of a CTA finish a chunk together. */
+    const uint32_t P = batch.num_programs;
+    const uint32_t target_ctas = (uint32_t)sm_count * 8u;
+    uint32_t ppc = (P + target_ctas - 1) / target_ctas;
+    unsigned long long min_ppc = ((unsigned long long)plan.warps * 8 + items_per_program - 1) / items_per_program;
+    if (min_ppc < 4) min_ppc = 4;
+    if (ppc < min_ppc) ppc = (uint32_t)min_ppc;
+    if (ppc > P) ppc = P;
+    while (items_per_program * ppc > 0xfffffff0ull && ppc > 1) ppc /= 2; /* item ids are 32-bit */
+    const uint32_t groups = (P + ppc - 1) / ppc;
+    plan.programs_per_cta = ppc;
     /* Too few program groups to occupy the GPU: split the rows across CTAs as well. */
     uint32_t splits = 1;
     const size_t chunks = (prob.num_rows + plan.tile_rows - 1) / plan.tile_rows;

@@ -29,6 +29,7 @@ struct DeviceBatch {
     uint32_t max_insn;    /* largest instruction count in the batch */
     uint32_t max_extra;   /* largest n_affine + n_lits */
     uint32_t max_slots;   /* largest spill-slot count */
+    uint32_t max_hoisted; /* largest number of prelude values */
 };
 
 struct EvalProblem {

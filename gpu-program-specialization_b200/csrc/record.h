@@ -23,7 +23,8 @@
 #include <stdint.h>
 
 /* Operand kinds. */
-enum { SB_KIND_ROW = 0, SB_KIND_CST = 1, SB_KIND_SLOT = 2, SB_KIND_IMM = 3, SB_NUM_KINDS = 4 };
+/* HROW: a bank-independent value computed by the program's prelude, one float per row. */
+enum { SB_KIND_ROW = 0, SB_KIND_CST = 1, SB_KIND_SLOT = 2, SB_KIND_IMM = 3, SB_KIND_HROW = 4, SB_NUM_KINDS = 5 };
 /* For FMA operand descriptors kind 3 means "the accumulator". */
 enum { SB_FMA_ACC = 3 };
 
@@ -37,7 +38,8 @@ enum {
     SB_CASE_END = 0,
     SB_CASE_LOAD = 1,                                  /* + kind           : acc = X            */
     SB_CASE_STORE = SB_CASE_LOAD + SB_NUM_KINDS,       /* slot[index] = acc                     */
-    SB_CASE_BIN = SB_CASE_STORE + 1,                   /* + op * 4 + kind  : acc = acc (op) X   */
+    SB_CASE_STOREH = SB_CASE_STORE + 1,                /* hoisted[index] = acc (row part only)  */
+    SB_CASE_BIN = SB_CASE_STOREH + 1,                  /* + op * 5 + kind  : acc = acc (op) X   */
     SB_CASE_UN = SB_CASE_BIN + SB_NUM_BIN * SB_NUM_KINDS, /* + op          : acc = f(acc)       */
     SB_CASE_FMA = SB_CASE_UN + SB_NUM_UN,              /* acc = fma(A, B, C), generic operands  */
     SB_NUM_CASES
@@ -84,6 +86,13 @@ typedef struct SbProgram {
     uint16_t n_lits;
     uint16_t n_slots;
     uint16_t n_ops; /* arithmetic nodes after routine inlining, for work accounting */
+    /* Instructions [0, main_off) form the prelude: sub-expressions that do not depend on the
+     * coefficient bank, evaluated once per row chunk and kept as per-row values (STOREH); the
+     * main part starting at main_off runs once per bank group and reads them back as HROW
+     * operands.  0 = no prelude. */
+    uint16_t main_off;
+    uint16_t n_hoisted;
+    uint32_t index;    /* position of the program in the run (output row, bank table) */
     uint32_t reserved;
 } SbProgram;
 

@@ -105,6 +105,7 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run) {
         db.max_insn = enc.max_insn;
         db.max_extra = enc.max_extra;
         db.max_slots = enc.max_slots > rules.reserved_slots ? enc.max_slots : rules.reserved_slots;
+        db.max_hoisted = 0;
         Rk4Problem p;
         p.num_systems = (uint32_t)run->num_systems; p.num_states = (uint32_t)S; p.num_constants = (uint32_t)K;
         p.num_banks = (uint32_t)run->num_banks; p.toggle_bits = run->toggle_bits;

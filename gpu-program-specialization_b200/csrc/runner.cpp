@@ -13,6 +13,7 @@
 #include "evaluator.cuh"
 #include "internal.h"
 
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <condition_variable>
@@ -114,7 +115,7 @@ struct SecantB200PopulationImpl {
     std::vector<const uint8_t*> ast_ptrs, routine_ptrs;
     SecantAstProgramSet set{};
     unsigned toggle_bits = 0;
-    struct Resident { void* device = nullptr; DeviceBatch db{}; size_t first = 0; };
+    struct Resident { void* device = nullptr; std::vector<DeviceBatch> views; size_t first = 0; };
     std::vector<Resident> batches;
     uint64_t total_ops = 0;
 };
@@ -147,8 +148,10 @@ void worker_main(SecantCubinRunnerImpl* r, size_t worker_index) {
         SecantResult status = SECANT_SUCCESS;
         slot->enc.clear();
         slot->enc.programs.reserve(count);
-        for (size_t i = 0; i < count && status == SECANT_SUCCESS; ++i)
+        for (size_t i = 0; i < count && status == SECANT_SUCCESS; ++i) {
             status = encode_program(programs->asts.items[first + i], programs->routines, arity, rules, slot->enc);
+            if (status == SECANT_SUCCESS) slot->enc.programs.back().index = (uint32_t)(first + i);
+        }
         const double spent = now_seconds() - begin;
 
         lock.lock();
@@ -263,8 +266,20 @@ SecantResult create_common(SecantCubinRunnerImpl* r, const SecantCubinRunnerOpti
 
 /* Copies an encoded batch into the slot's pinned buffer, grows the device buffer when
  * needed, and enqueues the upload.  Layout: programs | insns | patches | affines | lits. */
-SecantResult upload_batch(SecantCubinRunnerImpl* r, Slot& s, DeviceBatch* db) {
-    const EncodedBatch& e = s.enc;
+/* Programs that need more than this many spill slots are launched separately, so that the
+ * shared-memory budget of the common case (16 warps per CTA) is not sized by rare programs. */
+constexpr unsigned kLightSlots = 2;
+
+SecantResult upload_batch(SecantCubinRunnerImpl* r, Slot& s, std::vector<DeviceBatch>* views) {
+    EncodedBatch& e = s.enc;
+    /* light programs first, heavy ones after them; SbProgram::index keeps their place in the run */
+    std::stable_partition(e.programs.begin(), e.programs.end(), [](const SbProgram& p) { return p.n_slots <= kLightSlots; });
+    size_t num_light = 0;
+    unsigned light_slots = 0, heavy_slots = 0;
+    for (const auto& p : e.programs) {
+        if (p.n_slots <= kLightSlots) { ++num_light; light_slots = std::max<unsigned>(light_slots, p.n_slots); }
+        else heavy_slots = std::max<unsigned>(heavy_slots, p.n_slots);
+    }
     const size_t o_prog = 0;
     const size_t o_insn = align256(o_prog + e.programs.size() * sizeof(SbProgram));
     const size_t o_patch = align256(o_insn + e.insns.size() * sizeof(SbInsn));
@@ -292,15 +307,27 @@ SecantResult upload_batch(SecantCubinRunnerImpl* r, Slot& s, DeviceBatch* db) {
     SB_CUDA(cudaMemcpyAsync(s.device, s.pinned, total, cudaMemcpyHostToDevice, r->copy_stream), "program upload");
     SB_CUDA(cudaEventRecord(s.uploaded, r->copy_stream), "cudaEventRecord");
     const char* d = static_cast<const char*>(s.device);
-    db->programs = reinterpret_cast<const SbProgram*>(d + o_prog);
-    db->insns = reinterpret_cast<const SbInsn*>(d + o_insn);
-    db->patches = reinterpret_cast<const SbPatch*>(d + o_patch);
-    db->affines = reinterpret_cast<const SbAffine*>(d + o_aff);
-    db->lits = reinterpret_cast<const float*>(d + o_lit);
-    db->num_programs = (uint32_t)e.programs.size();
-    db->max_insn = e.max_insn;
-    db->max_extra = e.max_extra;
-    db->max_slots = e.max_slots;
+    DeviceBatch db;
+    db.insns = reinterpret_cast<const SbInsn*>(d + o_insn);
+    db.patches = reinterpret_cast<const SbPatch*>(d + o_patch);
+    db.affines = reinterpret_cast<const SbAffine*>(d + o_aff);
+    db.lits = reinterpret_cast<const float*>(d + o_lit);
+    db.max_insn = e.max_insn;
+    db.max_extra = e.max_extra;
+    db.max_hoisted = e.max_hoisted;
+    views->clear();
+    if (num_light) {
+        db.programs = reinterpret_cast<const SbProgram*>(d + o_prog);
+        db.num_programs = (uint32_t)num_light;
+        db.max_slots = light_slots;
+        views->push_back(db);
+    }
+    if (num_light < e.programs.size()) {
+        db.programs = reinterpret_cast<const SbProgram*>(d + o_prog) + num_light;
+        db.num_programs = (uint32_t)(e.programs.size() - num_light);
+        db.max_slots = heavy_slots;
+        views->push_back(db);
+    }
     return SECANT_SUCCESS;
 }
 
@@ -348,7 +375,8 @@ SecantResult launch_batch(SecantCubinRunnerImpl* r, const DeviceBatch& db, size_
     for (size_t e = 0; e < runs.size(); ++e) {
         const size_t k = (*stream_cursor)++ % r->streams.size();
         cudaStream_t stream = r->streams[k];
-        EvalProblem prob = make_problem(plan, runs[e], first_program);
+        EvalProblem prob = make_problem(plan, runs[e], 0);
+        (void)first_program; /* SbProgram::index already places every program in the run */
         if (runs[e].program_bank_stride)
             prob.banks = reinterpret_cast<const float*>(runs[e].banks.address) + runs[e].first_program_index * runs[e].program_bank_stride;
         const LaunchPlan lp = plan_launch(db, prob, r->sm_count, r->smem_limit, r->forced_variant);
@@ -437,12 +465,15 @@ SecantResult execute(SecantCubinRunnerImpl* r, const std::vector<UnpackedRun>& r
         encode_sum += slot->encode_seconds;
         result = slot->status;
         if (result != SECANT_SUCCESS) break;
-        DeviceBatch db;
+        std::vector<DeviceBatch> views;
         const double t_up = now_seconds();
-        result = upload_batch(r, *slot, &db);
+        result = upload_batch(r, *slot, &views);
         upload_seconds += now_seconds() - t_up;
         if (result != SECANT_SUCCESS) break;
-        result = launch_batch(r, db, slot->first_program, runs, &stream_cursor, slot->uploaded, &slot->done, &slot->used);
+        for (const DeviceBatch& db : views) {
+            result = launch_batch(r, db, slot->first_program, runs, &stream_cursor, slot->uploaded, &slot->done, &slot->used);
+            if (result != SECANT_SUCCESS) break;
+        }
         in_flight.push_back(slot);
         ++launched_batches;
         /* recycle the oldest batch once two are queued behind it, so workers always find a slot */
@@ -663,7 +694,10 @@ SecantResult execute_resident(SecantCubinRunnerImpl* r, SecantB200PopulationImpl
     size_t cursor = 0;
     SecantResult result = SECANT_SUCCESS;
     for (auto& b : pop->batches) {
-        result = launch_batch(r, b.db, b.first, runs, &cursor, nullptr, nullptr, nullptr);
+        for (const DeviceBatch& db : b.views) {
+            result = launch_batch(r, db, b.first, runs, &cursor, nullptr, nullptr, nullptr);
+            if (result != SECANT_SUCCESS) break;
+        }
         if (result != SECANT_SUCCESS) break;
     }
     const double t_wait = now_seconds();
@@ -709,6 +743,7 @@ SecantResult secant_b200_population_create(SecantCubinRunner r, const SecantAstP
     rules.num_constants = plan.num_constants;
     rules.banks_allowed = plan.shape == SECANT_KERNEL_SHAPE_TOGGLE_SSE_F32;
     rules.toggle_bits = rules.banks_allowed ? toggle_bits : 0;
+    rules.hoist_invariants = rules.banks_allowed; /* a population is usually scored against many banks */
     for (size_t i = 0; i < programs->routines.count; ++i) {
         const SecantResult s = preflight(programs->routines.items[i], rules);
         if (s != SECANT_SUCCESS) return s;
@@ -739,8 +774,10 @@ SecantResult secant_b200_population_create(SecantCubinRunner r, const SecantAstP
         for (size_t first = 0; first < P && result == SECANT_SUCCESS; first += batch_size) {
             const size_t count = std::min(batch_size, P - first);
             staging.enc.clear();
-            for (size_t i = 0; i < count && result == SECANT_SUCCESS; ++i)
+            for (size_t i = 0; i < count && result == SECANT_SUCCESS; ++i) {
                 result = encode_program(programs->asts.items[first + i], programs->routines, arity, rules, staging.enc);
+                if (result == SECANT_SUCCESS) staging.enc.programs.back().index = (uint32_t)(first + i);
+            }
             if (result != SECANT_SUCCESS) break;
             for (const auto& p : staging.enc.programs) pop->total_ops += p.n_ops;
             if (!staging.uploaded && cudaEventCreateWithFlags(&staging.uploaded, cudaEventDisableTiming) != cudaSuccess) {
@@ -748,7 +785,7 @@ SecantResult secant_b200_population_create(SecantCubinRunner r, const SecantAstP
                 break;
             }
             SecantB200PopulationImpl::Resident res;
-            result = upload_batch(r, staging, &res.db);
+            result = upload_batch(r, staging, &res.views);
             if (result != SECANT_SUCCESS) break;
             if (cudaStreamSynchronize(r->copy_stream) != cudaSuccess) { result = SECANT_ERROR_DRIVER_FAILED; break; }
             res.device = staging.device; /* keep this allocation; the next batch gets a new one */

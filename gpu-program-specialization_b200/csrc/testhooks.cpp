@@ -28,6 +28,8 @@ SBT_EXPORT int sbt_encode(const uint8_t* routine_blob, const uint64_t* routine_o
                           const uint8_t* ast_blob, const uint64_t* ast_off, size_t num_asts, size_t num_columns,
                           size_t num_constants, int banks_allowed, unsigned toggle_bits, int run_preflight,
                           SbtBatch** out) {
+    const bool hoist = (run_preflight & 2) != 0; /* bit 1 of the flag word asks for the prelude split */
+    run_preflight &= 1;
     std::vector<const SecantAstInstruction*> routines(num_routines), asts(num_asts);
     for (size_t i = 0; i < num_routines; ++i) routines[i] = routine_blob + routine_off[i];
     for (size_t i = 0; i < num_asts; ++i) asts[i] = ast_blob + ast_off[i];
@@ -40,6 +42,7 @@ SBT_EXPORT int sbt_encode(const uint8_t* routine_blob, const uint64_t* routine_o
     b->rules.num_constants = num_constants;
     b->rules.banks_allowed = banks_allowed != 0;
     b->rules.toggle_bits = toggle_bits;
+    b->rules.hoist_invariants = hoist;
     SecantResult r = SECANT_SUCCESS;
     if (run_preflight) {
         for (size_t i = 0; i < num_routines && r == SECANT_SUCCESS; ++i) r = preflight(routines[i], b->rules);
@@ -56,8 +59,11 @@ SBT_EXPORT void sbt_free(SbtBatch* b) { delete b; }
 
 SBT_EXPORT void sbt_info(const SbtBatch* b, size_t program, uint32_t* n_insn, uint32_t* n_slots, uint32_t* n_ops,
                          uint32_t* n_patch, uint32_t* n_affine, uint32_t* n_lits) {
+    /* with the prelude split requested, n_patch / n_affine report main_off / n_hoisted instead */
     const SbProgram& p = b->enc.programs[program];
-    *n_insn = p.n_insn; *n_slots = p.n_slots; *n_ops = p.n_ops; *n_patch = p.n_patch; *n_affine = p.n_affine; *n_lits = p.n_lits;
+    *n_insn = p.n_insn; *n_slots = p.n_slots; *n_ops = p.n_ops; *n_lits = p.n_lits;
+    *n_patch = b->rules.hoist_invariants ? p.main_off : p.n_patch;
+    *n_affine = b->rules.hoist_invariants ? p.n_hoisted : p.n_affine;
 }
 
 static float apply_bin(unsigned op, float a, float x) {
@@ -111,21 +117,39 @@ SBT_EXPORT int sbt_eval(const SbtBatch* b, size_t program, const float* input, s
     }
     for (unsigned j = 0; j < p.n_lits; ++j) cst[K + p.n_affine + j] = e.lits[p.lit_off + j];
     std::vector<float> slots(p.n_slots ? p.n_slots : 1, 0.0f);
+    std::vector<float> hoisted(p.n_hoisted ? p.n_hoisted : 1, 0.0f);
     float acc = 0.0f;
+    bool second_round = false;
     auto operand = [&](unsigned kind, unsigned index, uint32_t imm) -> float {
         switch (kind) {
         case SB_KIND_ROW: return input[(size_t)index * input_ld + row];
         case SB_KIND_CST: return cst[index];
         case SB_KIND_SLOT: return slots[index];
+        case SB_KIND_HROW: return hoisted[index];
         default: { float f; std::memcpy(&f, &imm, 4); return f; }
         }
     };
     for (size_t pc = 0; pc < code.size(); ++pc) {
         const SbInsn ins = code[pc];
         const unsigned cs = ins.w0 & 0xffu, index = ins.w0 >> 16;
-        if (cs == SB_CASE_END) { *value = acc; return SECANT_SUCCESS; }
+        if (cs == SB_CASE_END) {
+            if (pc + 1 <= p.main_off) continue; /* end of the prelude: fall through into the main part */
+            if (p.main_off && !second_round) {
+                /* The device runs the main part once per bank group after ONE prelude: do it a
+                 * second time with every spill slot poisoned, so a main part that relied on a
+                 * slot written by the prelude or by its own previous run is caught. */
+                second_round = true;
+                for (auto& v : slots) v = std::nanf("");
+                acc = std::nanf("");
+                pc = (size_t)p.main_off - 1;
+                continue;
+            }
+            *value = acc;
+            return SECANT_SUCCESS;
+        }
         if (cs >= SB_CASE_LOAD && cs < SB_CASE_LOAD + SB_NUM_KINDS) acc = operand(cs - SB_CASE_LOAD, index, ins.w1);
         else if (cs == SB_CASE_STORE) slots[index] = acc;
+        else if (cs == SB_CASE_STOREH) hoisted[index] = acc;
         else if (cs >= SB_CASE_BIN && cs < SB_CASE_UN) {
             const unsigned rel = cs - SB_CASE_BIN;
             acc = apply_bin(rel / SB_NUM_KINDS, acc, operand(rel % SB_NUM_KINDS, index, ins.w1));

@@ -11,10 +11,10 @@ import support as S
 from secant_b200 import abi, programs as P
 
 
-def encode(packed, columns, constants, banks_allowed=True, toggle_bits=0, preflight=True):
+def encode(packed, columns, constants, banks_allowed=True, toggle_bits=0, preflight=True, hoist=False):
     handle = C.c_void_p()
     code = S.hooks().sbt_encode(*S.blob_args(packed), C.c_size_t(columns), C.c_size_t(constants), int(banks_allowed),
-                                toggle_bits, int(preflight), C.byref(handle))
+                                toggle_bits, int(preflight) | (2 if hoist else 0), C.byref(handle))
     return code, handle
 
 
@@ -31,13 +31,14 @@ def same(a, b):
     return (np.isnan(a) and np.isnan(b)) or a.view(np.uint32) == b.view(np.uint32)
 
 
+@pytest.mark.parametrize("hoist", [False, True])
 @pytest.mark.parametrize("seed,max_tokens,bits", [(3, 15, 0), (4, 32, 3), (5, 48, 8)])
-def test_records_evaluate_like_the_oracle(seed, max_tokens, bits):
+def test_records_evaluate_like_the_oracle(seed, max_tokens, bits, hoist):
     pop = P.random_population(seed, 150, max_tokens, 6, 8, 2.0, toggle_bits=bits)
     n = 29
     x = np.stack([P.uniform(seed, c, n, -2, 2) for c in range(6)])
     banks = np.stack([P.normal(seed + 1, b, 8) for b in range(3)])
-    code, handle = encode(pop, 6, 8, True, bits)
+    code, handle = encode(pop, 6, 8, True, bits, hoist=hoist)  # with and without the bank-independent prelude
     assert code == 0
     configs = 3 << bits
     for cfg in sorted({0, 1, configs // 2, configs - 1}):
@@ -84,7 +85,12 @@ def test_fma_routines_and_shared_arguments():
     pop = P.PackedPrograms(progs, [sq, mix])
     x = np.stack([P.uniform(1, c, 7, 0.1, 2) for c in range(3)])
     banks = np.stack([P.normal(2, b, 2) for b in range(2)])
-    code, handle = encode(pop, 3, 2, True, 2)
+    for hoist in (False, True):
+        check_hand_written(pop, progs, x, banks, hoist)
+
+
+def check_hand_written(pop, progs, x, banks, hoist):
+    code, handle = encode(pop, 3, 2, True, 2, hoist=hoist)
     assert code == 0
     for cfg in range(8):
         _, want = S.oracle_toggle_materialize(pop, x, banks, 2, 2, cfg)
