@@ -268,14 +268,14 @@ struct Emitter {
     Operand describe(int id, bool allow_imm) {
         const Node& n = nodes[id];
         if (n.slot >= 0) return Operand{SB_KIND_SLOT, (unsigned)n.slot, 0};
-        if (n.hoisted >= 0) return Operand{SB_KIND_HROW, (unsigned)n.hoisted, 0};
+        if (n.hoisted >= 0) return Operand{SB_KIND_ROW, SB_ROW_HOISTED | (unsigned)n.hoisted, 0};
         switch (n.type) {
         case N_COL: return rules.columns_are_slots ? Operand{SB_KIND_SLOT, n.index, 0} : Operand{SB_KIND_ROW, n.index, 0};
         case N_BANK: return Operand{SB_KIND_CST, n.index, 0};
         case N_AFFINE: return Operand{SB_KIND_CST, (unsigned)rules.num_constants + n.index, 0};
         default: break;
         }
-        if (allow_imm) return Operand{SB_KIND_IMM, 0, n.bits};
+        (void)allow_imm; /* literals always live in the program's part of the constant area */
         float f;
         std::memcpy(&f, &n.bits, 4);
         size_t i = lit_base;

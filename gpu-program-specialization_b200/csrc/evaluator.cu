@@ -88,7 +88,7 @@ __device__ __noinline__ float rare_unop(unsigned op, float a) {
  * operand kinds.  Nothing here touches the register tile, which therefore stays in
  * registers. */
 template <int RR, int RC>
-__device__ __noinline__ void fma_over_scratch(uint2 ins, const float* rowp, uint32_t tile_ld, const float* cst,
+__device__ __noinline__ void fma_over_scratch(uint2 ins, const float* rowp, const float* hrowp, uint32_t tile_ld, const float* cst,
                                               float4* slots, uint32_t scratch_slot) {
     constexpr int V = RR * RC;
     const unsigned kinds = (ins.x >> 8) & 0x3fu;
@@ -101,7 +101,7 @@ __device__ __noinline__ void fma_over_scratch(uint2 ins, const float* rowp, uint
             const unsigned kind = (kinds >> (2 * i)) & 3u;
             const uint32_t index = (ins.y >> (10 * i)) & 1023u;
             const int r = k / RC, c = k % RC;
-            if (kind == SB_KIND_ROW) v[i] = rowp[(size_t)index * tile_ld + (r / 4) * 128 + (r % 4)];
+            if (kind == SB_KIND_ROW) v[i] = ((index & SB_ROW_HOISTED) ? hrowp : rowp)[(size_t)(index & 0x7fu) * tile_ld + (r / 4) * 128 + (r % 4)];
             else if (kind == SB_KIND_CST) v[i] = cst[index * RC + c];
             else {
                 const uint32_t slot = kind == SB_FMA_ACC ? scratch_slot : index;
@@ -132,8 +132,11 @@ struct Machine {
 
     float acc[RR][RC];
 
-    __device__ __forceinline__ void fetch_row(const float* rowp, uint32_t tile_ld, uint32_t col, float (&x)[RR]) const {
-        const float* q = rowp + (size_t)col * tile_ld;
+    /* one float per row: a dataset column from the staged tile, or (index bit 7) a value the
+     * prelude left in the warp's hoist buffer; both are laid out [column][row of the chunk] */
+    __device__ __forceinline__ void fetch_row(const float* rowp, const float* hrowp, uint32_t tile_ld, uint32_t col,
+                                              float (&x)[RR]) const {
+        const float* q = ((col & SB_ROW_HOISTED) ? hrowp : rowp) + (size_t)(col & 0x7fu) * tile_ld;
 #pragma unroll
         for (int g = 0; g < GROUPS; ++g) {
             const float4 v = *reinterpret_cast<const float4*>(q + g * 128);
@@ -173,7 +176,7 @@ struct Machine {
 
 #define SB_BIN_CASES(OP)                                                                             \
     case SB_CASE_BIN + OP * SB_NUM_KINDS + SB_KIND_ROW: {                                            \
-        float x[RR]; fetch_row(rowp, tile_ld, idx, x);                                               \
+        float x[RR]; fetch_row(rowp, hrowp, tile_ld, idx, x);                                               \
         SB_FOR_TILE acc[r][c] = binop<OP>(acc[r][c], x[r]);                                          \
         break; }                                                                                     \
     case SB_CASE_BIN + OP * SB_NUM_KINDS + SB_KIND_CST: {                                            \
@@ -183,14 +186,6 @@ struct Machine {
     case SB_CASE_BIN + OP * SB_NUM_KINDS + SB_KIND_SLOT: {                                           \
         float x[RR][RC]; fetch_slot(slots, idx, x);                                                  \
         SB_FOR_TILE acc[r][c] = binop<OP>(acc[r][c], x[r][c]);                                       \
-        break; }                                                                                     \
-    case SB_CASE_BIN + OP * SB_NUM_KINDS + SB_KIND_IMM: {                                            \
-        const float x = __uint_as_float(ins.y);                                                      \
-        SB_FOR_TILE acc[r][c] = binop<OP>(acc[r][c], x);                                             \
-        break; }                                                                                     \
-    case SB_CASE_BIN + OP * SB_NUM_KINDS + SB_KIND_HROW: {                                           \
-        float x[RR]; fetch_row(hrowp, tile_ld, idx, x);                                              \
-        SB_FOR_TILE acc[r][c] = binop<OP>(acc[r][c], x[r]);                                          \
         break; }
 
 #define SB_UN_CASE(OP) \
@@ -221,7 +216,7 @@ struct Machine {
             case SB_CASE_END:
                 return;
             case SB_CASE_LOAD + SB_KIND_ROW: {
-                float x[RR]; fetch_row(rowp, tile_ld, idx, x);
+                float x[RR]; fetch_row(rowp, hrowp, tile_ld, idx, x);
                 SB_FOR_TILE acc[r][c] = x[r];
                 break; }
             case SB_CASE_LOAD + SB_KIND_CST: {
@@ -231,14 +226,6 @@ struct Machine {
             case SB_CASE_LOAD + SB_KIND_SLOT:
                 fetch_slot(slots, idx, acc);
                 break;
-            case SB_CASE_LOAD + SB_KIND_IMM: {
-                const float x = __uint_as_float(ins.y);
-                SB_FOR_TILE acc[r][c] = x;
-                break; }
-            case SB_CASE_LOAD + SB_KIND_HROW: {
-                float x[RR]; fetch_row(hrowp, tile_ld, idx, x);
-                SB_FOR_TILE acc[r][c] = x[r];
-                break; }
             case SB_CASE_STORE:
                 store_slot(slots, idx);
                 break;
@@ -259,25 +246,18 @@ struct Machine {
             case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_CST:
             case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_CST:
             case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_SLOT:
-            case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_SLOT:
-            case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_IMM:
-            case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_IMM:
-            case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_HROW:
-            case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_HROW: {
+            case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_SLOT: {
                 const unsigned rel = (ins.x & 0xffu) - SB_CASE_BIN;
                 const unsigned kind = rel % SB_NUM_KINDS;
                 float xv[RR][RC];
-                if (kind == SB_KIND_ROW || kind == SB_KIND_HROW) {
-                    float x[RR]; fetch_row(kind == SB_KIND_ROW ? rowp : hrowp, tile_ld, idx, x);
+                if (kind == SB_KIND_ROW) {
+                    float x[RR]; fetch_row(rowp, hrowp, tile_ld, idx, x);
                     SB_FOR_TILE xv[r][c] = x[r];
                 } else if (kind == SB_KIND_CST) {
                     float x[RC]; fetch_cst(cst, idx, x);
                     SB_FOR_TILE xv[r][c] = x[c];
-                } else if (kind == SB_KIND_SLOT) {
-                    fetch_slot(slots, idx, xv);
                 } else {
-                    const float x = __uint_as_float(ins.y);
-                    SB_FOR_TILE xv[r][c] = x;
+                    fetch_slot(slots, idx, xv);
                 }
                 if (rel / SB_NUM_KINDS == SB_BIN_RDIV) { /* operand / acc: swap so that one body divides acc by xv */
                     SB_FOR_TILE { const float t = acc[r][c]; acc[r][c] = xv[r][c]; xv[r][c] = t; }
@@ -316,7 +296,7 @@ struct Machine {
                 break;
             case SB_CASE_FMA:
                 store_slot(slots, scratch_slot);
-                fma_over_scratch<RR, RC>(ins, rowp, tile_ld, cst, slots, scratch_slot);
+                fma_over_scratch<RR, RC>(ins, rowp, hrowp, tile_ld, cst, slots, scratch_slot);
                 fetch_slot(slots, scratch_slot, acc);
                 break;
             default:
@@ -459,7 +439,7 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
                         }
                     } else if (prob.mode == EVAL_SSE && T == 1) {
                         float t[RR];
-                        m.fetch_row(rowp, tile_ld, prob.num_inputs, t);
+                        m.fetch_row(rowp, rowp, tile_ld, prob.num_inputs, t);
                         if (full) {
 #pragma unroll
                             for (int r = 0; r < RR; ++r)
@@ -487,7 +467,7 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
                             float t[RR];
                             const bool is_target = prob.mode == EVAL_SSE || q >= 2;
                             const uint32_t tcol = prob.num_inputs + (prob.mode == EVAL_SSE ? q : q - 2);
-                            if (is_target) m.fetch_row(rowp, tile_ld, tcol, t);
+                            if (is_target) m.fetch_row(rowp, rowp, tile_ld, tcol, t);
                             float s[RC];
 #pragma unroll
                             for (int c = 0; c < RC; ++c) s[c] = 0.0f;

@@ -15,7 +15,7 @@
  *     never manipulates a stack.
  *
  * Instruction word 0:  bits 0..7 case id (SB_CASE_*), bits 8..15 aux, bits 16..31 operand index.
- * Instruction word 1:  immediate f32 bits (IMM kind) or packed FMA operand indices.
+ * Instruction word 1:  packed FMA operand indices (unused by the other instructions).
  */
 #ifndef SECANT_B200_RECORD_H
 #define SECANT_B200_RECORD_H
@@ -23,8 +23,14 @@
 #include <stdint.h>
 
 /* Operand kinds. */
-/* HROW: a bank-independent value computed by the program's prelude, one float per row. */
-enum { SB_KIND_ROW = 0, SB_KIND_CST = 1, SB_KIND_SLOT = 2, SB_KIND_IMM = 3, SB_KIND_HROW = 4, SB_NUM_KINDS = 5 };
+/* Operand kinds.  Few kinds means few interpreter cases, and the interpreter's hot code has to
+ * stay small enough for the instruction caches:
+ *   ROW   one float per row: a dataset column (index < SB_ROW_HOISTED) or a bank-independent
+ *         value left by the program's prelude (index = SB_ROW_HOISTED | n)
+ *   CST   one float per bank: a bank slot, a derived affine entry or a literal of the program
+ *   SLOT  one float per (row, bank): a spill slot */
+enum { SB_KIND_ROW = 0, SB_KIND_CST = 1, SB_KIND_SLOT = 2, SB_NUM_KINDS = 3 };
+enum { SB_ROW_HOISTED = 0x80 };
 /* For FMA operand descriptors kind 3 means "the accumulator". */
 enum { SB_FMA_ACC = 3 };
 
@@ -39,7 +45,7 @@ enum {
     SB_CASE_LOAD = 1,                                  /* + kind           : acc = X            */
     SB_CASE_STORE = SB_CASE_LOAD + SB_NUM_KINDS,       /* slot[index] = acc                     */
     SB_CASE_STOREH = SB_CASE_STORE + 1,                /* hoisted[index] = acc (row part only)  */
-    SB_CASE_BIN = SB_CASE_STOREH + 1,                  /* + op * 5 + kind  : acc = acc (op) X   */
+    SB_CASE_BIN = SB_CASE_STOREH + 1,                  /* + op * 3 + kind  : acc = acc (op) X   */
     SB_CASE_UN = SB_CASE_BIN + SB_NUM_BIN * SB_NUM_KINDS, /* + op          : acc = f(acc)       */
     SB_CASE_FMA = SB_CASE_UN + SB_NUM_UN,              /* acc = fma(A, B, C), generic operands  */
     SB_NUM_CASES
@@ -74,7 +80,7 @@ typedef struct SbAffine {
 
 /* Per-program header; offsets index the pools of the batch the program belongs to.
  * Constant-area entries are laid out [0, K) bank slots, [K, K + n_affine) derived
- * entries, [K + n_affine, K + n_affine + n_lits) literals (only FMA operands use them). */
+ * entries, [K + n_affine, K + n_affine + n_lits) the program's literals. */
 typedef struct SbProgram {
     uint32_t insn_off;
     uint32_t patch_off;

@@ -122,11 +122,9 @@ SBT_EXPORT int sbt_eval(const SbtBatch* b, size_t program, const float* input, s
     bool second_round = false;
     auto operand = [&](unsigned kind, unsigned index, uint32_t imm) -> float {
         switch (kind) {
-        case SB_KIND_ROW: return input[(size_t)index * input_ld + row];
+        case SB_KIND_ROW: return (index & SB_ROW_HOISTED) ? hoisted[index & 0x7f] : input[(size_t)index * input_ld + row];
         case SB_KIND_CST: return cst[index];
-        case SB_KIND_SLOT: return slots[index];
-        case SB_KIND_HROW: return hoisted[index];
-        default: { float f; std::memcpy(&f, &imm, 4); return f; }
+        default: (void)imm; return slots[index];
         }
     };
     for (size_t pc = 0; pc < code.size(); ++pc) {
