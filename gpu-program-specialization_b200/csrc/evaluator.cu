@@ -760,14 +760,14 @@ LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm
     }
     if (!plan.ok) return plan;
 
-    /* Queue items: an item covers up to eight bank groups of one permutation, so the prelude of
+    /* Queue items: an item covers up to sixteen bank groups of one permutation, so the prelude of
      * a program is amortised over them, and never straddles permutations (toggles are patched
      * per item). */
     unsigned long long items_per_program = 1;
     if (prob.mode != EVAL_MATERIALIZE) {
         const unsigned long long bank_groups = (prob.num_banks + rc - 1) / rc;
         const unsigned long long cfg_groups = bank_groups << prob.toggle_bits;
-        unsigned long long gpi = bank_groups < 8 ? bank_groups : 8;
+        unsigned long long gpi = bank_groups < 16 ? bank_groups : 16;
         while (bank_groups % gpi) --gpi;
         plan.groups_per_item = (uint32_t)gpi;
         items_per_program = cfg_groups / gpi;
@@ -784,12 +784,19 @@ LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm
     while (items_per_program * ppc > 0xfffffff0ull && ppc > 1) ppc /= 2; /* item ids are 32-bit */
     const uint32_t groups = (P + ppc - 1) / ppc;
     plan.programs_per_cta = ppc;
-    /* Too few program groups to occupy the GPU: split the rows across CTAs as well. */
+    /* Split the rows across CTAs as well until the grid is many waves deep: a CTA that walks
+     * every row of a large dataset runs for seconds, and the last partial wave of such CTAs
+     * leaves most of the GPU idle.  Sums are combined with atomic adds either way.  A split
+     * keeps at least eight chunks unless the program groups alone cannot fill the GPU. */
     uint32_t splits = 1;
     const size_t chunks = (prob.num_rows + plan.tile_rows - 1) / plan.tile_rows;
-    if (groups < (uint32_t)sm_count && prob.mode != EVAL_MATERIALIZE) {
-        splits = ((uint32_t)sm_count * 2 + groups - 1) / groups;
-        if (splits > chunks) splits = (uint32_t)chunks;
+    if (prob.mode != EVAL_MATERIALIZE) {
+        const uint32_t want_ctas = (uint32_t)sm_count * 32u;
+        size_t most = groups < (uint32_t)sm_count * 2u ? chunks : chunks / 8;
+        const size_t fill = ((size_t)sm_count * 2 + groups - 1) / groups; /* splits that fill the GPU twice */
+        if (most < fill) most = fill < chunks ? fill : chunks;
+        splits = (want_ctas + groups - 1) / groups;
+        if (splits > most) splits = (uint32_t)most;
         if (splits < 1) splits = 1;
     }
     const size_t chunks_per_split = (chunks + splits - 1) / splits;

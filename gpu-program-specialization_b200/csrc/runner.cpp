@@ -274,6 +274,12 @@ SecantResult upload_batch(SecantCubinRunnerImpl* r, Slot& s, std::vector<DeviceB
     EncodedBatch& e = s.enc;
     /* light programs first, heavy ones after them; SbProgram::index keeps their place in the run */
     std::stable_partition(e.programs.begin(), e.programs.end(), [](const SbProgram& p) { return p.n_slots <= kLightSlots; });
+    /* inside each group, costly programs first: CTAs then start with the long work and the
+     * items dealt round-robin to the warp teams of a CTA are of similar cost */
+    const auto light_end = std::find_if(e.programs.begin(), e.programs.end(), [](const SbProgram& p) { return p.n_slots > kLightSlots; });
+    const auto by_cost = [](const SbProgram& a, const SbProgram& b) { return a.n_insn > b.n_insn; };
+    std::stable_sort(e.programs.begin(), light_end, by_cost);
+    std::stable_sort(light_end, e.programs.end(), by_cost);
     size_t num_light = 0;
     unsigned light_slots = 0, heavy_slots = 0;
     for (const auto& p : e.programs) {

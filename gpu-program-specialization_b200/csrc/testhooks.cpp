@@ -66,6 +66,18 @@ SBT_EXPORT void sbt_info(const SbtBatch* b, size_t program, uint32_t* n_insn, ui
     *n_affine = b->rules.hoist_invariants ? p.n_hoisted : p.n_affine;
 }
 
+/* Instruction counts by case id over all programs: prelude[SB_NUM_CASES] for the
+ * bank-independent part, main[SB_NUM_CASES] for the part repeated per bank group. */
+SBT_EXPORT unsigned sbt_case_histogram(const SbtBatch* b, uint64_t* prelude, uint64_t* main_part) {
+    for (unsigned c = 0; c < SB_NUM_CASES; ++c) prelude[c] = main_part[c] = 0;
+    for (const SbProgram& p : b->enc.programs)
+        for (unsigned i = 0; i < p.n_insn; ++i) {
+            const unsigned c = b->enc.insns[p.insn_off + i].w0 & 0xffu;
+            if (c < SB_NUM_CASES) (i < p.main_off ? prelude : main_part)[c]++;
+        }
+    return SB_NUM_CASES;
+}
+
 static float apply_bin(unsigned op, float a, float x) {
     switch (op) {
     case SB_BIN_ADD: return a + x;
