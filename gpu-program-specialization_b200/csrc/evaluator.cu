@@ -46,7 +46,6 @@ struct Geom {
     uint32_t warp_bytes;
     uint32_t tile_bytes;
     unsigned long long rows_per_split;
-    uint32_t use_atomics;
     uint32_t groups_per_item; /* configuration groups one queue item covers */
     uint32_t scratch_slot;    /* spill slot reserved for the out-of-line unary functions */
 };
@@ -709,7 +708,6 @@ Geom make_geom(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPl
     g.warp_bytes = g.exec_bytes + g.cst_bytes + g.tacc_bytes + g.hoist_bytes + ((uint32_t)batch.max_slots + 1u) * rr * rc * 128u;
     g.tile_bytes = round16((size_t)ncols * plan.tile_rows * 4);
     g.rows_per_split = plan.rows_per_split;
-    g.use_atomics = plan.row_splits > 1 ? 1u : 0u;
     g.groups_per_item = plan.groups_per_item ? plan.groups_per_item : 1u;
     return g;
 }

@@ -227,3 +227,54 @@ def test_size_independent_properties_at_a_million_rows(cuda):
     assert got[0, 0].tolist() == [0.0] * 4
     assert got[1, 0].tolist() == [float(rows)] * 4
     assert got[2, 0].tolist() == [0.0, float(rows), 4.0 * rows, 0.25 * rows]
+
+
+def _ulps(got, exact64):
+    """Error of float32 results in units of the last place of the correctly rounded answer."""
+    with np.errstate(all="ignore"):
+        ref = exact64.astype(np.float32)
+        ulp = np.spacing(np.abs(ref)).astype(np.float64)
+        err = np.abs(got.astype(np.float64) - exact64) / ulp
+    same_special = (np.isnan(got) & np.isnan(ref)) | (np.isinf(ref) & (got == ref)) | ((ref == 0) & (got == 0))
+    return np.where(same_special, 0.0, err)
+
+
+def test_device_functions_against_float64(cuda):
+    """Every unary operation and the division on arguments from tiny to huge, with the special
+    values: arithmetic is correctly rounded, transcendentals stay within 2-3 ulp of float64,
+    and NaN / infinity appear exactly where the host functions produce them."""
+    words = P._stream(77, 0, 1 << 16)
+    mags = np.float32(10.0) ** (P.uniform(77, 1, 1 << 16, -6, 6))
+    signs = np.where(words & 1, np.float32(1), np.float32(-1))
+    x = (mags * signs).astype(np.float32)
+    x[:24] = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1.0, -1.0, 88.0, 88.72, 88.73, 89.5, -87.0, -88.0, -103.0,
+                       -104.5, 1e-40, -1e-40, 3.4e38, 4095.9, 4096.0, 1e30, 86.0, 86.00001, 127.5], dtype=np.float32)
+    x[24:4096] = P.uniform(77, 2, 4072, -100, 100)       # the range exp and trig arguments usually live in
+    x[4096:6144] = (np.arange(2048, dtype=np.float64) * np.pi / 2).astype(np.float32)   # zeros of sin and cos
+    y = np.roll(x, 7919).copy()
+    unary = [("NEG", lambda a: -a, 0.0), ("ABS", np.abs, 0.0), ("SQRT", np.sqrt, 0.5), ("RCP", lambda a: 1.0 / a, 0.5),
+             ("RSQRT", lambda a: 1.0 / np.sqrt(a), 2.0), ("SIN", np.sin, 2.0), ("COS", np.cos, 2.0),
+             ("EXP", np.exp, 2.5), ("LOG", np.log, 2.0), ("EX2", np.exp2, 2.5), ("LG2", np.log2, 2.0), ("TANH", np.tanh, 2.5)]
+    asts = [P.col(0) + P.op(name) + P.RET for name, _, _ in unary]
+    asts.append(P.col(0) + P.col(1) + P.op("DIV") + P.RET)
+    asts.append(P.col(1) + P.col(0) + P.col(0) + P.op("MUL") + P.op("DIV") + P.RET)   # operand on the left of a computed value
+    pop = P.PackedPrograms(asts)
+    with Runner(abi.SHAPE_MATERIALIZE, 2) as rn:
+        got = rn.materialize(pop, dev(np.stack([x, y]))).cpu().numpy()
+    x64, y64 = x.astype(np.float64), y.astype(np.float64)
+    with np.errstate(all="ignore"):
+        for i, (name, fn, bound) in enumerate(unary):
+            exact = fn(x64)
+            err = _ulps(got[i], exact)
+            if name in ("EXP", "EX2"):    # results in the denormal range are rounded twice
+                err = np.where(np.abs(exact) < 1.2e-38, np.minimum(err, bound), err)
+            assert np.nanmax(err) <= bound + 0.5 * (bound > 0), (name, float(np.nanmax(err)), float(x[np.nanargmax(err)]))
+            want = exact.astype(np.float32)
+            assert np.array_equal(np.isnan(got[i]), np.isnan(want)), name
+            assert np.array_equal(np.isinf(got[i]), np.isinf(want)), name
+        assert np.array_equal(got[len(unary)].view(np.uint32)[~np.isnan(got[len(unary)])],
+                              (x / y).view(np.uint32)[~np.isnan(x / y)])             # IEEE division, bit for bit
+        assert np.array_equal(np.isnan(got[len(unary)]), np.isnan(x / y))
+        xx = x * x
+        want = y / xx
+        assert np.array_equal(got[len(unary) + 1].view(np.uint32)[~np.isnan(want)], want.view(np.uint32)[~np.isnan(want)])
