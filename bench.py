@@ -192,6 +192,67 @@ def reference_arm(args, w):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------ comparator arm ----
+
+def comparator_arm(args, w):
+    """`--impl comparator`: the reference's kernel design with compiler-written program bodies
+    (secant_b200/comparator.py) against this library's evaluator, on the same sample of the
+    workload with one shared coefficient table (the reference's bank semantics).  Compile time
+    is reported beside the kernel time; it is what the reference's machine-code patching and
+    this library's record interpreter both exist to avoid."""
+    import torch
+    from secant_b200 import comparator as K
+    from secant_b200.runner import Runner
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device")
+    dev = torch.device("cuda", 0)
+    count = min(w["programs"], 512)
+    NB, Kc, F, N = w["banks"], w["slots"], w["features"], w["rows"]
+    w = dict(w, programs=count)
+    pop, x_h, y_h, banks_h = make_workload(w, 0)
+    x, y, banks = (torch.from_numpy(a).to(dev) for a in (x_h, y_h, np.ascontiguousarray(banks_h[0])))
+    row_evals = float(count) * NB * N
+    out = torch.empty((count, 1, NB), device=dev)
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+    result = {"impl": "comparator", "metric": "row-evals/s", "unit": "row-evals/s", "n_gpus": 1, "data": "synthetic",
+              "config": {"workload": w["name"] + f" (sample: {count} programs, shared coefficient table)", "rows": N,
+                         "coefficient_sets": NB, "recipe": "8 kernels x 8 programs per module, tile 128 rows, 128 threads"}}
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for mode, fast in (("fast_math", True), ("accurate", False)):
+        compiled = K.CompiledPopulation(pop, F, Kc, 1, fast_math=fast)
+        times = []
+        for it in range(args.warmup + args.steps):
+            out.zero_()
+            flush.fill_(1)
+            start.record()
+            launches = compiled.score(x, y, banks, NB, 0, out)
+            stop.record()
+            stop.synchronize()
+            if it >= args.warmup:
+                times.append(start.elapsed_time(stop) * 1e-3)
+        seconds = sum(times) / len(times)
+        result[mode] = {"row_evals_per_s": row_evals / seconds, "kernel_ms": seconds * 1e3, "launches": launches,
+                        "compile_s": compiled.compile_seconds, "module_load_s": compiled.load_seconds,
+                        "compile_ms_per_program": compiled.compile_seconds * 1e3 / count,
+                        "finite_fraction": float(torch.isfinite(out).float().mean().item())}
+        compiled.close()
+    with Runner(abi.SHAPE_TOGGLE_SSE, F, 1, Kc, workers=4, streams=2) as runner:
+        req = runner.toggle_request(pop, x, y, banks, NB, 0, out)
+        times = []
+        for it in range(args.warmup + args.steps):
+            flush.fill_(1)
+            runner.run(req)                      # encodes and uploads the programs every time
+            if it >= args.warmup:
+                times.append((runner.stats.runtime_seconds, runner.stats.compile_work_seconds, runner.stats.total_seconds))
+        kernel = sum(t[0] for t in times) / len(times)
+        result["this_library"] = {"row_evals_per_s": row_evals / kernel, "kernel_ms": kernel * 1e3,
+                                  "encode_ms_per_program": 1e3 * sum(t[1] for t in times) / len(times) / count,
+                                  "call_ms": 1e3 * sum(t[2] for t in times) / len(times),
+                                  "finite_fraction": float(torch.isfinite(out).float().mean().item())}
+    result["value"] = result["fast_math"]["row_evals_per_s"]
+    print(json.dumps(result))
+
+
 # ------------------------------------------------------------------------- GPU arm ----
 
 def gpu_arm(args, w):
@@ -326,7 +387,9 @@ def gpu_arm(args, w):
             "roofline": {"bound": "fp32", "achieved": achieved / 1e12, "peak": peak.value / 1e12, "unit": "TFLOP/s",
                          "frac": achieved / peak.value, "traffic": None,
                          "note": "achieved = sum over programs of (ops + 2) x sets x rows / kernel time, one per "
-                                 "algorithmic operation; peak = FFMA lane-instructions/s probed on this device in this run"},
+                                 "algorithmic operation; peak = FFMA lane-instructions/s probed on this device in this "
+                                 "run; DRAM traffic needs a multi-pass capture: measured on a reduced case only "
+                                 "(18.8 MB per launch against 17.8 MB algorithmic) and not proportional to the unit count"},
             "cpu_baseline": cpu,
             "top1024_head": [int(i) for i in top[:4].tolist()],
         }
@@ -343,7 +406,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "comparator"])
     ap.add_argument("--programs", type=int, default=None, help="development only: shrink the population")
     ap.add_argument("--rows", type=int, default=None, help="development only: shrink the dataset")
     args = ap.parse_args()
@@ -357,6 +420,8 @@ def main():
     args.warmup = max(args.warmup, 0)
     if args.impl == "reference":
         reference_arm(args, w)
+    elif args.impl == "comparator":
+        comparator_arm(args, w)
     else:
         gpu_arm(args, w)
 

@@ -8,8 +8,8 @@
  * that one warp interprets:
  *
  *   - every thread owns a register tile acc[rows][banks];
- *   - an instruction combines acc with ONE operand X (a dataset column of the staged
- *     row tile, an entry of the per-warp constant area, a spill slot, or an immediate),
+ *   - an instruction combines acc with ONE operand X (a per-row value, an entry of the
+ *     per-warp constant area, or a spill slot),
  *     or applies a unary function to acc, or stores acc into a spill slot;
  *   - spill slots and the order of evaluation are fixed by the encoder, so the device
  *     never manipulates a stack.
@@ -22,7 +22,6 @@
 
 #include <stdint.h>
 
-/* Operand kinds. */
 /* Operand kinds.  Few kinds means few interpreter cases, and the interpreter's hot code has to
  * stay small enough for the instruction caches:
  *   ROW   one float per row: a dataset column (index < SB_ROW_HOISTED) or a bank-independent
@@ -94,8 +93,8 @@ typedef struct SbProgram {
     uint16_t n_ops; /* arithmetic nodes after routine inlining, for work accounting */
     /* Instructions [0, main_off) form the prelude: sub-expressions that do not depend on the
      * coefficient bank, evaluated once per row chunk and kept as per-row values (STOREH); the
-     * main part starting at main_off runs once per bank group and reads them back as HROW
-     * operands.  0 = no prelude. */
+     * main part starting at main_off runs once per bank group and reads them back as ROW
+     * operands with SB_ROW_HOISTED set.  0 = no prelude. */
     uint16_t main_off;
     uint16_t n_hoisted;
     uint32_t index;    /* position of the program in the run (output row, bank table) */

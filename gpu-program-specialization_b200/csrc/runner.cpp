@@ -536,8 +536,14 @@ SecantResult execute(SecantCubinRunnerImpl* r, const std::vector<UnpackedRun>& r
         for (double w : r->worker_seconds) critical = w > critical ? w : critical;
         stats->compile_critical_seconds = critical;
     }
-    stats->num_modules = launched_batches;
-    stats->modules_loaded = launched_batches;
+    /* module counts in the reference's unit, a recipe-capacity worth of programs (callers such as
+     * projects/secant/tests/toggle_cuda_test.c:245 check them); batches here are much larger */
+    {
+        const size_t capacity = std::max<size_t>(1, r->plan->num_kernels * r->plan->asts_per_kernel);
+        const size_t launched_programs = std::min<size_t>(P, launched_batches * batch_size);
+        stats->num_modules = (P + capacity - 1) / capacity;
+        stats->modules_loaded = (launched_programs + capacity - 1) / capacity;
+    }
     stats->num_asts = P;
     stats->compile_work_seconds = encode_sum;
     stats->compile_window_seconds = now_seconds() - t_begin - wait_seconds;
@@ -718,7 +724,10 @@ SecantResult execute_resident(SecantCubinRunnerImpl* r, SecantB200PopulationImpl
     if (ce == cudaSuccess) ce = cudaEventElapsedTime(&ms, r->ev_start, r->ev_stop);
     stats->completion_wait_seconds = now_seconds() - t_wait;
     stats->runtime_seconds = ms * 1e-3;
-    stats->num_modules = stats->modules_loaded = pop->batches.size();
+    {
+        const size_t capacity = std::max<size_t>(1, r->plan->num_kernels * r->plan->asts_per_kernel);
+        stats->num_modules = stats->modules_loaded = (pop->set.asts.count + capacity - 1) / capacity;
+    }
     stats->num_asts = pop->set.asts.count;
     if (ce != cudaSuccess) {
         cuda_fail(r, ce, "completion");

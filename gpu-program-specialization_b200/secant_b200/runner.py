@@ -20,10 +20,10 @@ _SHAPE_RECIPE = {
 }
 
 
-def make_recipe(shape, num_inputs, num_targets=1, num_constants=0):
+def make_recipe(shape, num_inputs, num_targets=1, num_constants=0, num_kernels=8, asts_per_kernel=None):
     r = abi.init_header(_SHAPE_RECIPE[shape](), abi.RECIPE_VERSION, shape)
-    r.num_kernels = 8
-    r.asts_per_kernel = 8 if shape == abi.SHAPE_TOGGLE_SSE else 4
+    r.num_kernels = num_kernels
+    r.asts_per_kernel = asts_per_kernel or (8 if shape == abi.SHAPE_TOGGLE_SSE else 4)
     r.num_inputs = num_inputs
     r.patch_capacity_instructions = 2048
     if shape != abi.SHAPE_MATERIALIZE:
@@ -47,7 +47,8 @@ def _matrix(t, leading_dimension=None):
 class Runner:
     """One runner handle for one kernel shape, bound to torch's current CUDA context."""
 
-    def __init__(self, shape, num_inputs, num_targets=1, num_constants=0, workers=1, streams=1, via_plan=False):
+    def __init__(self, shape, num_inputs, num_targets=1, num_constants=0, workers=1, streams=1, via_plan=False,
+                 num_kernels=8, asts_per_kernel=None):
         if not torch.cuda.is_available():
             raise RuntimeError("a CUDA device is required: this library has no CPU fallback")
         torch.cuda.init()
@@ -55,7 +56,7 @@ class Runner:
         self.lib = abi.load()
         self.shape = shape
         self.num_inputs, self.num_targets, self.num_constants = num_inputs, num_targets, num_constants
-        self.recipe = make_recipe(shape, num_inputs, num_targets, num_constants)
+        self.recipe = make_recipe(shape, num_inputs, num_targets, num_constants, num_kernels, asts_per_kernel)
         self.handle = C.c_void_p()
         options = abi.runner_options(workers, streams)
         if via_plan:

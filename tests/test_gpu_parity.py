@@ -27,10 +27,13 @@ def dev(a):
     return torch.tensor(np.ascontiguousarray(a), device="cuda")
 
 
-def test_fixture_closed_forms_padding_and_changed_banks(cuda):
+@pytest.mark.parametrize("packed_asts", [1, 3])
+def test_fixture_closed_forms_padding_and_changed_banks(cuda, packed_asts):
+    """projects/secant/tests/toggle_cuda_test.c:166-256 with its two recipes (3 kernels of 1 or 3 programs)."""
     fx = packed("fixture")
     x, y, banks = G["fixture_x"], G["fixture_y"], G["fixture_banks"]
-    with Runner(abi.SHAPE_TOGGLE_SSE, 3, 2, 2, workers=3, streams=2, via_plan=True) as rn:
+    with Runner(abi.SHAPE_TOGGLE_SSE, 3, 2, 2, workers=3, streams=2, via_plan=True, num_kernels=3,
+                asts_per_kernel=packed_asts) as rn:
         for pass_idx in range(2):
             b = banks if pass_idx == 0 else (banks + np.float32(0.137)).astype(np.float32)
             out = torch.full((7, 2, 109), -123.0, device="cuda")
@@ -45,7 +48,9 @@ def test_fixture_closed_forms_padding_and_changed_banks(cuda):
                         e = np.array([toggle_expected(a, p, x[:, r], b[bank]) for r in range(17)], dtype=np.float64)
                         ref = ((e - y[1].astype(np.float64)) ** 2).sum()
                         assert abs(got[a, 1, bank * 8 + p] - ref) <= 1e-5 * (1 + abs(ref))
-        assert rn.stats.num_asts == 7 and rn.stats.num_modules == 1 and rn.stats.runtime_seconds > 0
+        # module counts come in the reference's unit: programs per recipe capacity (toggle_cuda_test.c:245)
+        assert rn.stats.modules_loaded == (7 + 3 * packed_asts - 1) // (3 * packed_asts) == rn.stats.num_modules
+        assert rn.stats.num_asts == 7 and rn.stats.runtime_seconds > 0
 
 
 def test_affine_leaf_exact_values(cuda):
