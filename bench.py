@@ -192,6 +192,67 @@ def reference_arm(args, w):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------------ RK4 arm ----
+
+def rk4_arm(args, w):
+    """`--impl rk4`: the rollout-scoring variant at BASELINE configs[3] (16,384 candidate systems of
+    3 right-hand sides with at most 24 tokens over 3 states and 8 coefficients, 64 initial
+    conditions, 1,000 fixed RK4 steps scored at every step).  Reference trajectories come from
+    the same integrator run on the Lorenz system; programs are seeded random stand-ins."""
+    import torch
+    from secant_b200.runner import rk4_score
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device")
+    dev = torch.device("cuda", 0)
+    systems, S, ics, steps, K = (args.programs or 16384), 3, 64, 1000, 8
+    pop = P.random_population(4, systems * S, 24, S, K, 1.0)
+    ops = P.count_ops(pop).reshape(systems, S).sum(axis=1)
+    rng = np.random.Generator(np.random.Philox(key=4))
+    coeffs = rng.standard_normal((systems, 1, K), dtype=np.float32)
+    h = np.float32(0.01)
+    state = rng.uniform(-10, 10, size=(3, ics)).astype(np.float32)
+    ref = np.empty((3, ics, steps + 1), dtype=np.float32)
+    ref[:, :, 0] = state
+
+    def rhs(v):
+        return np.stack([(v[1] - v[0]) * np.float32(10.0), v[0] * (np.float32(28.0) - v[2]) - v[1],
+                         v[0] * v[1] - np.float32(8.0 / 3.0) * v[2]]).astype(np.float32)
+    for k in range(1, steps + 1):
+        k1 = rhs(state); k2 = rhs(state + h / 2 * k1); k3 = rhs(state + h / 2 * k2); k4 = rhs(state + h * k3)
+        state = (state + h / 6 * (k1 + 2 * k2 + 2 * k3 + k4)).astype(np.float32)
+        ref[:, :, k] = state
+    times = (np.arange(steps + 1, dtype=np.float32) * h).astype(np.float32)
+    ref_d = torch.from_numpy(ref.reshape(3, ics * (steps + 1))).to(dev)
+    times_d, coeffs_d = torch.from_numpy(times).to(dev), torch.from_numpy(coeffs).to(dev)
+    lib = abi.load()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    seconds = []
+    for it in range(args.warmup + args.steps):
+        launches0 = lib.secant_b200_kernel_launch_count()
+        start.record()
+        scores = rk4_score(pop, S, ref_d, times_d, coeffs_d, K)     # encodes, uploads, integrates, blocks
+        stop.record()
+        stop.synchronize()
+        if it >= args.warmup:
+            seconds.append(start.elapsed_time(stop) * 1e-3)
+    dt = sum(seconds) / len(seconds)
+    stage_evals = float(systems) * ics * steps * 4
+    lane_ops = float((4 * ops + 4 * 2 * S + S + 2 * S).sum()) * ics * steps      # per (system, IC, step)
+    peak = C.c_double()
+    abi.check(lib.secant_b200_fp32_peak_probe(0.5, C.byref(peak)), "fp32 peak probe")
+    valid = float((scores < 3.0e38).float().mean().item())
+    print(json.dumps({"impl": "rk4", "metric": "system-stage evaluations/sec", "value": stage_evals / dt, "unit": "system-stages/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+                      "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "configs[3] RK4 rollout scoring", "systems": systems, "states": S, "coefficients": K,
+                                 "initial_conditions": ics, "rk4_steps": steps, "max_tokens_per_state": 24,
+                                 "mean_ops_per_system": float(ops.mean()), "valid_fraction": valid,
+                                 "timed": "secant_b200_rk4_score with host programs: encoding, upload and kernel"},
+                      "gpu_launches": int(lib.secant_b200_kernel_launch_count() - launches0),
+                      "roofline": {"bound": "fp32", "achieved": lane_ops / dt / 1e12, "peak": peak.value / 1e12, "unit": "TFLOP/s",
+                                   "frac": lane_ops / dt / peak.value, "traffic": None}}))
+
+
 # ------------------------------------------------------------------ comparator arm ----
 
 def comparator_arm(args, w):
@@ -406,7 +467,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "comparator"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "comparator", "rk4"])
     ap.add_argument("--programs", type=int, default=None, help="development only: shrink the population")
     ap.add_argument("--rows", type=int, default=None, help="development only: shrink the dataset")
     args = ap.parse_args()
@@ -422,6 +483,8 @@ def main():
         reference_arm(args, w)
     elif args.impl == "comparator":
         comparator_arm(args, w)
+    elif args.impl == "rk4":
+        rk4_arm(args, w)
     else:
         gpu_arm(args, w)
 

@@ -11,6 +11,11 @@
 #include <stdint.h>
 
 namespace sb {
+/* adds to the process-wide count reported by secant_b200_kernel_launch_count() */
+void note_kernel_launches(unsigned n);
+}
+
+namespace sb {
 
 enum EvalMode : int {
     EVAL_SSE = 0,          /* sum over rows of (prediction - target)^2 per (program, target, configuration) */

@@ -14,6 +14,7 @@
  *     written for any k up to 2048.
  */
 #include "../../include/secant_b200.h"
+#include "evaluator.cuh"
 
 #include <cuda_runtime.h>
 #include <math_constants.h>
@@ -148,14 +149,17 @@ static cudaError_t topk_rounds(const float* scores, unsigned long long count, un
     unsigned long long* cur = scratch;
     unsigned long long* nxt = scratch + tiles * k;
     topk_first_kernel<<<(unsigned)tiles, kSortThreads, 0, stream>>>(scores, count, k, cur);
+    unsigned launched = 2; /* first + emit */
     unsigned long long have = (unsigned long long)tiles * k;
     while (tiles > 1) {
         tiles = tiles_of(have);
         topk_merge_kernel<<<(unsigned)tiles, kSortThreads, 0, stream>>>(cur, have, k, nxt);
+        ++launched;
         have = (unsigned long long)tiles * k;
         unsigned long long* t = cur; cur = nxt; nxt = t;
     }
     topk_emit_kernel<<<(k + 255) / 256, 256, 0, stream>>>(cur, scores, count, k, indices, values);
+    sb::note_kernel_launches(launched);
     return cudaGetLastError();
 }
 
@@ -173,6 +177,7 @@ SecantResult secant_b200_best_config(uintptr_t scores, size_t num_vectors, size_
         return SECANT_ERROR_INVALID_VALUE;
     best_config_kernel<<<(unsigned)num_vectors, kBestThreads, 0, (cudaStream_t)stream>>>(
         reinterpret_cast<const float*>(scores), num_configurations, leading_dimension, reinterpret_cast<SecantB200Score*>(best_out));
+    sb::note_kernel_launches(1);
     return cudaGetLastError() == cudaSuccess ? SECANT_SUCCESS : SECANT_ERROR_DRIVER_FAILED;
 }
 

@@ -120,6 +120,7 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run) {
         p.output = reinterpret_cast<float*>(run->output.address);
         p.output_ld = run->output.leading_dimension;
         e = launch_rk4(db, p, (size_t)limit, nullptr);
+        if (e == cudaSuccess) note_kernel_launches(1);
         if (e == cudaErrorInvalidConfiguration) { cudaFree(d); return SECANT_ERROR_REGISTER_OVERFLOW; }
         if (e == cudaSuccess) e = cudaDeviceSynchronize();
     }

@@ -27,6 +27,7 @@
 namespace sb {
 
 std::atomic<uint64_t> g_kernel_launches{0};
+void note_kernel_launches(unsigned n) { g_kernel_launches.fetch_add(n); }
 
 namespace {
 
