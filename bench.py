@@ -20,7 +20,7 @@ The line printed by rank 0:
   e2e         the same metric through the reference-facing call secant_cubin_runner_run with
               host programs, including host->device copies of data, banks and programs and
               the device->host copy of all scores, every step
-  roofline    FP32-pipe roofline of the evaluator kernel (see DESIGN.md): algorithmic
+  roofline    FP32-pipe roofline of the evaluator kernel: algorithmic
               lane-operations per second over the probed FFMA rate of this device
   cpu_baseline the CPU evaluator timed on this box's cores on a bounded sample
 """
@@ -428,6 +428,9 @@ def gpu_arm(args, w):
             rate, kind, dt, sample = cpu_throughput(w, per_thread, 4096, threads)
             cpu = {"value": rate, "unit": "program-rows/s", "cores": threads, "kind": kind,
                    "sample": f"{sample}, {dt:.1f} s on {threads} host threads"}
+            # the evaluator as shipped is single-threaded: one thread on a slice of the same sample
+            one, _, dt1, sample1 = cpu_throughput(w, max(1, per_thread // 4), 4096, 1)
+            cpu["one_thread"] = {"value": one, "sample": f"{sample1}, {dt1:.1f} s"}
         total_program_rows = float(Pn) * N * world
         line = {
             "metric": METRIC, "value": total_program_rows / step_wall, "unit": "program-rows/s", "n_gpus": world,

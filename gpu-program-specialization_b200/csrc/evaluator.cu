@@ -534,10 +534,12 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
  * Mapping (different from the reference, which gives a thread one configuration and loops all
  * trajectories inside it): one warp per (system, configuration), lanes = trajectories, four
  * per lane.  The integrator's vectors live in the warp's spill slots: slot s = stage state s
- * (what COLUMN s of a right-hand side reads), then next-stage, base, sum and state vectors. */
-constexpr int kRk4Warps = 8;
+ * (what COLUMN s of a right-hand side reads), then next-stage, sum and state vectors (the state
+ * is not touched during a step, so it doubles as the step's base).  Warps per CTA are chosen at
+ * launch so that as many warps as possible fit the SM's shared memory. */
+constexpr int kRk4MaxWarps = 16;
 
-__global__ void __launch_bounds__(kRk4Warps * 32)
+__global__ void __launch_bounds__(kRk4MaxWarps * 32, 2)
 rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, uint32_t cst_bytes, uint32_t warp_bytes,
            uint32_t scratch_slot) {
     using M = Machine<4, 1>;
@@ -547,7 +549,7 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, 
     unsigned char* const warea = smem + (size_t)warp * warp_bytes;
     float4* const slots = reinterpret_cast<float4*>(warea + (size_t)S * (exec_bytes + cst_bytes)) + lane;
     const unsigned long long configs = (unsigned long long)prob.num_banks << prob.toggle_bits;
-    const unsigned long long item = (unsigned long long)blockIdx.x * kRk4Warps + warp;
+    const unsigned long long item = (unsigned long long)blockIdx.x * (blockDim.x >> 5) + warp;
     if (item >= configs * prob.num_systems) return;
     const uint32_t sys = (uint32_t)(item / configs);
     const unsigned long long cfg = item % configs;
@@ -580,7 +582,7 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, 
     }
     __syncwarp();
 
-    const uint32_t STAGE = 0, NEXT = S, BASE = 2 * S, SUM = 3 * S, STATE = 4 * S;
+    const uint32_t STAGE = 0, NEXT = S, SUM = 2 * S, STATE = 3 * S, BASE = STATE;
     const uint32_t points = prob.points_per_trajectory;
     M m;
     float sq = 0.0f;
@@ -611,7 +613,6 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, 
             for (uint32_t sub = 0; sub < prob.substeps; ++sub) {
                 for (uint32_t s = 0; s < S; ++s) {
                     m.fetch_slot(slots, STATE + s, m.acc);
-                    m.store_slot(slots, BASE + s);
                     m.store_slot(slots, STAGE + s);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) m.acc[q][0] = 0.0f;
@@ -837,14 +838,24 @@ cudaError_t launch_rk4(const DeviceBatch& batch, const Rk4Problem& prob, size_t 
     const uint32_t cst_bytes = round16(((size_t)prob.num_constants + batch.max_extra) * 4 + 16);
     const uint32_t scratch_slot = batch.max_slots; /* max_slots already includes the integrator's reserved slots */
     const uint32_t warp_bytes = prob.num_states * (exec_bytes + cst_bytes) + (batch.max_slots + 1u) * 4u * 128u;
-    const size_t smem = (size_t)warp_bytes * kRk4Warps;
-    if (smem > smem_limit) return cudaErrorInvalidConfiguration;
+    /* warps per CTA: the count that puts most warps on an SM (shared memory per SM is the CTA
+     * limit plus 1 KB reserved per resident CTA; 64 registers per thread allow 32 warps) */
+    int warps = 0, best = 0;
+    for (int w = 2; w <= kRk4MaxWarps; ++w) {
+        const size_t cta = (size_t)warp_bytes * w;
+        if (cta > smem_limit) break;
+        int ctas = (int)((smem_limit + 1024) / (cta + 1024));
+        if (ctas * w > 32) ctas = 32 / w;
+        if (ctas * w >= best) { best = ctas * w; warps = w; }
+    }
+    if (!warps) return cudaErrorInvalidConfiguration;
+    const size_t smem = (size_t)warp_bytes * warps;
     cudaError_t e = cudaFuncSetAttribute(rk4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
     if (e != cudaSuccess) return e;
     const unsigned long long items = ((unsigned long long)prob.num_banks << prob.toggle_bits) * prob.num_systems;
-    const unsigned long long blocks = (items + kRk4Warps - 1) / kRk4Warps;
+    const unsigned long long blocks = (items + warps - 1) / warps;
     if (blocks > 0x7fffffffull) return cudaErrorInvalidConfiguration;
-    rk4_kernel<<<(unsigned)blocks, kRk4Warps * 32, smem, stream>>>(batch, prob, exec_bytes, cst_bytes, warp_bytes, scratch_slot);
+    rk4_kernel<<<(unsigned)blocks, warps * 32, smem, stream>>>(batch, prob, exec_bytes, cst_bytes, warp_bytes, scratch_slot);
     return cudaGetLastError();
 }
 

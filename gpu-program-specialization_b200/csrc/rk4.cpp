@@ -52,7 +52,7 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run) {
     rules.banks_allowed = true;
     rules.toggle_bits = run->toggle_bits;
     rules.columns_are_slots = true;
-    rules.reserved_slots = (unsigned)(5 * S); /* stage, next stage, base, sum, state vectors */
+    rules.reserved_slots = (unsigned)(4 * S); /* stage, next stage, sum, state vectors */
     for (size_t i = 0; i < programs.routines.count; ++i) {
         const SecantResult r = preflight(programs.routines.items[i], rules);
         if (r != SECANT_SUCCESS) return r;
