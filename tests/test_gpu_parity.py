@@ -320,3 +320,47 @@ def test_toggle_heavy_population_with_best_variant(cuda):
         assert grid[a, chosen] - best <= 2e-4 * abs(best) + 2 * slack[a, 0, chosen] + 1e-6, (a, chosen)
         assert abs(float(sse[a]) - got[a, 0, chosen]) == 0
         assert not (got[a, 0, :chosen] <= got[a, 0, chosen]).any()
+
+
+def test_zero_columns_constants_toggles_and_routine_toggle_propagation(cuda):
+    """projects/secant/tests/toggle_cuda_test.c:431-497: a literal-only program with no input
+    matrix, no constants and no toggle; then a toggle over two bank leaves that lives inside a
+    routine, called from the program."""
+    t = np.array([[0, .1, .2, .3, .4, .5, .6, .7, .8]], dtype=np.float32)
+    literal = P.PackedPrograms([P.lit_bits(0x40000000) + P.RET])                      # 2.0f
+    with Runner(abi.SHAPE_TOGGLE_SSE, 0, 1, 0, via_plan=True, num_kernels=1, asts_per_kernel=1) as rn:
+        out = torch.full((1, 1, 2), -7.0, device="cuda")
+        rn.run(rn.toggle_request(literal, None, dev(t), None, 1, 0, out, out_ld=2))
+        got = out.cpu().numpy().reshape(-1)
+    assert abs(got[0] - float(((2.0 - t.astype(np.float64)) ** 2).sum())) < 1e-5 and got[1] == -7.0
+    routed = P.PackedPrograms([P.routine(0) + P.RET], [P.bank(0) + P.bank(1) + P.tog2(0) + P.RET])
+    banks = np.array([[.7, -.3]], dtype=np.float32)
+    with Runner(abi.SHAPE_TOGGLE_SSE, 0, 1, 2, via_plan=True, num_kernels=1, asts_per_kernel=1) as rn:
+        got = rn.toggle_sse(routed, None, dev(t), dev(banks), 1, 1).cpu().numpy().reshape(-1)
+    want = [float(((v - t.astype(np.float64)) ** 2).sum()) for v in (np.float32(.7), np.float32(-.3))]
+    assert np.allclose(got, want, rtol=1e-6, atol=1e-6)
+    _, _, want64 = S.oracle_toggle_sse(routed, None, t, banks, 2, 1)
+    assert np.allclose(got, want64.reshape(-1), rtol=1e-6, atol=1e-6)
+
+
+def test_box_scale_population_of_a_million_programs(cuda):
+    """The sharded benchmark configuration's population size on one GPU (rows reduced): 2^20
+    programs, 16 coefficient sets, 16 features.  The population repeats a block of 65,536
+    programs, so every block of scores must repeat the first one bit for bit (one chunk of rows,
+    hence one addition per bin), and the first programs are checked against the oracle."""
+    block, repeats, rows, F, K, nb = 65536, 16, 256, 16, 16, 16
+    base = P.random_population(5, block, 32, F, K, 1.0)
+    pop = P.PackedPrograms(base.asts * repeats, base.routines)
+    x = np.stack([P.uniform(5, c, rows, -1, 1) for c in range(F)])
+    y = np.stack([P.normal(5, 100, rows)])
+    banks = np.stack([P.normal(5, 200 + b, K) for b in range(nb)])
+    with Runner(abi.SHAPE_TOGGLE_SSE, F, 1, K, workers=8, streams=2) as rn:
+        out = rn.toggle_sse(pop, dev(x), dev(y), dev(banks), nb, 0)
+        assert rn.stats.num_asts == block * repeats
+    grid = out.view(repeats, block, nb)
+    same = (grid == grid[0:1]) | (torch.isnan(grid) & torch.isnan(grid[0:1]))
+    assert bool(same.all())
+    head = base.subset(range(200))
+    _, _, want64 = S.oracle_toggle_sse(head, x, y, banks, K, 0)
+    slack = S.sse_slack(head, x, y, banks, K, 0)
+    assert not parity.sse_mismatches(grid[0, :200].cpu().numpy()[:, None, :], want64, slack).any()
