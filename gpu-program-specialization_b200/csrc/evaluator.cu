@@ -122,7 +122,7 @@ __device__ __noinline__ void rare_over_scratch(unsigned op, float4* slots, uint3
     }
 }
 
-template <int RR, int RC>
+template <int RR, int RC, bool FAST = false>
 struct Machine {
     static constexpr int V = RR * RC;
     static constexpr int PASS = 32 * RR;      /* rows one warp covers per pass */
@@ -266,6 +266,11 @@ struct Machine {
                     const float* fx = &xv[0][0];
 #pragma unroll
                     for (int j = 0; j < V / 4; ++j) {
+                        if (FAST) {
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) fa[4 * j + k] = sbm::fast_div(fa[4 * j + k], fx[4 * j + k]);
+                            continue;
+                        }
                         const float4 o = sbm::div4(make_float4(fa[4 * j], fa[4 * j + 1], fa[4 * j + 2], fa[4 * j + 3]),
                                                    make_float4(fx[4 * j], fx[4 * j + 1], fx[4 * j + 2], fx[4 * j + 3]));
                         fa[4 * j] = o.x; fa[4 * j + 1] = o.y; fa[4 * j + 2] = o.z; fa[4 * j + 3] = o.w;
@@ -276,19 +281,33 @@ struct Machine {
             SB_BIN_CASES(SB_BIN_MAX)
             SB_UN_CASE(SB_UN_NEG)
             SB_UN_CASE(SB_UN_ABS)
-            case SB_CASE_UN + SB_UN_EX2: SB_FOR_QUADS(sbm::exp2_4(in)) break;
-            case SB_CASE_UN + SB_UN_EXP: SB_FOR_QUADS(sbm::exp4(in)) break;
-            case SB_CASE_UN + SB_UN_LOG: SB_FOR_QUADS(sbm::log4(in)) break;
+            case SB_CASE_UN + SB_UN_EX2:
+                if (FAST) { SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_EX2, acc[r][c]); } else SB_FOR_QUADS(sbm::exp2_4(in))
+                break;
+            case SB_CASE_UN + SB_UN_EXP:
+                if (FAST) { SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_EXP, acc[r][c]); } else SB_FOR_QUADS(sbm::exp4(in))
+                break;
+            case SB_CASE_UN + SB_UN_LOG:
+                if (FAST) { SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_LOG, acc[r][c]); } else SB_FOR_QUADS(sbm::log4(in))
+                break;
             case SB_CASE_UN + SB_UN_SIN:
             case SB_CASE_UN + SB_UN_COS: { /* cos x = sin(x + pi/2): one body, shifted quadrant */
                 const int shift = (int)(ins.x & 0xffu) - (SB_CASE_UN + SB_UN_SIN);
-                SB_FOR_QUADS(sbm::sincos4(in, shift))
+                if (FAST) {
+                    if (shift) { SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_COS, acc[r][c]); }
+                    else { SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_SIN, acc[r][c]); }
+                } else SB_FOR_QUADS(sbm::sincos4(in, shift))
                 break; }
             case SB_CASE_UN + SB_UN_SQRT:
             case SB_CASE_UN + SB_UN_RCP:
             case SB_CASE_UN + SB_UN_LG2:
             case SB_CASE_UN + SB_UN_RSQRT:
             case SB_CASE_UN + SB_UN_TANH:
+                if (FAST) {
+                    const unsigned op = (ins.x & 0xffu) - SB_CASE_UN;
+                    SB_FOR_TILE acc[r][c] = sbm::fast_unary(op, acc[r][c]);
+                    break;
+                }
                 store_slot(slots, scratch_slot);
                 rare_over_scratch<V>((ins.x & 0xffu) - SB_CASE_UN, slots, scratch_slot);
                 fetch_slot(slots, scratch_slot, acc);
@@ -313,10 +332,10 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 /* 16-value tiles run 16 warps per CTA within 128 registers; 32-value tiles need more
  * registers per thread and run 12 warps. */
-template <int RR, int RC>
+template <int RR, int RC, bool FAST>
 __global__ void __launch_bounds__(RR * RC > 16 ? 384 : 640, 1)
 eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
-    using M = Machine<RR, RC>;
+    using M = Machine<RR, RC, FAST>;
     extern __shared__ __align__(16) unsigned char smem[];
     float* const tile = reinterpret_cast<float*>(smem);
     unsigned int* const queue = reinterpret_cast<unsigned int*>(smem + geom.tile_bytes);
@@ -683,7 +702,11 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, 
 template <int RR, int RC>
 cudaError_t launch_variant(const DeviceBatch& batch, const EvalProblem& prob, const Geom& geom, const LaunchPlan& plan,
                            cudaStream_t stream) {
-    eval_kernel<RR, RC><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom);
+    /* approximate math exists for the 16-value tiles, which are the ones the planner picks */
+    if (RR * RC <= 16 && prob.fast_math)
+        eval_kernel<RR, RC, (RR * RC <= 16)><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom);
+    else
+    eval_kernel<RR, RC, false><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom);
     return cudaGetLastError();
 }
 
@@ -827,7 +850,8 @@ cudaError_t configure_kernels() {
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
     if ((e = cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return e;
 #define SB_CONFIGURE(RR, RC) \
-    if ((e = cudaFuncSetAttribute(eval_kernel<RR, RC>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(eval_kernel<RR, RC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e; \
+    if (RR * RC <= 16 && (e = cudaFuncSetAttribute(eval_kernel<RR, RC, (RR * RC <= 16)>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
     SB_FOR_VARIANTS(SB_CONFIGURE)
 #undef SB_CONFIGURE
     return cudaSuccess;

@@ -53,6 +53,7 @@ struct EvalProblem {
     uint32_t num_banks;       /* >= 1 */
     uint32_t toggle_bits;
     uint32_t fixed_permutation; /* materialize: the single permutation evaluated */
+    uint32_t fast_math;       /* 1: approximate division and transcendental functions (see sbmath.cuh) */
     size_t num_rows;
     float* output;
     size_t out_program_stride; /* elements between consecutive programs */

@@ -103,6 +103,7 @@ struct SecantCubinRunnerImpl {
     /* handle state */
     bool active = false, failed = false, shutdown = false;
     int forced_variant = -1;       /* test hook: pin the register-tile variant */
+    uint32_t fast_math = 0;        /* secant_b200_runner_set_math */
     std::string last_error;
 };
 
@@ -383,6 +384,7 @@ SecantResult launch_batch(SecantCubinRunnerImpl* r, const DeviceBatch& db, size_
         const size_t k = (*stream_cursor)++ % r->streams.size();
         cudaStream_t stream = r->streams[k];
         EvalProblem prob = make_problem(plan, runs[e], 0);
+        prob.fast_math = r->fast_math;
         (void)first_program; /* SbProgram::index already places every program in the run */
         if (runs[e].program_bank_stride)
             prob.banks = reinterpret_cast<const float*>(runs[e].banks.address) + runs[e].first_program_index * runs[e].program_bank_stride;
@@ -889,6 +891,14 @@ SecantResult secant_b200_population_destroy(SecantB200Population pop) {
         if (b.device && cudaFree(b.device) != cudaSuccess) result = SECANT_ERROR_DRIVER_FAILED;
     delete pop;
     return result;
+}
+
+SecantResult secant_b200_runner_set_math(SecantCubinRunner r, uint32_t mode) {
+    if (!r || mode > SECANT_B200_MATH_FAST) return SECANT_ERROR_INVALID_VALUE;
+    std::lock_guard<std::mutex> lock(r->mutex);
+    if (r->active) return SECANT_ERROR_INVALID_STATE;
+    r->fast_math = mode == SECANT_B200_MATH_FAST ? 1u : 0u;
+    return SECANT_SUCCESS;
 }
 
 /* Test hook: pins the register-tile variant (0: 4x4, 1: 8x2, 2: 16x1, -1: automatic). */

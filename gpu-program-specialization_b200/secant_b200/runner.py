@@ -160,6 +160,10 @@ class Runner:
         self.run(self.materialize_request(packed, x, out))
         return out
 
+    def set_math(self, fast):
+        """fast=True selects the approximate division / transcendental functions of the reference's GPU kernels."""
+        abi.check(self.lib.secant_b200_runner_set_math(self.handle, 1 if fast else 0), "secant_b200_runner_set_math")
+
     def force_variant(self, variant):
         self.lib.secant_b200_runner_force_variant(self.handle, variant)
 

@@ -72,6 +72,21 @@ SECANT_DEC SecantResult secant_b200_population_run_batch(SecantB200Population po
 SECANT_DEC uint64_t secant_b200_population_num_ops(SecantB200Population population);
 SECANT_DEC SecantResult secant_b200_population_destroy(SecantB200Population population);
 
+/*
+ * Arithmetic of division and of the transcendental functions.
+ *   ACCURATE (default): IEEE division, sin/cos/exp/log within 2-2.5 ulp of the correctly rounded
+ *       result over the whole float range - the numerics of the reference HOST evaluator
+ *       (projects/secant/s_cpu.c:329-352), which the parity tests are held to.
+ *   FAST: special-function-unit approximations (__sinf, __expf, __logf, __fdividef, ...), the
+ *       lowerings the reference's GPU kernels are compiled with (--use_fast_math,
+ *       projects/secant/tests/toggle_cuda_test.c:74).  Sums agree with the host evaluator to
+ *       the reference GPU test's tolerance, 2e-4 * (1 + |sum|), on well-conditioned programs.
+ * Add, subtract, multiply, min, max, negate and abs are exact in both modes.  Returns
+ * INVALID_STATE while a run is in flight.  The RK4 entry point always uses ACCURATE.
+ */
+enum { SECANT_B200_MATH_ACCURATE = 0, SECANT_B200_MATH_FAST = 1 };
+SECANT_DEC SecantResult secant_b200_runner_set_math(SecantCubinRunner runner, uint32_t mode);
+
 /* Pins the per-thread register tile used by the evaluator: 0 = 4 rows x 4 banks,
  * 1 = 8 x 2, 2 = 16 x 1, -1 = automatic.  Every variant computes the same values. */
 SECANT_DEC void secant_b200_runner_force_variant(SecantCubinRunner runner, int variant);

@@ -364,3 +364,31 @@ def test_box_scale_population_of_a_million_programs(cuda):
     _, _, want64 = S.oracle_toggle_sse(head, x, y, banks, K, 0)
     slack = S.sse_slack(head, x, y, banks, K, 0)
     assert not parity.sse_mismatches(grid[0, :200].cpu().numpy()[:, None, :], want64, slack).any()
+
+
+def test_fast_math_mode_meets_the_reference_gpu_tolerance(cuda):
+    """secant_b200_runner_set_math(FAST) selects the approximations the reference's GPU kernels are
+    compiled with; its results are held to the reference GPU test's own bound against the host
+    evaluator, 2e-4 * (1 + |cpu|) (projects/secant/tests/toggle_cuda_test.c:158-165), on that
+    test's two workloads: the closed-form fixture and the seeded random toggle population."""
+    def close(got, want):
+        return np.abs(got - want) <= 2e-4 * (1 + np.abs(want))
+    fx = packed("fixture")
+    with Runner(abi.SHAPE_TOGGLE_SSE, 3, 2, 2, workers=2, streams=2) as rn:
+        assert rn.lib.secant_b200_runner_set_math(rn.handle, 2) == abi.ERROR_INVALID_VALUE
+        args = (fx, dev(G["fixture_x"]), dev(G["fixture_y"]), dev(G["fixture_banks"]), 13, 3)
+        accurate = rn.toggle_sse(*args).cpu().numpy()
+        rn.set_math(True)
+        fast = rn.toggle_sse(*args).cpu().numpy()
+        rn.set_math(False)
+        again = rn.toggle_sse(*args).cpu().numpy()
+    want = G["fixture_sse_pass0"][:, :, :104]
+    assert close(fast, want).all() and np.array_equal(accurate, again)
+    pop = packed("random")
+    with Runner(abi.SHAPE_TOGGLE_SSE, 3, 2, 4, workers=2, streams=2) as rn:
+        rn.set_math(True)
+        fast = rn.toggle_sse(pop, dev(G["random_x"]), dev(G["random_y"]), dev(G["random_banks"]), 5, 3).cpu().numpy()
+    ref = G["random_sse"]
+    finite = np.isfinite(ref)
+    assert np.array_equal(np.isfinite(fast), finite)
+    assert close(fast[finite], ref[finite]).mean() > 0.97     # ill-conditioned bins aside (the accurate mode widens them too)
