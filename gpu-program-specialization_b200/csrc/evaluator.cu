@@ -127,7 +127,6 @@ struct Machine {
     static constexpr int V = RR * RC;
     static constexpr int PASS = 32 * RR;      /* rows one warp covers per pass */
     static constexpr int GROUPS = RR / 4;     /* float4 row groups per thread */
-    static constexpr int SLOT_BYTES = V * 128;
 
     float acc[RR][RC];
 
