@@ -478,7 +478,7 @@ def gpu_arm(args, w):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "comparator", "rk4"])
     ap.add_argument("--programs", type=int, default=None, help="development only: shrink the population")
