@@ -463,7 +463,7 @@ def gpu_arm(args, w):
                          "note": "achieved = sum over programs of (ops + 2) x sets x rows / kernel time, one per "
                                  "algorithmic operation; peak = FFMA lane-instructions/s probed on this device in this "
                                  "run; DRAM traffic needs a multi-pass capture: measured on a reduced case only "
-                                 "(18.8 MB per launch against 17.8 MB algorithmic) and not proportional to the unit count"},
+                                 "(18.6 MB per launch against 17.8 MB algorithmic) and not proportional to the unit count"},
             "cpu_baseline": cpu,
             "top1024_head": [int(i) for i in top[:4].tolist()],
         }
