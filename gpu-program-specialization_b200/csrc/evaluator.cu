@@ -557,7 +557,7 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
  * launch so that as many warps as possible fit the SM's shared memory. */
 constexpr int kRk4MaxWarps = 16;
 
-__global__ void __launch_bounds__(kRk4MaxWarps * 32, 2)
+__global__ void __launch_bounds__(kRk4MaxWarps * 32, 1)
 rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, uint32_t cst_bytes, uint32_t warp_bytes,
            uint32_t scratch_slot) {
     using M = Machine<4, 1>;
@@ -601,33 +601,57 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, 
     __syncwarp();
 
     const uint32_t STAGE = 0, NEXT = S, SUM = 2 * S, STATE = 3 * S, BASE = STATE;
-    const uint32_t points = prob.points_per_trajectory;
+    const bool ragged = prob.offsets != nullptr;
     M m;
     float sq = 0.0f;
-    bool ok = true;
+    unsigned long long residuals = 0;
+    /* any non-finite time or reference value (NaN excepted where it means "unobserved"), found
+     * by the validation kernel, invalidates every score; so do offsets that do not span the data */
+    bool ok = *prob.invalid_flag == 0;
+    if (ragged) ok = ok && prob.offsets[0] == 0u && prob.offsets[prob.num_trajectories] == prob.total_points;
     for (uint32_t t0 = 0; t0 < prob.num_trajectories; t0 += 128) {
-        bool live[4];
-        size_t first[4];
+        uint32_t begin[4], npts[4], longest = 0;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const uint32_t traj = t0 + lane * 4 + q;
-            live[q] = traj < prob.num_trajectories;
-            first[q] = (size_t)(live[q] ? traj : 0) * points;
+            const bool live = traj < prob.num_trajectories;
+            begin[q] = 0; npts[q] = 0;
+            if (live && ragged) {
+                const uint32_t b = prob.offsets[traj], e = prob.offsets[traj + 1];
+                const bool sane = e > b && e <= prob.total_points;
+                ok = ok && sane;
+                if (sane) { begin[q] = b; npts[q] = e - b; }
+            } else if (live) {
+                begin[q] = traj * prob.points_per_trajectory; npts[q] = prob.points_per_trajectory;
+            }
+            longest = max(longest, npts[q]);
         }
+#pragma unroll
+        for (int d = 16; d; d >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, d));
         for (uint32_t s = 0; s < S; ++s) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                const float v = live[q] ? prob.reference[(size_t)s * prob.reference_ld + first[q]] : 0.0f;
-                ok = ok && (!live[q] || (fabsf(v) <= 3.402823466e+38f));
+                const float v = npts[q] ? prob.reference[(size_t)s * prob.reference_ld + begin[q]] : 0.0f;
+                ok = ok && (fabsf(v) <= 3.402823466e+38f); /* initial states must be complete and finite */
                 m.acc[q][0] = v;
             }
             m.store_slot(slots, STATE + s);
         }
-        for (uint32_t k = 1; k < points; ++k) {
-            const float interval = prob.times[k] - prob.times[k - 1];
-            const float h = interval / (float)prob.substeps;
-            ok = ok && (fabsf(interval) <= 3.402823466e+38f) && interval > 0.0f && h > 0.0f;
-            const float half = 0.5f * h, sixth = h / 6.0f;
+        for (uint32_t k = 1; k < longest; ++k) {
+            /* per trajectory step size; a trajectory that has ended keeps integrating with h = 0
+             * and is left out of every check and sum */
+            float h[4], sixth[4];
+            bool act[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                act[q] = k < npts[q];
+                const uint32_t at = ragged ? begin[q] + k : k;
+                const float interval = act[q] ? prob.times[at] - prob.times[at - 1] : 0.0f;
+                const float step = interval / (float)prob.substeps;
+                ok = ok && (!act[q] || ((fabsf(interval) <= 3.402823466e+38f) && interval > 0.0f && step > 0.0f));
+                h[q] = act[q] ? step : 0.0f;
+                sixth[q] = h[q] / 6.0f;
+            }
             for (uint32_t sub = 0; sub < prob.substeps; ++sub) {
                 for (uint32_t s = 0; s < S; ++s) {
                     m.fetch_slot(slots, STATE + s, m.acc);
@@ -639,7 +663,6 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, 
 #pragma unroll 1
                 for (int stage = 0; stage < 4; ++stage) {
                     const float weight = (stage == 0 || stage == 3) ? 1.0f : 2.0f;
-                    const float stage_h = stage == 2 ? h : half;
                     for (uint32_t s = 0; s < S; ++s) {
                         const SbInsn* exec = reinterpret_cast<const SbInsn*>(warea + (size_t)s * exec_bytes);
                         const float* cst = reinterpret_cast<const float*>(warea + (size_t)S * exec_bytes + (size_t)s * cst_bytes);
@@ -654,7 +677,8 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, 
                         if (stage != 3) {
                             m.fetch_slot(slots, BASE + s, v);
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) m.acc[q][0] = __fmaf_rn(stage_h, rhs[q], v[q][0]);
+                            for (int q = 0; q < 4; ++q)
+                                m.acc[q][0] = __fmaf_rn(stage == 2 ? h[q] : __fmul_rn(0.5f, h[q]), rhs[q], v[q][0]);
                             m.store_slot(slots, NEXT + s);
                         }
                     }
@@ -669,33 +693,60 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, 
                     m.fetch_slot(slots, SUM + s, sum);
                     m.fetch_slot(slots, BASE + s, base);
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) m.acc[q][0] = __fmaf_rn(sixth, sum[q][0], base[q][0]);
+                    for (int q = 0; q < 4; ++q) m.acc[q][0] = __fmaf_rn(sixth[q], sum[q][0], base[q][0]);
                     m.store_slot(slots, STATE + s);
                 }
             }
             for (uint32_t s = 0; s < S; ++s) { /* all states must be finite before any residual counts */
                 m.fetch_slot(slots, STATE + s, m.acc);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) ok = ok && (!live[q] || fabsf(m.acc[q][0]) <= 3.402823466e+38f);
+                for (int q = 0; q < 4; ++q) ok = ok && (!act[q] || fabsf(m.acc[q][0]) <= 3.402823466e+38f);
             }
             for (uint32_t s = 0; s < S; ++s) {
                 m.fetch_slot(slots, STATE + s, m.acc);
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
-                    if (live[q]) {
-                        const float err = __fsub_rn(m.acc[q][0], prob.reference[(size_t)s * prob.reference_ld + first[q] + k]);
+                    if (act[q]) {
+                        const float ref = prob.reference[(size_t)s * prob.reference_ld + begin[q] + k];
+                        if (prob.allow_missing && ref != ref) continue; /* unobserved */
+                        const float err = __fsub_rn(m.acc[q][0], ref);
                         sq = __fmaf_rn(err, err, sq);
+                        ++residuals;
                     }
             }
         }
     }
     const float total = warp_sum(sq);
+    uint32_t lo = (uint32_t)residuals, hi = (uint32_t)(residuals >> 32);
+#pragma unroll
+    for (int d = 16; d; d >>= 1) {
+        const unsigned long long other = ((unsigned long long)__shfl_xor_sync(0xffffffffu, hi, d) << 32) | __shfl_xor_sync(0xffffffffu, lo, d);
+        residuals += other;
+        lo = (uint32_t)residuals; hi = (uint32_t)(residuals >> 32);
+    }
     const bool all_ok = __all_sync(0xffffffffu, ok);
     if (lane == 0) {
-        const float residuals = (float)((unsigned long long)prob.num_trajectories * (points - 1) * S);
         const bool finite = fabsf(total) <= 3.402823466e+38f;
-        prob.output[(size_t)sys * prob.output_ld + cfg] = (all_ok && finite) ? total / residuals : 3.402823466e+38f;
+        prob.output[(size_t)sys * prob.output_ld + cfg] = (all_ok && residuals && finite) ? total / (float)residuals : 3.402823466e+38f;
     }
+}
+
+/* Raises *flag when a time or a reference value of an active state is not finite; NaN reference
+ * values are tolerated when they mean "unobserved" (initial points are checked by the scorer). */
+__global__ void rk4_validate_kernel(const Rk4Problem prob) {
+    const size_t n = (size_t)prob.total_points * (prob.num_states + 1);
+    bool bad = false;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / prob.total_points, col = i % prob.total_points;
+        if (row == prob.num_states) {
+            if (!prob.offsets && col >= prob.points_per_trajectory) continue; /* uniform form: one shared time axis */
+            bad = bad || !(fabsf(prob.times[col]) <= 3.402823466e+38f);
+        } else {
+            const float v = prob.reference[row * prob.reference_ld + col];
+            bad = bad || !((fabsf(v) <= 3.402823466e+38f) || (prob.allow_missing && v != v));
+        }
+    }
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(prob.invalid_flag, 1);
 }
 
 template <int RR, int RC>
@@ -863,13 +914,13 @@ cudaError_t launch_rk4(const DeviceBatch& batch, const Rk4Problem& prob, size_t 
     const uint32_t scratch_slot = batch.max_slots; /* max_slots already includes the integrator's reserved slots */
     const uint32_t warp_bytes = prob.num_states * (exec_bytes + cst_bytes) + (batch.max_slots + 1u) * 4u * 128u;
     /* warps per CTA: the count that puts most warps on an SM (shared memory per SM is the CTA
-     * limit plus 1 KB reserved per resident CTA; 64 registers per thread allow 32 warps) */
+     * limit plus 1 KB reserved per resident CTA; the register file holds about 24 warps) */
     int warps = 0, best = 0;
     for (int w = 2; w <= kRk4MaxWarps; ++w) {
         const size_t cta = (size_t)warp_bytes * w;
         if (cta > smem_limit) break;
         int ctas = (int)((smem_limit + 1024) / (cta + 1024));
-        if (ctas * w > 32) ctas = 32 / w;
+        if (ctas * w > 24) ctas = 24 / w; /* registers: about 80 per thread */
         if (ctas * w >= best) { best = ctas * w; warps = w; }
     }
     if (!warps) return cudaErrorInvalidConfiguration;
@@ -879,6 +930,8 @@ cudaError_t launch_rk4(const DeviceBatch& batch, const Rk4Problem& prob, size_t 
     const unsigned long long items = ((unsigned long long)prob.num_banks << prob.toggle_bits) * prob.num_systems;
     const unsigned long long blocks = (items + warps - 1) / warps;
     if (blocks > 0x7fffffffull) return cudaErrorInvalidConfiguration;
+    const size_t values = (size_t)prob.total_points * (prob.num_states + 1);
+    rk4_validate_kernel<<<(unsigned)std::min<size_t>(1024, (values + 255) / 256), 256, 0, stream>>>(prob);
     rk4_kernel<<<(unsigned)blocks, warps * 32, smem, stream>>>(batch, prob, exec_bytes, cst_bytes, warp_bytes, scratch_slot);
     return cudaGetLastError();
 }

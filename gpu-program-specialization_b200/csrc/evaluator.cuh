@@ -89,7 +89,11 @@ struct Rk4Problem {
     const float* reference;        /* [state][total_points]; a trajectory starts at its first point */
     size_t reference_ld;
     uint32_t num_trajectories, points_per_trajectory, substeps;
-    const float* times;            /* [points_per_trajectory] */
+    const float* times;            /* [points_per_trajectory], or [total_points] with offsets */
+    const uint32_t* offsets;       /* [num_trajectories + 1] partition of total_points, or null */
+    uint32_t total_points;         /* concatenated points (both forms) */
+    uint32_t allow_missing;        /* NaN reference values after a first point are unobserved */
+    int* invalid_flag;             /* device word the validation kernel raises */
     float* output;                 /* [system][configuration] */
     size_t output_ld;
 };

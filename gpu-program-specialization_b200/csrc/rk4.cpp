@@ -13,13 +13,22 @@
 #include "evaluator.cuh"
 #include "internal.h"
 
+#include <cstddef>
 #include <cstring>
 #include <vector>
 
 using namespace sb;
 
-extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run) {
-    if (!run || run->struct_size < sizeof(*run)) return SECANT_ERROR_INVALID_VALUE;
+extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
+    /* the uniform form ends before trajectory_offsets; shorter structs are extended with zeros */
+    const size_t uniform_size = offsetof(SecantB200Rk4Run, trajectory_offsets);
+    if (!given || given->struct_size < uniform_size) return SECANT_ERROR_INVALID_VALUE;
+    SecantB200Rk4Run local;
+    std::memset(&local, 0, sizeof(local));
+    std::memcpy(&local, given, given->struct_size < sizeof(local) ? given->struct_size : sizeof(local));
+    const SecantB200Rk4Run* run = &local;
+    const bool ragged = run->trajectory_offsets != 0;
+    if (run->reserved3 || run->allow_missing_observations > 1) return SECANT_ERROR_INVALID_VALUE;
     if (run->version != SECANT_CUBIN_RUN_VERSION_3) return SECANT_ERROR_UNSUPPORTED_VERSION;
     if (run->flags) return SECANT_ERROR_INVALID_VALUE;
     const size_t S = run->num_states, K = run->num_constants;
@@ -27,11 +36,14 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run) {
     if (!S || S > 8 || K > SECANT_AST_MAX_INPUTS || !run->num_systems || !programs.asts.items ||
         programs.asts.count != run->num_systems * S || programs.routines.count > SECANT_AST_MAX_ROUTINES ||
         (programs.routines.count && !programs.routines.items) || !run->num_banks || run->toggle_bits > 32 ||
-        !run->num_trajectories || run->points_per_trajectory < 2 || !run->steps_per_observation || !run->times ||
+        !run->num_trajectories || (!ragged && run->points_per_trajectory < 2) || !run->steps_per_observation || !run->times ||
         run->num_systems > 0x7fffffffull / S || run->num_trajectories > 0xffffffffull || run->points_per_trajectory > 0xffffffffull ||
         run->steps_per_observation > 0xffffffffull)
         return SECANT_ERROR_INVALID_VALUE;
-    const size_t total_points = run->num_trajectories * run->points_per_trajectory;
+    if (ragged && (run->trajectory_offsets % 4 || run->total_points < run->num_trajectories || run->total_points > 0xffffffffull))
+        return SECANT_ERROR_INVALID_VALUE;
+    if (!ragged && run->num_trajectories > 0xffffffffull / run->points_per_trajectory) return SECANT_ERROR_OVERFLOW;
+    const size_t total_points = ragged ? run->total_points : run->num_trajectories * run->points_per_trajectory;
     const size_t configs = run->num_banks << run->toggle_bits;
     if (run->reference.leading_dimension < total_points || run->reference.num_elements < (S - 1) * run->reference.leading_dimension + total_points ||
         !run->reference.address || run->reference.address % 4 || run->times % 4)
@@ -79,7 +91,8 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run) {
     const size_t o_patch = align256(o_insn + enc.insns.size() * sizeof(SbInsn));
     const size_t o_aff = align256(o_patch + enc.patches.size() * sizeof(SbPatch));
     const size_t o_lit = align256(o_aff + enc.affines.size() * sizeof(SbAffine));
-    const size_t total = align256(o_lit + enc.lits.size() * sizeof(float) + 16);
+    const size_t o_flag = align256(o_lit + enc.lits.size() * sizeof(float) + 16); /* one word raised by the data validation */
+    const size_t total = o_flag + 256;
     std::vector<char> host(total, 0);
     std::memcpy(host.data(), enc.programs.data(), enc.programs.size() * sizeof(SbProgram));
     std::memcpy(host.data() + o_insn, enc.insns.data(), enc.insns.size() * sizeof(SbInsn));
@@ -117,10 +130,14 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run) {
         p.num_trajectories = (uint32_t)run->num_trajectories; p.points_per_trajectory = (uint32_t)run->points_per_trajectory;
         p.substeps = (uint32_t)run->steps_per_observation;
         p.times = reinterpret_cast<const float*>(run->times);
+        p.offsets = reinterpret_cast<const uint32_t*>(run->trajectory_offsets);
+        p.total_points = (uint32_t)total_points;
+        p.allow_missing = run->allow_missing_observations;
+        p.invalid_flag = reinterpret_cast<int*>(d + o_flag);
         p.output = reinterpret_cast<float*>(run->output.address);
         p.output_ld = run->output.leading_dimension;
         e = launch_rk4(db, p, (size_t)limit, nullptr);
-        if (e == cudaSuccess) note_kernel_launches(1);
+        if (e == cudaSuccess) note_kernel_launches(2);
         if (e == cudaErrorInvalidConfiguration) { cudaFree(d); return SECANT_ERROR_REGISTER_OVERFLOW; }
         if (e == cudaSuccess) e = cudaDeviceSynchronize();
     }

@@ -141,7 +141,9 @@ class Rk4Run(C.Structure):  # SecantB200Rk4Run
                 ("num_systems", _sz), ("num_states", _sz), ("num_constants", _sz), ("constants", DeviceBanks),
                 ("system_bank_stride", _sz), ("num_banks", _sz), ("toggle_bits", _u32), ("reserved2", _u32),
                 ("reference", DeviceMatrix), ("num_trajectories", _sz), ("points_per_trajectory", _sz),
-                ("times", C.c_size_t), ("steps_per_observation", _sz), ("output", DeviceMatrix)]
+                ("times", C.c_size_t), ("steps_per_observation", _sz), ("output", DeviceMatrix),
+                ("trajectory_offsets", C.c_size_t), ("total_points", _sz), ("allow_missing_observations", _u32),
+                ("reserved3", _u32)]
 
 
 class Score(C.Structure):  # SecantB200Score, layout of the reference consumer's SRScore

@@ -248,17 +248,19 @@ def topk(scores, k):
 
 
 def rk4_score(packed, num_states, reference, times, constants=None, num_constants=0, num_banks=1, toggle_bits=0,
-              steps_per_observation=1, points_per_trajectory=None):
+              steps_per_observation=1, points_per_trajectory=None, offsets=None, allow_missing=False):
     """Fixed-step RK4 rollout scores [system][configuration] (extension API).
 
     packed: num_systems * num_states right-hand-side programs, system-major.
-    reference: CUDA tensor [state][trajectories * points]; times: CUDA tensor [points];
+    Uniform form: reference is a CUDA tensor [state][trajectories * points], times a CUDA tensor
+    [points].  Ragged form (offsets given: CUDA int32/uint32 tensor [trajectories + 1]): reference
+    is [state][concatenated points], times is [concatenated points]; with allow_missing NaN
+    reference values after a trajectory's first point are unobserved.
     constants: CUDA tensor [system][bank][slot] or None."""
     lib = abi.load()
     run = abi.Rk4Run()
     run.struct_size, run.version = C.sizeof(run), abi.RUN_VERSION
     packed.fill(run.programs)
-    points = points_per_trajectory or times.numel()
     systems = len(packed.asts) // num_states
     run.num_systems, run.num_states, run.num_constants = systems, num_states, num_constants
     if constants is not None and num_constants:
@@ -266,8 +268,15 @@ def rk4_score(packed, num_states, reference, times, constants=None, num_constant
             constants.data_ptr(), constants.numel(), constants.shape[-1])
     run.num_banks, run.toggle_bits = num_banks, toggle_bits
     run.reference = _matrix(reference)
-    run.num_trajectories = reference.shape[-1] // points
-    run.points_per_trajectory = points
+    if offsets is not None:
+        run.trajectory_offsets = offsets.data_ptr()
+        run.num_trajectories = offsets.numel() - 1
+        run.total_points = times.numel()
+        run.allow_missing_observations = 1 if allow_missing else 0
+    else:
+        points = points_per_trajectory or times.numel()
+        run.num_trajectories = reference.shape[-1] // points
+        run.points_per_trajectory = points
     run.times = times.data_ptr()
     run.steps_per_observation = steps_per_observation
     out = torch.empty((systems, num_banks << toggle_bits), dtype=torch.float32, device=reference.device)

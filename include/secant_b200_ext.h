@@ -103,6 +103,15 @@ SECANT_DEC void secant_b200_runner_force_variant(SecantCubinRunner runner, int v
  * soon as a time step, an initial state, an integrated state or the error sum is not finite.
  *   reference   [state][trajectory * points_per_trajectory + point], device, f32
  *   times       device float[points_per_trajectory], shared by all trajectories
+ * Ragged form, the reference engine's launch layout (projects/odezza/core/odezza.h:275-289): when
+ * trajectory_offsets is non-zero it addresses device uint32[num_trajectories + 1] partitioning
+ * total_points concatenated points (first point of a trajectory = its initial condition),
+ * times is device float[total_points] (strictly increasing inside a trajectory, steps may be
+ * irregular), reference is [state][concatenated point] and points_per_trajectory is ignored.
+ * Offsets that do not start at zero, increase strictly and end at total_points, a non-finite
+ * time or reference value anywhere, or no scored value at all give FLT_MAX in every score.  With
+ * allow_missing_observations a NaN reference value after a trajectory's first point is an
+ * unobserved value: it is skipped, and the mean divides by the values that were observed.
  *   constants   [system][bank][slot]; system_bank_stride 0 = num_banks * bank_stride
  *   output      [system][configuration], configuration = bank * 2^toggle_bits + permutation
  * Blocking; uses the current CUDA device and context.  Transcendental opcodes are allowed in
@@ -121,6 +130,10 @@ typedef struct SecantB200Rk4Run {
     uintptr_t times;
     size_t steps_per_observation;
     SecantDeviceMatrixF32 output;
+    /* appended fields; a struct_size that ends before them, or zeros, select the uniform form */
+    uintptr_t trajectory_offsets;
+    size_t total_points;
+    uint32_t allow_missing_observations, reserved3;
 } SecantB200Rk4Run;
 SECANT_DEC SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run);
 

@@ -581,21 +581,43 @@ SO_EXPORT size_t so_topk(const float* scores, size_t count, size_t k, uint64_t* 
  * rounded operations (add, sub, mul, div, fma, sqrt, rcp, neg, abs, min, max).
  * Parity: unpinned beyond the closed-form case in the test-suite (the reference has no
  * general fp32 host scorer to run). */
-SO_EXPORT SecantResult so_rk4_score(const uint8_t* routine_blob, const uint64_t* routine_off, size_t num_routines,
-                                    const uint8_t* rhs_blob, const uint64_t* rhs_off, size_t num_systems,
-                                    size_t num_states, size_t num_constants, const float* constants,
-                                    size_t system_constant_stride, const float* reference, size_t num_trajectories,
-                                    size_t points_per_trajectory, const float* times, size_t substeps, uint32_t toggle_bits,
-                                    uint32_t permutation, float* scores, double* scores64) {
+/* General form.  offsets == NULL: every trajectory has points_per_trajectory points and
+ * times[points_per_trajectory] is shared.  offsets != NULL: the reference engine's launch layout
+ * (projects/odezza/core/odezza.h:275-289, checks and loop of
+ * projects/odezza/core/o_generate_scoring_cuda.c:494-588): offsets[num_trajectories + 1]
+ * partition total_points concatenated points, times is per point, and with allow_missing a NaN
+ * reference value after a trajectory's first point is an unobserved value: it is skipped and the
+ * mean divides by the residuals that were observed. */
+static SecantResult so_rk4_general(const uint8_t* routine_blob, const uint64_t* routine_off, size_t num_routines,
+                                   const uint8_t* rhs_blob, const uint64_t* rhs_off, size_t num_systems, size_t num_states,
+                                   size_t num_constants, const float* constants, size_t system_constant_stride,
+                                   const float* reference, size_t num_trajectories, size_t points_per_trajectory,
+                                   const uint32_t* offsets, size_t total_points, int allow_missing, const float* times,
+                                   size_t substeps, uint32_t toggle_bits, uint32_t permutation, float* scores, double* scores64) {
     SoPrograms p;
     SoEnv env;
-    const size_t total_points = num_trajectories * points_per_trajectory;
-    size_t sys, tr, k, sub, stage, s;
+    size_t sys, tr, point, sub, stage, s;
     float state[8], base[8], work[8], sum[8], rhs[8];
     SecantResult r;
-    if (!num_states || num_states > 8 || !num_systems || !num_trajectories || points_per_trajectory < 2 || !substeps ||
+    if (!num_states || num_states > 8 || !num_systems || !num_trajectories || (!offsets && points_per_trajectory < 2) || !substeps ||
         !reference || !times || !scores)
         return SECANT_ERROR_INVALID_VALUE;
+    if (!offsets) total_points = num_trajectories * points_per_trajectory;
+    {   /* the reference kernel stages every time and reference value first and gives up on all
+         * scores when one of them is not finite (o_generate_scoring_cuda.c:457-477) */
+        int invalid_data = 0;
+        const size_t num_times = offsets ? total_points : points_per_trajectory;
+        for (s = 0; s < num_states; ++s)
+            for (point = 0; point < total_points; ++point) {
+                const float v = reference[s * total_points + point];
+                invalid_data |= !isfinite(v) && !(allow_missing && isnan(v));
+            }
+        for (point = 0; point < num_times; ++point) invalid_data |= !isfinite(times[point]);
+        if (invalid_data) {
+            for (sys = 0; sys < num_systems; ++sys) { scores[sys] = FLT_MAX; if (scores64) scores64[sys] = (double)FLT_MAX; }
+            return SECANT_SUCCESS;
+        }
+    }
     r = so_programs_open(&p, routine_blob, routine_off, num_routines, rhs_blob, rhs_off, num_systems * num_states);
     memset(&env, 0, sizeof(env));
     env.routines = p.routines; env.num_routines = num_routines; env.arity = p.arity;
@@ -604,17 +626,22 @@ SO_EXPORT SecantResult so_rk4_score(const uint8_t* routine_blob, const uint64_t*
     for (sys = 0; r == SECANT_SUCCESS && sys < num_systems; ++sys) {
         float sq = 0.0f;
         double sq64 = 0.0; /* same residuals accumulated in binary64, free of summation-order error */
-        size_t residuals = 0;
+        size_t residuals = 0, scored_points = 0, expected = 0;
         int valid = 1;
         env.constants = num_constants ? constants + sys * system_constant_stride : NULL;
         for (tr = 0; r == SECANT_SUCCESS && tr < num_trajectories; ++tr) {
-            const size_t first = tr * points_per_trajectory;
+            const size_t begin = offsets ? offsets[tr] : tr * points_per_trajectory;
+            const size_t end = offsets ? offsets[tr + 1] : begin + points_per_trajectory;
+            if (offsets) {
+                if (begin != expected || end <= begin || end > total_points) { valid = 0; break; }
+                expected = end;
+            }
             for (s = 0; s < num_states; ++s) {
-                state[s] = reference[s * total_points + first];
+                state[s] = reference[s * total_points + begin];
                 valid = valid && isfinite(state[s]);
             }
-            for (k = 1; r == SECANT_SUCCESS && k < points_per_trajectory; ++k) {
-                const float interval = times[k] - times[k - 1];
+            for (point = begin + 1; r == SECANT_SUCCESS && point < end; ++point) {
+                const float interval = offsets ? times[point] - times[point - 1] : times[point - begin] - times[point - begin - 1];
                 const float h = interval / (float)substeps;
                 const float half = 0.5f * h, sixth = h / 6.0f;
                 valid = valid && isfinite(interval) && interval > 0.0f && h > 0.0f;
@@ -632,20 +659,51 @@ SO_EXPORT SecantResult so_rk4_score(const uint8_t* routine_blob, const uint64_t*
                     for (s = 0; s < num_states; ++s) state[s] = fmaf(sixth, sum[s], base[s]);
                 }
                 for (s = 0; s < num_states; ++s) valid = valid && isfinite(state[s]);
+                ++scored_points;
                 for (s = 0; s < num_states; ++s) {
-                    const float err = state[s] - reference[s * total_points + first + k];
-                    sq = fmaf(err, err, sq);
-                    sq64 += (double)err * (double)err;
-                    ++residuals;
+                    const float ref = reference[s * total_points + point];
+                    if (allow_missing && isnan(ref)) continue;
+                    {
+                        const float err = state[s] - ref;
+                        sq = fmaf(err, err, sq);
+                        sq64 += (double)err * (double)err;
+                        ++residuals;
+                    }
                 }
             }
         }
         if (r != SECANT_SUCCESS) break;
-        scores[sys] = (valid && residuals && isfinite(sq)) ? sq / (float)residuals : FLT_MAX;
-        if (scores64) scores64[sys] = (valid && residuals && isfinite(sq)) ? sq64 / (double)residuals : (double)FLT_MAX;
+        valid = valid && (!offsets || expected == total_points) && scored_points && residuals;
+        scores[sys] = (valid && isfinite(sq)) ? sq / (float)residuals : FLT_MAX;
+        if (scores64) scores64[sys] = (valid && isfinite(sq)) ? sq64 / (double)residuals : (double)FLT_MAX;
     }
     so_programs_close(&p);
     return r;
+}
+
+SO_EXPORT SecantResult so_rk4_score(const uint8_t* routine_blob, const uint64_t* routine_off, size_t num_routines,
+                                    const uint8_t* rhs_blob, const uint64_t* rhs_off, size_t num_systems,
+                                    size_t num_states, size_t num_constants, const float* constants,
+                                    size_t system_constant_stride, const float* reference, size_t num_trajectories,
+                                    size_t points_per_trajectory, const float* times, size_t substeps, uint32_t toggle_bits,
+                                    uint32_t permutation, float* scores, double* scores64) {
+    return so_rk4_general(routine_blob, routine_off, num_routines, rhs_blob, rhs_off, num_systems, num_states, num_constants,
+                          constants, system_constant_stride, reference, num_trajectories, points_per_trajectory, NULL, 0, 0,
+                          times, substeps, toggle_bits, permutation, scores, scores64);
+}
+
+/* Ragged trajectories, per-point times, optional missing observations. */
+SO_EXPORT SecantResult so_rk4_score_ragged(const uint8_t* routine_blob, const uint64_t* routine_off, size_t num_routines,
+                                           const uint8_t* rhs_blob, const uint64_t* rhs_off, size_t num_systems,
+                                           size_t num_states, size_t num_constants, const float* constants,
+                                           size_t system_constant_stride, const float* reference, size_t num_trajectories,
+                                           const uint32_t* offsets, size_t total_points, int allow_missing, const float* times,
+                                           size_t substeps, uint32_t toggle_bits, uint32_t permutation, float* scores,
+                                           double* scores64) {
+    if (!offsets) return SECANT_ERROR_INVALID_VALUE;
+    return so_rk4_general(routine_blob, routine_off, num_routines, rhs_blob, rhs_off, num_systems, num_states, num_constants,
+                          constants, system_constant_stride, reference, num_trajectories, 0, offsets, total_points,
+                          allow_missing, times, substeps, toggle_bits, permutation, scores, scores64);
 }
 
 /* Evaluate one program once; the smallest building block, used by unit tests. */

@@ -251,12 +251,23 @@ def sse_slack(packed, x, y, banks, num_constants, toggle_bits, program_bank_stri
 
 
 def oracle_rk4(packed, num_states, reference, num_trajectories, times, constants=None, substeps=1, toggle_bits=0,
-               permutation=0, want64=False):
-    """RK4 rollout scores of the CPU restatement, one per system (single bank per system)."""
+               permutation=0, want64=False, offsets=None, allow_missing=False):
+    """RK4 rollout scores of the CPU restatement, one per system (single bank per system).
+    With offsets (uint32[num_trajectories + 1]) the ragged form: times and reference are per
+    concatenated point."""
     systems = len(packed.asts) // num_states
     K = constants.shape[1] if constants is not None else 0
     scores = np.zeros(systems, dtype=np.float32)
     scores64 = np.zeros(systems, dtype=np.float64)
+    if offsets is not None:
+        offsets = np.ascontiguousarray(offsets, dtype=np.uint32)
+        code = oracle().so_rk4_score_ragged(*blob_args(packed)[:5], C.c_size_t(systems), C.c_size_t(num_states), C.c_size_t(K),
+                                            fptr(constants) if K else None, C.c_size_t(K), fptr(reference),
+                                            C.c_size_t(len(offsets) - 1), offsets.ctypes.data_as(C.POINTER(C.c_uint32)),
+                                            C.c_size_t(len(times)), C.c_int(1 if allow_missing else 0), fptr(times),
+                                            C.c_size_t(substeps), C.c_uint32(toggle_bits), C.c_uint32(permutation),
+                                            fptr(scores), scores64.ctypes.data_as(F64P))
+        return (code, scores, scores64) if want64 else (code, scores)
     code = oracle().so_rk4_score(*blob_args(packed)[:5], C.c_size_t(systems), C.c_size_t(num_states), C.c_size_t(K),
                                  fptr(constants) if K else None, C.c_size_t(K), fptr(reference), C.c_size_t(num_trajectories),
                                  C.c_size_t(len(times)), fptr(times), C.c_size_t(substeps), C.c_uint32(toggle_bits),

@@ -99,3 +99,51 @@ def test_banks_toggles_and_random_right_hand_sides(cuda):
         code, want = S.oracle_rk4(pop, S_, ref, ntraj, times, np.ascontiguousarray(banks[:, cfg >> bits, :]), 2, bits, cfg & 1)
         assert code == 0
         assert np.allclose(got[:, cfg], want, rtol=2e-4, atol=1e-6), cfg
+
+
+def test_reference_launch_layout_ragged_trajectories_and_invalid_matrix(cuda):
+    """The reference engine's own scoring test (projects/odezza/tests/o_scoring_cuda_test.c:97-186):
+    ragged trajectories, irregular times, two steps per observation, closed form 0.4375 * e^2, and
+    every invalid variation scores FLT_MAX."""
+    from test_rk4_cpu import invalid_launch_matrix, reference_launch_case
+    systems, reference, times, offsets, constants = reference_launch_case()
+    off = torch.tensor(offsets.astype(np.int32), device="cuda")
+    got = rk4_score(systems, 1, dev(reference), dev(times), dev(constants[:, None, :]), 1, steps_per_observation=2,
+                    offsets=off).cpu().numpy()[:, 0]
+    assert np.allclose(got, [0.4375 * e * e for e in range(4)], atol=2e-6)
+    for oo, tt, rr in invalid_launch_matrix():
+        got = rk4_score(systems, 1, dev(rr), dev(tt), dev(constants[:, None, :]), 1, steps_per_observation=2,
+                        offsets=torch.tensor(oo.astype(np.int32), device="cuda")).cpu().numpy()
+        assert np.all(got == FLT_MAX), (oo, tt, rr)
+
+
+def test_ragged_missing_observations_against_the_oracle(cuda):
+    """Random ragged layout (1 to 40 points per trajectory, 150 trajectories so that several
+    128-trajectory groups and idle lanes occur), irregular steps, a tenth of the later observations
+    missing; damped linear systems with per-system coefficients."""
+    rng = np.random.default_rng(12)
+    lengths = rng.integers(1, 41, size=150)
+    lengths[5] = 1                                                      # a singleton: nothing to score, still validated
+    offsets = np.concatenate([[0], np.cumsum(lengths)]).astype(np.uint32)
+    total = int(offsets[-1])
+    times = np.concatenate([np.cumsum(rng.uniform(0.01, 0.08, size=n)) for n in lengths]).astype(np.float32)
+    reference = rng.normal(0, 1, size=(2, total)).astype(np.float32)
+    later = np.ones(total, dtype=bool); later[offsets[:-1]] = False
+    holes = later & (rng.random(total) < 0.1)
+    reference[0, holes] = np.nan
+    reference[1, np.roll(holes, 3) & later] = np.nan
+    col, bank, op = P.col, P.bank, P.op
+    n_sys = 20                                                           # x' = a y - b x, y' = -a x - b y
+    pop = P.PackedPrograms([bank(0) + col(1) + op("MUL") + bank(1) + col(0) + op("MUL") + op("SUB") + P.RET,
+                            bank(0) + col(0) + op("MUL") + op("NEG") + bank(1) + col(1) + op("MUL") + op("SUB") + P.RET] * n_sys)
+    coeffs = np.stack([rng.uniform(0.5, 3, n_sys), rng.uniform(0.1, 1, n_sys)], axis=1).astype(np.float32)
+    code, want, want64 = S.oracle_rk4(pop, 2, reference, len(lengths), times, coeffs, substeps=3, want64=True,
+                                      offsets=offsets, allow_missing=True)
+    assert code == 0 and np.all(want != FLT_MAX)
+    off = torch.tensor(offsets.astype(np.int32), device="cuda")
+    got = rk4_score(pop, 2, dev(reference), dev(times), dev(coeffs[:, None, :]), 2, steps_per_observation=3, offsets=off,
+                    allow_missing=True).cpu().numpy()[:, 0]
+    assert np.allclose(got, want64, rtol=1e-4, atol=1e-7)
+    strict = rk4_score(pop, 2, dev(reference), dev(times), dev(coeffs[:, None, :]), 2, steps_per_observation=3,
+                       offsets=off).cpu().numpy()
+    assert np.all(strict == FLT_MAX)                                     # NaN observations need the opt-in
