@@ -19,8 +19,9 @@
  * (tests/toggle_fixture.h closed forms, tests/toggle_test.c exact affine values and error
  * cases, tests/cpu_test.c closed forms) and, where the reference tree is available, against
  * the reference's s_cpu.c compiled unmodified (oracle/_ref/libsecant_ref.so).  The RK4
- * scorer has no general reference implementation to run; it is pinned on the reference's
- * closed-form test value only (see so_rk4_score).
+ * scorer has no general reference implementation to run; it is pinned on the reference's own
+ * launch test data, closed-form value and invalid-data matrix
+ * (projects/odezza/tests/o_scoring_cuda_test.c:97-186), parity otherwise unpinned.
  *
  * Arithmetic contract: IEEE binary32, libm for transcendental functions, no contraction
  * of a*b+c except where the program says FMA.  Compile with -ffp-contract=off.
@@ -579,8 +580,8 @@ SO_EXPORT size_t so_topk(const float* scores, size_t count, size_t k, uint64_t* 
  * Transcendental opcodes are evaluated with libm here; a device implementation that
  * wants bit-identical chaotic rollouts must restrict right-hand sides to exactly
  * rounded operations (add, sub, mul, div, fma, sqrt, rcp, neg, abs, min, max).
- * Parity: unpinned beyond the closed-form case in the test-suite (the reference has no
- * general fp32 host scorer to run). */
+ * Parity: unpinned beyond the reference's closed-form value and invalid-data matrix in the
+ * test-suite (the reference has no general fp32 host scorer to run). */
 /* General form.  offsets == NULL: every trajectory has points_per_trajectory points and
  * times[points_per_trajectory] is shared.  offsets != NULL: the reference engine's launch layout
  * (projects/odezza/core/odezza.h:275-289, checks and loop of
