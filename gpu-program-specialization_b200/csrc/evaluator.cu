@@ -557,6 +557,18 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
  * launch so that as many warps as possible fit the SM's shared memory. */
 constexpr int kRk4MaxWarps = 16;
 
+/* projects/odezza/core/o_sampled_constants_source.h:32-44 */
+__device__ __forceinline__ float sampled_constant(const Rk4Problem& prob, unsigned long long index, uint32_t bank) {
+    const SecantB200SampledParameter p = prob.sampled[index];
+    if (!p.distribution) return p.shift;
+    const unsigned long long delta = (unsigned long long)bank * p.stride;
+    if (p.offset >= prob.pool_size || delta >= prob.pool_size - p.offset) return __int_as_float(0x7fc00000);
+    const float* pool = p.distribution == 1 ? prob.uniform_pool : p.distribution == 2 ? prob.normal_pool : nullptr;
+    if (!pool) return __int_as_float(0x7fc00000);
+    const float value = __fadd_rn(__fmul_rn(pool[p.offset + delta], p.scale), p.shift);
+    return fminf(p.upper, fmaxf(p.lower, value));
+}
+
 __global__ void __launch_bounds__(kRk4MaxWarps * 32, 1)
 rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, uint32_t cst_bytes, uint32_t warp_bytes,
            uint32_t scratch_slot) {
@@ -590,10 +602,11 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, 
         }
         for (uint32_t e = lane; e < K + pr.n_affine + pr.n_lits; e += 32) {
             float v;
-            if (e < K) v = bank_ptr[e];
+            if (e < K) v = prob.sampled ? sampled_constant(prob, (unsigned long long)sys * K + e, bank) : bank_ptr[e];
             else if (e < K + pr.n_affine) {
                 const SbAffine a = batch.affines[pr.affine_off + e - K];
-                v = __fadd_rn(__fmul_rn(bank_ptr[a.slot], a.scale), a.offset);
+                const float slot = prob.sampled ? sampled_constant(prob, (unsigned long long)sys * K + a.slot, bank) : bank_ptr[a.slot];
+                v = __fadd_rn(__fmul_rn(slot, a.scale), a.offset);
             } else v = batch.lits[pr.lit_off + e - K - pr.n_affine];
             cst[e] = v;
         }

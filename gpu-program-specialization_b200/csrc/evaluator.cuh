@@ -4,6 +4,7 @@
 #ifndef SECANT_B200_EVALUATOR_CUH
 #define SECANT_B200_EVALUATOR_CUH
 
+#include "../../include/secant_b200.h"
 #include "record.h"
 
 #include <cuda_runtime.h>
@@ -94,6 +95,10 @@ struct Rk4Problem {
     uint32_t total_points;         /* concatenated points (both forms) */
     uint32_t allow_missing;        /* NaN reference values after a first point are unobserved */
     int* invalid_flag;             /* device word the validation kernel raises */
+    const SecantB200SampledParameter* sampled; /* [system][constant] descriptors, or null: explicit banks */
+    const float* uniform_pool;
+    const float* normal_pool;
+    unsigned long long pool_size;
     float* output;                 /* [system][configuration] */
     size_t output_ld;
 };

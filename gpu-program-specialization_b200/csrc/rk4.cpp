@@ -50,7 +50,11 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
         return run->reference.address && run->reference.leading_dimension >= total_points ? SECANT_ERROR_INSUFFICIENT_BUFFER : SECANT_ERROR_INVALID_VALUE;
     if (run->output.leading_dimension < configs || !run->output.address || run->output.address % 4) return SECANT_ERROR_INVALID_VALUE;
     if (run->output.num_elements < (run->num_systems - 1) * run->output.leading_dimension + configs) return SECANT_ERROR_INSUFFICIENT_BUFFER;
-    if (K) {
+    const bool sampled = run->sampled_parameters != 0;
+    if (sampled && (!K || run->sampled_parameters % 8 || run->uniform_pool % 4 || run->normal_pool % 4 ||
+                    (run->rng_pool_size && !run->uniform_pool && !run->normal_pool)))
+        return SECANT_ERROR_INVALID_VALUE;
+    if (K && !sampled) {
         if (run->constants.bank_stride < K || !run->constants.address || run->constants.address % 4) return SECANT_ERROR_INVALID_VALUE;
         const size_t per_system = run->system_bank_stride ? run->system_bank_stride : run->num_banks * run->constants.bank_stride;
         if (per_system < (run->num_banks - 1) * run->constants.bank_stride + K) return SECANT_ERROR_INVALID_VALUE;
@@ -134,6 +138,11 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
         p.total_points = (uint32_t)total_points;
         p.allow_missing = run->allow_missing_observations;
         p.invalid_flag = reinterpret_cast<int*>(d + o_flag);
+        p.sampled = reinterpret_cast<const SecantB200SampledParameter*>(run->sampled_parameters);
+        p.uniform_pool = reinterpret_cast<const float*>(run->uniform_pool);
+        p.normal_pool = reinterpret_cast<const float*>(run->normal_pool);
+        p.pool_size = run->rng_pool_size;
+        if (sampled) p.banks = nullptr;
         p.output = reinterpret_cast<float*>(run->output.address);
         p.output_ld = run->output.leading_dimension;
         e = launch_rk4(db, p, (size_t)limit, nullptr);

@@ -143,7 +143,13 @@ class Rk4Run(C.Structure):  # SecantB200Rk4Run
                 ("reference", DeviceMatrix), ("num_trajectories", _sz), ("points_per_trajectory", _sz),
                 ("times", C.c_size_t), ("steps_per_observation", _sz), ("output", DeviceMatrix),
                 ("trajectory_offsets", C.c_size_t), ("total_points", _sz), ("allow_missing_observations", _u32),
-                ("reserved3", _u32)]
+                ("reserved3", _u32), ("sampled_parameters", C.c_size_t), ("uniform_pool", C.c_size_t),
+                ("normal_pool", C.c_size_t), ("rng_pool_size", C.c_uint64)]
+
+
+class SampledParameter(C.Structure):  # SecantB200SampledParameter, layout of the reference's OdezzaSampledParameter
+    _fields_ = [("offset", C.c_uint64), ("stride", _u32), ("distribution", _u32), ("scale", C.c_float), ("shift", C.c_float),
+                ("lower", C.c_float), ("upper", C.c_float)]
 
 
 class Score(C.Structure):  # SecantB200Score, layout of the reference consumer's SRScore

@@ -248,7 +248,7 @@ def topk(scores, k):
 
 
 def rk4_score(packed, num_states, reference, times, constants=None, num_constants=0, num_banks=1, toggle_bits=0,
-              steps_per_observation=1, points_per_trajectory=None, offsets=None, allow_missing=False):
+              steps_per_observation=1, points_per_trajectory=None, offsets=None, allow_missing=False, sampled=None):
     """Fixed-step RK4 rollout scores [system][configuration] (extension API).
 
     packed: num_systems * num_states right-hand-side programs, system-major.
@@ -256,7 +256,9 @@ def rk4_score(packed, num_states, reference, times, constants=None, num_constant
     [points].  Ragged form (offsets given: CUDA int32/uint32 tensor [trajectories + 1]): reference
     is [state][concatenated points], times is [concatenated points]; with allow_missing NaN
     reference values after a trajectory's first point are unobserved.
-    constants: CUDA tensor [system][bank][slot] or None."""
+    constants: CUDA tensor [system][bank][slot] or None.
+    sampled: (descriptors, uniform_pool, normal_pool) instead of constants - a CUDA uint8 tensor
+    holding abi.SampledParameter[system][constant] and two CUDA float pools of equal size."""
     lib = abi.load()
     run = abi.Rk4Run()
     run.struct_size, run.version = C.sizeof(run), abi.RUN_VERSION
@@ -277,6 +279,11 @@ def rk4_score(packed, num_states, reference, times, constants=None, num_constant
         points = points_per_trajectory or times.numel()
         run.num_trajectories = reference.shape[-1] // points
         run.points_per_trajectory = points
+    if sampled is not None:
+        descriptors, uniform_pool, normal_pool = sampled
+        run.sampled_parameters = descriptors.data_ptr()
+        run.uniform_pool, run.normal_pool = uniform_pool.data_ptr(), normal_pool.data_ptr()
+        run.rng_pool_size = uniform_pool.numel()
     run.times = times.data_ptr()
     run.steps_per_observation = steps_per_observation
     out = torch.empty((systems, num_banks << toggle_bits), dtype=torch.float32, device=reference.device)

@@ -118,6 +118,18 @@ SECANT_DEC void secant_b200_runner_force_variant(SecantCubinRunner runner, int v
  * right-hand sides, but only exactly rounded operations (add, sub, mul, div, fma, sqrt, neg,
  * abs, min, max) reproduce a host rollout bit for bit, which chaotic systems need.
  */
+/* A coefficient drawn from a shared pool instead of an explicit bank table: layout and rule of the
+ * reference engine's OdezzaSampledParameter (projects/odezza/core/odezza.h:304-311,
+ * projects/odezza/core/o_sampled_constants_source.h:32-44).  distribution 0: the value is `shift`
+ * for every bank; 1 / 2: pool = uniform / normal, value = clamp(pool[offset + bank * stride] * scale
+ * + shift, lower, upper) with the multiply and the add rounded separately; an index outside the
+ * pool or another distribution gives NaN (and with it an invalid score). */
+typedef struct SecantB200SampledParameter {
+    uint64_t offset;
+    uint32_t stride, distribution;
+    float scale, shift, lower, upper;
+} SecantB200SampledParameter;
+
 typedef struct SecantB200Rk4Run {
     uint32_t struct_size, version, flags, reserved;   /* version = SECANT_CUBIN_RUN_VERSION_3 */
     SecantAstProgramSet programs;
@@ -134,6 +146,10 @@ typedef struct SecantB200Rk4Run {
     uintptr_t trajectory_offsets;
     size_t total_points;
     uint32_t allow_missing_observations, reserved3;
+    /* non-zero sampled_parameters: device SecantB200SampledParameter[num_systems][num_constants];
+     * `constants` is then unused and may be zero; the pools hold rng_pool_size floats each */
+    uintptr_t sampled_parameters, uniform_pool, normal_pool;
+    uint64_t rng_pool_size;
 } SecantB200Rk4Run;
 SECANT_DEC SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run);
 

@@ -275,3 +275,27 @@ def oracle_rk4(packed, num_states, reference, num_trajectories, times, constants
     if want64:
         return code, scores, scores64
     return code, scores
+
+
+def sampled_constants(descriptors, uniform_pool, normal_pool, num_banks):
+    """Explicit [system][bank][constant] table of sampled coefficients: the rule of the reference
+    engine (projects/odezza/core/o_sampled_constants_source.h:32-44) restated in float32 numpy.
+    descriptors: [system][constant] tuples (offset, stride, distribution, scale, shift, lower, upper)."""
+    systems, K = len(descriptors), len(descriptors[0])
+    out = np.zeros((systems, num_banks, K), dtype=np.float32)
+    size = len(uniform_pool)
+    for i in range(systems):
+        for k in range(K):
+            offset, stride, dist, scale, shift, lower, upper = descriptors[i][k]
+            for b in range(num_banks):
+                if dist == 0:
+                    out[i, b, k] = np.float32(shift)
+                    continue
+                delta = b * stride
+                pool = uniform_pool if dist == 1 else normal_pool if dist == 2 else None
+                if offset >= size or delta >= size - offset or pool is None:
+                    out[i, b, k] = np.nan
+                    continue
+                v = np.float32(np.float32(pool[offset + delta]) * np.float32(scale)) + np.float32(shift)
+                out[i, b, k] = min(np.float32(upper), max(np.float32(lower), np.float32(v)))
+    return out

@@ -147,3 +147,42 @@ def test_ragged_missing_observations_against_the_oracle(cuda):
     strict = rk4_score(pop, 2, dev(reference), dev(times), dev(coeffs[:, None, :]), 2, steps_per_observation=3,
                        offsets=off).cpu().numpy()
     assert np.all(strict == FLT_MAX)                                     # NaN observations need the opt-in
+
+
+def test_sampled_parameter_pools_match_explicit_banks(cuda):
+    """Coefficients drawn from shared pools (the reference engine's sampled parameters) must give the
+    scores of the explicit bank table built with the same rule, bank by bank; a descriptor that
+    points outside the pool makes that configuration invalid."""
+    import ctypes as C
+    from secant_b200 import abi
+    rng = np.random.default_rng(21)
+    n_sys, nb, K, pool_size = 12, 5, 2, 64
+    uniform = rng.random(pool_size).astype(np.float32)
+    normal = rng.normal(0, 1, pool_size).astype(np.float32)
+    desc = [[(int(rng.integers(0, 40)), int(rng.integers(1, 5)), 1, 2.5, 0.5, 0.6, 2.8),        # a in [0.6, 2.8]
+             (int(rng.integers(0, 40)), int(rng.integers(1, 5)), 2, 0.3, 0.5, 0.1, 1.0)] for _ in range(n_sys)]
+    desc[3][1] = (0, 0, 0, 0.0, 0.25, 0.0, 0.0)          # fixed shift, the same for every bank
+    desc[7][0] = (60, 3, 1, 1.0, 0.0, 0.0, 9.0)          # banks 2.. fall outside the pool
+    raw = (abi.SampledParameter * (n_sys * K))()
+    for i in range(n_sys):
+        for k in range(K):
+            raw[i * K + k] = abi.SampledParameter(*desc[i][k])
+    blob = torch.tensor(np.frombuffer(bytes(raw), dtype=np.uint8).copy(), device="cuda")
+    table = S.sampled_constants(desc, uniform, normal, nb)
+    times = (np.arange(41, dtype=np.float32) * np.float32(0.05)).astype(np.float32)
+    reference = np.concatenate([np.cos(times)[None, :], -np.sin(times)[None, :]]).astype(np.float32)
+    reference = np.concatenate([reference, 0.5 * reference], axis=1)                     # two trajectories
+    col, bank, op = P.col, P.bank, P.op
+    pop = P.PackedPrograms([bank(0) + col(1) + op("MUL") + bank(1) + col(0) + op("MUL") + op("SUB") + P.RET,
+                            bank(0) + col(0) + op("MUL") + op("NEG") + bank(1) + col(1) + op("MUL") + op("SUB") + P.RET] * n_sys)
+    got = rk4_score(pop, 2, dev(reference), dev(times), None, K, num_banks=nb,
+                    sampled=(blob, dev(uniform), dev(normal))).cpu().numpy()
+    explicit = rk4_score(pop, 2, dev(reference), dev(times), dev(table), K, num_banks=nb).cpu().numpy()
+    assert np.array_equal(got, explicit)                                                   # same constants, same bits
+    assert np.all(got[7, 2:] == FLT_MAX) and np.all(got[7, :2] != FLT_MAX)
+    for b in range(nb):
+        code, want, want64 = S.oracle_rk4(pop, 2, reference, 2, times, np.ascontiguousarray(table[:, b, :]), want64=True)
+        assert code == 0
+        assert np.array_equal(got[:, b] == FLT_MAX, want == FLT_MAX)
+        fin = want != FLT_MAX
+        assert np.allclose(got[fin, b], want64[fin], rtol=1e-4, atol=1e-7)
