@@ -139,6 +139,69 @@ constexpr size_t kStaticMaxK = 1024;
 constexpr size_t kStaticWords = (kStaticMaxCount / kTile) * kStaticMaxK + ((kStaticMaxCount / kTile) * kStaticMaxK / kTile) * kStaticMaxK;
 static __device__ __align__(256) unsigned long long g_topk_static_scratch[kStaticWords];
 
+/* ---- grouped top-k of a [system][configuration] score grid ----------------------------------
+ * Rules of the reference engine's reducer (projects/odezza/core/o_score_reduce.cu:36-62,
+ * projects/odezza/core/odezza.h:438-486): a score is valid when 0 <= score < FLT_MAX (NaN,
+ * infinities, FLT_MAX and negatives are not; -0 is, and orders as +0); winners are ordered by
+ * (score, flat index); unfilled ranks are {FLT_MAX, 0, UINT64_MAX}; counts are valid, invalid and
+ * finite-negative scores of the group.  Groups: 0 = system, 1 = (system, permutation) over banks,
+ * 2 = one global group.  One CTA per group keeps the best k keys in shared memory and merges the
+ * group's scores into them 1024 - k at a time with a bitonic sort (the reference sorts with CUB). */
+constexpr int kGroupThreads = 256, kGroupKeys = 1024;
+
+__device__ __forceinline__ unsigned long long group_flat_index(unsigned long long group, unsigned long long e, unsigned long long configs,
+                                                              unsigned long long perms, unsigned mode) {
+    return mode == 2 ? e : mode == 0 ? group * configs + e : (group / perms) * configs + e * perms + group % perms;
+}
+
+__global__ void __launch_bounds__(kGroupThreads)
+grouped_topk_kernel(const float* __restrict__ scores, unsigned long long elements, unsigned long long configs, unsigned long long perms,
+                    unsigned mode, unsigned k, SecantB200Winner* winners, SecantB200ScoreCounts* counts) {
+    __shared__ unsigned long long keys[kGroupKeys];
+    __shared__ unsigned long long tally[3];
+    const unsigned long long group = blockIdx.x;
+    const unsigned fresh = kGroupKeys - k; /* scores merged per round */
+    for (int i = threadIdx.x; i < kGroupKeys; i += kGroupThreads) keys[i] = ~0ull;
+    if (threadIdx.x < 3) tally[threadIdx.x] = 0;
+    unsigned long long valid = 0, invalid = 0, negative = 0;
+    for (unsigned long long base = 0; base < elements; base += fresh) {
+        __syncthreads();
+        for (unsigned i = threadIdx.x; i < fresh; i += kGroupThreads) {
+            const unsigned long long e = base + i;
+            unsigned long long key = ~0ull;
+            if (e < elements) {
+                const float f = scores[group_flat_index(group, e, configs, perms, mode)];
+                const bool ok = f >= 0.0f && f < 3.402823466e+38f;
+                if (ok) { ++valid; key = ((unsigned long long)__float_as_uint(f == 0.0f ? 0.0f : f) << 32) | (unsigned)e; }
+                else { ++invalid; negative += (f < 0.0f && f > -CUDART_INF_F) ? 1 : 0; }
+            }
+            keys[k + i] = key;
+        }
+        for (unsigned size = 2; size <= kGroupKeys; size <<= 1)
+            for (unsigned stride = size >> 1; stride > 0; stride >>= 1) {
+                __syncthreads();
+                for (unsigned t = threadIdx.x; t < kGroupKeys / 2; t += kGroupThreads) {
+                    const unsigned lo = 2 * t - (t & (stride - 1)), hi = lo + stride;
+                    const bool up = (lo & size) == 0;
+                    const unsigned long long a = keys[lo], b = keys[hi];
+                    if ((a > b) == up) { keys[lo] = b; keys[hi] = a; }
+                }
+            }
+    }
+    atomicAdd(&tally[0], valid); atomicAdd(&tally[1], invalid); atomicAdd(&tally[2], negative);
+    __syncthreads();
+    for (unsigned rank = threadIdx.x; rank < k; rank += kGroupThreads) {
+        const unsigned long long key = keys[rank];
+        SecantB200Winner w{3.402823466e+38f, 0u, ~0ull};
+        if (key != ~0ull) {
+            w.score_index = group_flat_index(group, key & 0xffffffffull, configs, perms, mode);
+            w.mse = scores[w.score_index]; /* the original bits, signed zero included */
+        }
+        winners[group * k + rank] = w;
+    }
+    if (threadIdx.x == 0) counts[group] = SecantB200ScoreCounts{tally[0], tally[1], tally[2]};
+}
+
 }  // namespace
 
 /* Runs the selection rounds; `scratch` must hold secant_b200_topk_scratch_elements(count, k)
@@ -164,6 +227,26 @@ static cudaError_t topk_rounds(const float* scores, unsigned long long count, un
 }
 
 extern "C" {
+
+SecantResult secant_b200_grouped_topk(uintptr_t scores, size_t num_systems, size_t num_banks, uint32_t toggle_bits, uint32_t grouping,
+                                      uint32_t k, uintptr_t winners, uintptr_t counts, void* stream) {
+    if (!scores || !winners || !counts || scores % 4 || winners % 8 || counts % 8 || !num_systems || !num_banks || toggle_bits > 32 ||
+        grouping > SECANT_B200_GROUP_GLOBAL || !k || k > 256)
+        return SECANT_ERROR_INVALID_VALUE;
+    const unsigned long long perms = 1ull << toggle_bits;
+    if (num_banks > (~0ull >> toggle_bits) || (num_banks << toggle_bits) > ~0ull / num_systems) return SECANT_ERROR_OVERFLOW;
+    const unsigned long long configs = (unsigned long long)num_banks << toggle_bits;
+    unsigned long long groups, elements;
+    if (grouping == SECANT_B200_GROUP_BY_SYSTEM) { groups = num_systems; elements = configs; }
+    else if (grouping == SECANT_B200_GROUP_BY_SYSTEM_PERMUTATION) { groups = num_systems * perms; elements = num_banks; }
+    else { groups = 1; elements = configs * num_systems; }
+    if (groups > 0x7fffffffull || elements > 0xffffffffull) return SECANT_ERROR_OVERFLOW; /* grid size, 32-bit key index */
+    grouped_topk_kernel<<<(unsigned)groups, kGroupThreads, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const float*>(scores), elements, configs, perms, grouping, k, reinterpret_cast<SecantB200Winner*>(winners),
+        reinterpret_cast<SecantB200ScoreCounts*>(counts));
+    sb::note_kernel_launches(1);
+    return cudaGetLastError() == cudaSuccess ? SECANT_SUCCESS : SECANT_ERROR_DRIVER_FAILED;
+}
 
 size_t secant_b200_topk_scratch_elements(size_t count, size_t k) {
     const size_t first = tiles_of(count) * k;

@@ -152,6 +152,10 @@ class SampledParameter(C.Structure):  # SecantB200SampledParameter, layout of th
                 ("lower", C.c_float), ("upper", C.c_float)]
 
 
+class Winner(C.Structure):  # SecantB200Winner
+    _fields_ = [("mse", C.c_float), ("reserved", _u32), ("score_index", C.c_uint64)]
+
+
 class Score(C.Structure):  # SecantB200Score, layout of the reference consumer's SRScore
     _fields_ = [("sse", C.c_float), ("reserved", _u32), ("configuration", C.c_uint64), ("valid_configurations", C.c_uint64)]
 
@@ -205,6 +209,8 @@ EXPORTED = {
     "secant_b200_population_destroy": (C.c_int32, [C.c_void_p]),
     "secant_b200_runner_force_variant": (None, [C.c_void_p, C.c_int]),
     "secant_b200_runner_set_math": (C.c_int32, [C.c_void_p, C.c_uint32]),
+    "secant_b200_grouped_topk": (C.c_int32, [C.c_size_t, _sz, _sz, C.c_uint32, C.c_uint32, C.c_uint32, C.c_size_t, C.c_size_t,
+                                 C.c_void_p]),
     "secant_b200_rk4_score": (C.c_int32, [C.c_void_p]),
     "secant_b200_best_config": (C.c_int32, [C.c_size_t, _sz, _sz, _sz, C.c_size_t, C.c_void_p]),
     "secant_b200_topk": (C.c_int32, [C.c_size_t, _sz, _sz, C.c_size_t, C.c_size_t, C.c_void_p]),

@@ -290,3 +290,19 @@ def rk4_score(packed, num_states, reference, times, constants=None, num_constant
     run.output = _matrix(out)
     abi.check(lib.secant_b200_rk4_score(C.byref(run)), "secant_b200_rk4_score")
     return out
+
+
+def grouped_topk(scores, num_systems, num_banks, toggle_bits, grouping, k):
+    """Top-k per group of a contiguous [system][configuration] CUDA score grid (extension API).
+    Returns (mse [group][k] float32, score_index [group][k] int64 with -1 for unfilled ranks,
+    counts [group][3] int64 = valid, invalid, negative)."""
+    lib = abi.load()
+    perms = 1 << toggle_bits
+    groups = num_systems if grouping == 0 else num_systems * perms if grouping == 1 else 1
+    winners = torch.empty((groups, k, 2), dtype=torch.int64, device=scores.device)     # 16-byte records
+    counts = torch.empty((groups, 3), dtype=torch.int64, device=scores.device)
+    abi.check(lib.secant_b200_grouped_topk(scores.data_ptr(), num_systems, num_banks, toggle_bits, grouping, k,
+                                           winners.data_ptr(), counts.data_ptr(), torch.cuda.current_stream().cuda_stream),
+              "secant_b200_grouped_topk")
+    mse = winners.view(torch.float32)[:, :, 0].clone()          # first 4 bytes of every 16-byte record
+    return mse, winners[:, :, 1].clone(), counts

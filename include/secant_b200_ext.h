@@ -154,6 +154,29 @@ typedef struct SecantB200Rk4Run {
 SECANT_DEC SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run);
 
 /*
+ * Grouped top-k over a score grid [system][configuration] (contiguous, configuration = bank *
+ * 2^toggle_bits + permutation), the reduction of the reference engine
+ * (projects/odezza/core/odezza.h:438-486, projects/odezza/core/o_score_reduce.cu:36-62):
+ * grouping 0 = one group per system, 1 = one per (system, permutation) ranking the banks,
+ * 2 = one global group.  A score is valid when 0 <= score < FLT_MAX; winners[group][k] are ordered
+ * by (score, flat index) and carry the original score bits and the flat element index; unfilled
+ * ranks are {FLT_MAX, 0, UINT64_MAX}; counts[group] = valid, invalid and finite-negative scores.
+ * 1 <= k <= 256.  winners and counts are device addresses, 8-byte aligned.  Asynchronous on
+ * `stream`; no allocation.
+ */
+typedef struct SecantB200Winner {
+    float mse;
+    uint32_t reserved;
+    uint64_t score_index;
+} SecantB200Winner;
+typedef struct SecantB200ScoreCounts {
+    uint64_t valid, invalid, negative;
+} SecantB200ScoreCounts;
+enum { SECANT_B200_GROUP_BY_SYSTEM = 0, SECANT_B200_GROUP_BY_SYSTEM_PERMUTATION = 1, SECANT_B200_GROUP_GLOBAL = 2 };
+SECANT_DEC SecantResult secant_b200_grouped_topk(uintptr_t scores, size_t num_systems, size_t num_banks, uint32_t toggle_bits,
+                                                 uint32_t grouping, uint32_t k, uintptr_t winners, uintptr_t counts, void* stream);
+
+/*
  * Best configuration of every score vector, on the device.  `scores` is [vector][configuration]
  * float32 with `leading_dimension` elements between vectors (for a toggle-SSE grid with one
  * target: vector = program).  A score is valid when finite and >= 0; the winner is the

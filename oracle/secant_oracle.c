@@ -707,6 +707,43 @@ SO_EXPORT SecantResult so_rk4_score_ragged(const uint8_t* routine_blob, const ui
                           allow_missing, times, substeps, toggle_bits, permutation, scores, scores64);
 }
 
+/* Grouped top-k of a [system][configuration] score grid: rules of the reference engine's reducer
+ * (projects/odezza/core/o_score_reduce.cu:36-62): valid when 0 <= score < FLT_MAX, -0 orders as
+ * +0, winners by (score, flat index), unfilled ranks {FLT_MAX, UINT64_MAX}, counts of valid,
+ * invalid and finite-negative scores.  grouping 0: per system, 1: per (system, permutation) over
+ * banks, 2: global.  winners_mse / winners_index are [group][k], counts is [group][3]. */
+SO_EXPORT SecantResult so_grouped_topk(const float* scores, size_t num_systems, size_t num_banks, uint32_t toggle_bits,
+                                       uint32_t grouping, size_t k, float* winners_mse, uint64_t* winners_index, uint64_t* counts) {
+    const uint64_t perms = (uint64_t)1 << toggle_bits, configs = (uint64_t)num_banks << toggle_bits;
+    const uint64_t groups = grouping == 0 ? num_systems : grouping == 1 ? num_systems * perms : 1;
+    const uint64_t elements = grouping == 0 ? configs : grouping == 1 ? num_banks : configs * num_systems;
+    uint64_t g, e, r;
+    if (!scores || !k || grouping > 2 || !winners_mse || !winners_index || !counts) return SECANT_ERROR_INVALID_VALUE;
+    for (g = 0; g < groups; ++g) {
+        uint64_t valid = 0, invalid = 0, negative = 0;
+        for (r = 0; r < k; ++r) { winners_mse[g * k + r] = FLT_MAX; winners_index[g * k + r] = UINT64_MAX; }
+        for (e = 0; e < elements; ++e) {
+            const uint64_t index = grouping == 2 ? e : grouping == 0 ? g * configs + e : (g / perms) * configs + e * perms + g % perms;
+            const float f = scores[index];
+            uint64_t at;
+            if (!(f >= 0 && f < FLT_MAX)) { ++invalid; negative += isfinite(f) && f < 0; continue; }
+            ++valid;
+            /* insertion into the sorted prefix; elements arrive in flat-index order, so a strict
+             * comparison keeps the lower index first on ties */
+            for (at = k; at > 0; --at) {
+                const float w = winners_mse[g * k + at - 1];
+                if (winners_index[g * k + at - 1] != UINT64_MAX && !((f == 0 ? 0.f : f) < (w == 0 ? 0.f : w))) break;
+            }
+            if (at == k) continue;
+            for (r = k - 1; r > at; --r) { winners_mse[g * k + r] = winners_mse[g * k + r - 1]; winners_index[g * k + r] = winners_index[g * k + r - 1]; }
+            winners_mse[g * k + at] = f;
+            winners_index[g * k + at] = index;
+        }
+        counts[g * 3] = valid; counts[g * 3 + 1] = invalid; counts[g * 3 + 2] = negative;
+    }
+    return SECANT_SUCCESS;
+}
+
 /* Evaluate one program once; the smallest building block, used by unit tests. */
 SO_EXPORT SecantResult so_eval(const uint8_t* routine_blob, const uint64_t* routine_off, size_t num_routines,
                                const uint8_t* program, size_t num_columns, size_t num_constants, const float* input,

@@ -83,3 +83,32 @@ def test_topk_all_invalid_orders_by_index(cuda):
     scores = torch.full((5000,), float("nan"), device="cuda")
     idx, _ = R.topk(scores, 16)
     assert idx.cpu().tolist() == list(range(16))
+
+
+def oracle_grouped(grid, num_banks, bits, grouping, k):
+    systems = grid.shape[0]
+    perms = 1 << bits
+    groups = systems if grouping == 0 else systems * perms if grouping == 1 else 1
+    mse = np.zeros((groups, k), dtype=np.float32)
+    idx = np.zeros((groups, k), dtype=np.uint64)
+    counts = np.zeros((groups, 3), dtype=np.uint64)
+    code = S.oracle().so_grouped_topk(S.fptr(grid), C.c_size_t(systems), C.c_size_t(num_banks), C.c_uint32(bits),
+                                      C.c_uint32(grouping), C.c_size_t(k), S.fptr(mse), idx.ctypes.data_as(S.U64P),
+                                      counts.ctypes.data_as(S.U64P))
+    assert code == 0
+    return mse, idx, counts
+
+
+@pytest.mark.parametrize("grouping", [0, 1, 2])
+@pytest.mark.parametrize("systems,num_banks,bits,k", [(1, 1, 0, 1), (7, 13, 3, 4), (5, 300, 2, 256), (40, 3, 1, 9)])
+def test_grouped_topk_matches_the_reference_rule(cuda, grouping, systems, num_banks, bits, k):
+    rng = np.random.default_rng(systems * 1000 + num_banks * 10 + bits + grouping)
+    grid = noisy_scores(rng, (systems, num_banks << bits))
+    flat = grid.reshape(-1)
+    flat[rng.integers(0, flat.size, flat.size // 20 + 1)] = np.float32(3.402823466e38)     # FLT_MAX is not a score
+    grid[0, :] = np.nan                                                                   # a system with no valid score
+    mse, idx, counts = R.grouped_topk(torch.tensor(grid, device="cuda"), systems, num_banks, bits, grouping, k)
+    want_mse, want_idx, want_counts = oracle_grouped(grid, num_banks, bits, grouping, k)
+    assert np.array_equal(idx.cpu().numpy().view(np.uint64), want_idx)
+    assert np.array_equal(mse.cpu().numpy().view(np.uint32), want_mse.view(np.uint32))     # original bits, -0 included
+    assert np.array_equal(counts.cpu().numpy().view(np.uint64), want_counts)

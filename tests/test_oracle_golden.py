@@ -152,3 +152,21 @@ def test_best_config_and_topk_rules():
     lib.so_topk.restype = C.c_size_t
     n = lib.so_topk(S.fptr(flat), C.c_size_t(8), C.c_size_t(4), idx.ctypes.data_as(S.U64P))
     assert n == 4 and idx.tolist() == [4, 1, 3, 7]
+
+
+def test_grouped_topk_rule_on_a_hand_checked_grid():
+    """Valid = 0 <= score < FLT_MAX, -0 orders as +0 and keeps its bits, ties go to the lower flat
+    index, unfilled ranks are {FLT_MAX, UINT64_MAX} (projects/odezza/core/o_score_reduce.cu:36-62)."""
+    import ctypes as C
+    grid = np.array([[3, 1, -0.0, 1], [np.nan, -2, 5, np.inf]], dtype=np.float32)
+    mse = np.zeros((2, 3), np.float32); idx = np.zeros((2, 3), np.uint64); counts = np.zeros((2, 3), np.uint64)
+    assert S.oracle().so_grouped_topk(S.fptr(grid), C.c_size_t(2), C.c_size_t(4), C.c_uint32(0), C.c_uint32(0), C.c_size_t(3),
+                                      S.fptr(mse), idx.ctypes.data_as(S.U64P), counts.ctypes.data_as(S.U64P)) == 0
+    assert idx.tolist() == [[2, 1, 3], [6, 2 ** 64 - 1, 2 ** 64 - 1]]
+    assert np.signbit(mse[0, 0]) and mse[0].tolist() == [0.0, 1.0, 1.0] and mse[1, 0] == 5 and mse[1, 1] == np.float32(3.402823466e38)
+    assert counts.tolist() == [[4, 0, 0], [1, 3, 1]]
+    # per (system, permutation): one toggle bit, two banks -> groups (s0,p0) (s0,p1) (s1,p0) (s1,p1), each over 2 banks
+    mse = np.zeros((4, 1), np.float32); idx = np.zeros((4, 1), np.uint64); counts = np.zeros((4, 3), np.uint64)
+    assert S.oracle().so_grouped_topk(S.fptr(grid), C.c_size_t(2), C.c_size_t(2), C.c_uint32(1), C.c_uint32(1), C.c_size_t(1),
+                                      S.fptr(mse), idx.ctypes.data_as(S.U64P), counts.ctypes.data_as(S.U64P)) == 0
+    assert idx[:, 0].tolist() == [2, 1, 6, 2 ** 64 - 1] and counts[:, 0].tolist() == [2, 2, 1, 0]
