@@ -44,7 +44,7 @@ from secant_b200 import abi, programs as P  # noqa: E402
 
 WORKLOAD = dict(name="configs[1] Secant-SR population scoring", programs=65536, max_tokens=32, slots=16, banks=64,
                 rows=1 << 20, features=8, seed=2)
-METRIC = "scored program-rows/sec"
+METRIC = "scored program·rows/sec"
 
 
 def hidden_target(x, seed, depth=6):
