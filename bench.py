@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (BASELINE.json configs[1], "Secant-SR population scoring"): P = 65,536 seeded
+Workload ("Secant-SR population scoring"): P = 65,536 seeded
 random postfix programs of at most 32 tokens over {+, -, *, protected /, sin, cos, exp,
 protected log}, 16 coefficient slots, 64 coefficient sets per program (per-program bank
 tables), N = 1,048,576 rows of F = 8 float32 features ~U[-3, 3], target = a hidden seeded
@@ -15,11 +15,12 @@ same top-1024.
 
 The line printed by rank 0:
   value       scored program-rows per second (programs x rows / time; each program-row
-              covers all 64 coefficient sets), programs resident on the device, timed with
-              the library's CUDA events on its launch streams, max over ranks
-  e2e         the same metric through the reference-facing call secant_cubin_runner_run with
-              host programs, including host->device copies of data, banks and programs and
-              the device->host copy of all scores, every step
+              covers all 64 coefficient sets) over the device time of each step: the library's
+              CUDA events on its launch streams plus the combine kernels, max over ranks
+  e2e         the same metric over the wall clock of the same steps, each a call of the
+              reference-facing secant_cubin_runner_run with host programs, including
+              host->device copies of data and banks, program encoding and upload and the
+              device->host copy of all scores
   roofline    FP32-pipe roofline of the evaluator kernel: algorithmic
               lane-operations per second over the probed FFMA rate of this device
   cpu_baseline the CPU evaluator timed on this box's cores on a bounded sample
@@ -195,7 +196,7 @@ def reference_arm(args, w):
 # ------------------------------------------------------------------------ RK4 arm ----
 
 def rk4_arm(args, w):
-    """`--impl rk4`: the rollout-scoring variant at BASELINE configs[3] (16,384 candidate systems of
+    """`--impl rk4`: the rollout-scoring variant (16,384 candidate systems of
     3 right-hand sides with at most 24 tokens over 3 states and 8 coefficients, 64 initial
     conditions, 1,000 fixed RK4 steps scored at every step).  Reference trajectories come from
     the same integrator run on the Lorenz system; programs are seeded random stand-ins."""
@@ -326,6 +327,41 @@ def comparator_arm(args, w):
 
 # ------------------------------------------------------------------------- GPU arm ----
 
+def parity_spot(w, pop, x_h, y_h, banks_h, runner, dev, programs=32, rows=65536):
+    """Scores `programs` seeded programs of the timed population on a row prefix with the library and
+    with the CPU checker (float64-accumulated sums, widened by the 2-ulp sensitivity of the math
+    functions as in tests/parity.py) and counts the bins that disagree."""
+    import torch
+    from concurrent.futures import ThreadPoolExecutor
+    import parity
+    import support as S
+    NB, K = w["banks"], w["slots"]
+    rows = min(rows, x_h.shape[1])
+    pick = np.random.Generator(np.random.Philox(key=w["seed"] + 17)).choice(len(pop.asts), size=min(programs, len(pop.asts)),
+                                                                           replace=False)
+    pick.sort()
+    sub = pop.subset(pick.tolist())
+    xs, ys = np.ascontiguousarray(x_h[:, :rows]), np.ascontiguousarray(y_h[:, :rows])
+    bs = np.ascontiguousarray(banks_h[pick])
+    out = torch.empty((len(pick), 1, NB), dtype=torch.float32, device=dev)
+    req = runner.toggle_request(sub, torch.from_numpy(xs).to(dev), torch.from_numpy(ys).to(dev), torch.from_numpy(bs).to(dev),
+                                NB, 0, out, bank_stride=K, program_bank_stride=NB * K)
+    runner.run(req)
+    got = out.cpu().numpy()
+
+    def check(i):
+        one = sub.subset([i])
+        code, _, want64 = S.oracle_toggle_sse(one, xs, ys, bs[i:i + 1], K, 0, bank_stride=K, program_bank_stride=NB * K)
+        assert code == 0
+        slack = S.sse_slack(one, xs, ys, bs[i:i + 1], K, 0, program_bank_stride=NB * K)
+        bad = parity.sse_mismatches(got[i:i + 1], want64, slack)
+        return int(bad.sum()), int((~np.isfinite(slack)).sum()), int(bad.size)
+    with ThreadPoolExecutor(max_workers=min(len(pick), os.cpu_count() or 1)) as pool:
+        results = list(pool.map(check, range(len(pick))))
+    return {"programs": int(len(pick)), "rows": int(rows), "bins": sum(r[2] for r in results), "bad": sum(r[0] for r in results),
+            "skipped": sum(r[1] for r in results), "rule": "1e-4 relative to the float64-accumulated checker sum, widened by 2-ulp sensitivity"}
+
+
 def gpu_arm(args, w):
     import torch
     import torch.distributed as dist
@@ -339,6 +375,23 @@ def gpu_arm(args, w):
         raise RuntimeError("bench.py needs a CUDA device: the evaluator has no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    lib = abi.load()
+
+    # roofline denominator and (single-GPU runs only) the CPU baseline, before any rank waits on another
+    peak, cpu = None, None
+    if rank == 0:
+        probe = C.c_double()
+        abi.check(lib.secant_b200_fp32_peak_probe(0.5, C.byref(probe)), "fp32 peak probe")
+        peak = probe.value
+        if world == 1 and not args.no_cpu:
+            threads = os.cpu_count() or 1
+            rate, kind, dt, sample = cpu_throughput(w, 1, 1024, threads)
+            per_thread = max(1, int(rate * 5.0 / (4096 * threads)))
+            rate, kind, dt, sample = cpu_throughput(w, per_thread, 4096, threads)
+            cpu = {"value": rate, "unit": "program-rows/s", "cores": threads, "kind": kind,
+                   "sample": f"{sample}, {dt:.1f} s on {threads} host threads"}
+            one, _, dt1, sample1 = cpu_throughput(w, max(1, per_thread // 4), 4096, 1)  # the evaluator as shipped is single-threaded
+            cpu["one_thread"] = {"value": one, "sample": f"{sample1}, {dt1:.1f} s"}
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -347,7 +400,6 @@ def gpu_arm(args, w):
             dist.barrier()
         torch.cuda.synchronize()
 
-    lib = abi.load()
     Pn, NB, K, F, N = w["programs"], w["banks"], w["slots"], w["features"], w["rows"]
     pop, x_h, y_h, banks_h = make_workload(w, rank)
     ops = P.count_ops(pop)
@@ -355,12 +407,14 @@ def gpu_arm(args, w):
     pin = lambda a: torch.from_numpy(a).pin_memory()
     x_pin, y_pin, banks_pin = pin(x_h), pin(y_h), pin(banks_h)
     scores_pin = torch.empty((Pn, 1, NB), dtype=torch.float32).pin_memory()
-    x_d, y_d, banks_d = x_pin.to(dev), y_pin.to(dev), banks_pin.to(dev)
+    top_pin = torch.empty(1024, dtype=torch.int64).pin_memory()
+    x_d, y_d, banks_d = torch.empty_like(x_pin, device=dev), torch.empty_like(y_pin, device=dev), torch.empty_like(banks_pin, device=dev)
     out = torch.empty((Pn, 1, NB), dtype=torch.float32, device=dev)
     flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)   # larger than the 126 MB L2
 
     records = torch.empty(Pn * R.SCORE_BYTES, dtype=torch.uint8, device=dev)          # all-gather send buffer
     gathered = torch.empty(world * Pn * R.SCORE_BYTES, dtype=torch.uint8, device=dev) if world > 1 else records
+    k_top = min(1024, world * Pn)
 
     def combine(scores):
         """Best set per program (device kernel writing straight into the all-gather send
@@ -368,104 +422,113 @@ def gpu_arm(args, w):
         R.best_config(scores.view(Pn, NB), out=records)
         if world > 1:
             dist.all_gather_into_tensor(gathered, records)
-        return R.topk(R.score_fields(gathered)[0], 1024)[0]
+        return R.topk(R.score_fields(gathered)[0], k_top)[0]
 
     runner = Runner(abi.SHAPE_TOGGLE_SSE, F, 1, K, workers=min(8, max(2, (os.cpu_count() or 2) // max(1, world))), streams=2)
     req = runner.toggle_request(pop, x_d, y_d, banks_d, NB, 0, out, bank_stride=K, program_bank_stride=NB * K)
-    launches0 = lib.secant_b200_kernel_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-    # ---- value: programs, banks and data resident; kernel time from the library's events ----
-    resident = runner.population(pop, 0)
-    kernel_s = []
-    for _ in range(args.warmup):
-        flush.fill_(1)
-        resident.run(req)
-        combine(out)
-    barrier()
-    with ClockSampler(local) as clocks:
+    def step():
+        """One pass of the hot path through the reference-facing call: host buffers in, scores out.
+        Returns (wall seconds, device seconds of the evaluation and of the combine step)."""
         t0 = time.perf_counter()
-        launches_before = lib.secant_b200_kernel_launch_count()
-        for _ in range(args.steps):
-            flush.fill_(1)
-            resident.run(req)
-            kernel_s.append(runner.stats.runtime_seconds)
-            top = combine(out)
-        barrier()
-        wall = time.perf_counter() - t0
-        launches = lib.secant_b200_kernel_launch_count() - launches_before
-    clock_summary = clocks.summary()
-    resident.destroy()
-    step_s = torch.tensor([wall / args.steps, sum(kernel_s) / len(kernel_s)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(step_s, op=dist.ReduceOp.MAX)
-    step_wall, step_kernel = step_s.tolist()
-
-    # ---- e2e: host programs and host buffers through the reference-facing call ----
-    def e2e_step():
+        flush.fill_(1)
         x_d.copy_(x_pin, non_blocking=True)
         y_d.copy_(y_pin, non_blocking=True)
         banks_d.copy_(banks_pin, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        runner.run(req)                       # encodes and uploads the programs, evaluates, blocks
-        combine(out)
+        torch.cuda.current_stream().synchronize()          # the library's streams do not wait on torch's
+        runner.run(req)                                      # encodes and uploads the programs, evaluates, blocks
+        device_s = runner.stats.runtime_seconds              # CUDA events on the library's launch streams
+        ev0.record()
+        top = combine(out)
+        ev1.record()
         scores_pin.copy_(out, non_blocking=True)
+        top_pin[:k_top].copy_(top, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-    e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
-    barrier()
-    e2e_t = torch.tensor([(time.perf_counter() - t0) / args.steps], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
-    e2e_s = float(e2e_t.item())
-    encode_s, upload_s = runner.stats.compile_work_seconds, runner.stats.module_load_seconds
-    h2d = x_h.nbytes + y_h.nbytes + banks_h.nbytes + len(pop.ast_blob)
-    d2h = scores_pin.numel() * 4
+        return time.perf_counter() - t0, device_s + ev0.elapsed_time(ev1) * 1e-3
 
-    # ---- roofline denominator and CPU baseline (rank 0 only) ----
+    steps, warmup = args.steps, args.warmup
+    budget = float(os.environ.get("SECANT_BENCH_BUDGET_S", "700"))
+    t_first = time.perf_counter()
+    done_warm = 0
+    if warmup:
+        step()
+        done_warm = 1
+        first = time.perf_counter() - t_first
+        plan = torch.tensor([first], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(plan, op=dist.ReduceOp.MAX)
+        first = float(plan.item())
+        if first * (steps + warmup) > budget:                # keep the whole run inside the time the caller allows
+            room = max(2, int(budget / first))
+            warmup = min(warmup, max(1, min(3, room - 1)))
+            steps = max(1, min(steps, room - warmup))
+    for _ in range(done_warm, warmup):
+        step()
+    barrier()
+    launches_before = lib.secant_b200_kernel_launch_count()
+    walls, devices = [], []
+    with ClockSampler(local) as clocks:
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            wall, device_s = step()
+            walls.append(wall)
+            devices.append(device_s)
+        barrier()
+        total_wall = time.perf_counter() - t0
+    launches = lib.secant_b200_kernel_launch_count() - launches_before
+    clock_summary = clocks.summary()
+    encode_s, upload_s = runner.stats.compile_work_seconds, runner.stats.module_load_seconds
+    per_rank = torch.tensor([total_wall / steps, sum(devices) / len(devices)], dtype=torch.float64, device=dev)
+    all_ranks = [torch.empty_like(per_rank) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(all_ranks, per_rank)
+    else:
+        all_ranks = [per_rank]
+    step_wall = max(float(t[0]) for t in all_ranks)
+    step_device = max(float(t[1]) for t in all_ranks)
+    h2d = x_h.nbytes + y_h.nbytes + banks_h.nbytes + len(pop.ast_blob)
+    d2h = scores_pin.numel() * 4 + k_top * 8
+
     line = None
     if rank == 0:
-        peak = C.c_double()
-        abi.check(lib.secant_b200_fp32_peak_probe(0.5, C.byref(peak)), "fp32 peak probe")
-        achieved = lane_ops_per_step / step_kernel
-        cpu = None
-        if world == 1 or True:
-            threads = os.cpu_count() or 1
-            rate, kind, dt, sample = cpu_throughput(w, 1, 1024, threads)
-            per_thread = max(1, int(rate * 12.0 / (4096 * threads)))
-            rate, kind, dt, sample = cpu_throughput(w, per_thread, 4096, threads)
-            cpu = {"value": rate, "unit": "program-rows/s", "cores": threads, "kind": kind,
-                   "sample": f"{sample}, {dt:.1f} s on {threads} host threads"}
-            # the evaluator as shipped is single-threaded: one thread on a slice of the same sample
-            one, _, dt1, sample1 = cpu_throughput(w, max(1, per_thread // 4), 4096, 1)
-            cpu["one_thread"] = {"value": one, "sample": f"{sample1}, {dt1:.1f} s"}
+        spot = None
+        if not args.no_cpu:
+            try:
+                spot = parity_spot(w, pop, x_h, y_h, banks_h, runner, dev)
+            except Exception as exc:  # the line is still printed
+                spot = {"error": repr(exc)}
+        achieved = lane_ops_per_step / step_device
         total_program_rows = float(Pn) * N * world
         line = {
-            "metric": METRIC, "value": total_program_rows / step_wall, "unit": "program-rows/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_wall * 1e3, "higher_is_better": True,
+            "metric": METRIC, "value": total_program_rows / step_device, "unit": "program-rows/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": step_device * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": w["name"], "programs_per_gpu": Pn, "rows": N, "features": F, "coefficient_slots": K,
                        "coefficient_sets": NB, "banks": "per-program", "max_tokens": w["max_tokens"],
                        "row_evals_per_step_per_gpu": float(Pn) * NB * N, "mean_ops_per_program": float(ops.mean()),
                        "l2": "192 MiB flush between steps", "combine": "best-set kernel, all-gather of 24-byte records, top-1024 kernel",
-                       "kernel_ms_per_step": step_kernel * 1e3},
-            "row_evals_per_s": float(Pn) * NB * N * world / step_wall,
-            "node_evals_per_s": lane_ops_per_step * world / step_wall,
-            "e2e": {"value": total_program_rows / e2e_s, "unit": "program-rows/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3, "encode_ms": encode_s * 1e3,
+                       "timed": "value: CUDA events of the library's launch streams plus the combine kernels, inputs resident; "
+                                "e2e: wall clock of the same steps including host-to-device copies of data and banks, program "
+                                "encoding and upload, and the device-to-host copy of all scores",
+                       "steps_requested": args.steps, "warmup_requested": args.warmup,
+                       "per_rank_device_ms": [float(t[1]) * 1e3 for t in all_ranks]},
+            "row_evals_per_s": float(Pn) * NB * N * world / step_device,
+            "node_evals_per_s": lane_ops_per_step * world / step_device,
+            "e2e": {"value": total_program_rows / step_wall, "unit": "program-rows/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": step_wall * 1e3, "encode_ms": encode_s * 1e3,
                     "program_upload_ms": upload_s * 1e3},
             "gpu_launches": int(launches),
             "clocks": clock_summary,
-            "roofline": {"bound": "fp32", "achieved": achieved / 1e12, "peak": peak.value / 1e12, "unit": "TFLOP/s",
-                         "frac": achieved / peak.value, "traffic": None,
-                         "note": "achieved = sum over programs of (ops + 2) x sets x rows / kernel time, one per "
+            "roofline": {"bound": "fp32", "achieved": achieved / 1e12, "peak": peak / 1e12, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": None,
+                         "note": "achieved = sum over programs of (ops + 2) x sets x rows / device time, one per "
                                  "algorithmic operation; peak = FFMA lane-instructions/s probed on this device in this "
-                                 "run; DRAM traffic needs a multi-pass capture: measured on a reduced case only "
-                                 "(18.6 MB per launch against 17.8 MB algorithmic) and not proportional to the unit count"},
+                                 "run; DRAM traffic needs a multi-pass capture: measured on a reduced case only and not "
+                                 "proportional to the unit count"},
             "cpu_baseline": cpu,
-            "top1024_head": [int(i) for i in top[:4].tolist()],
+            "parity_spot": spot,
+            "top1024_head": [int(i) for i in top_pin[:4].tolist()],
         }
     if world > 1:
         dist.barrier()
@@ -483,6 +546,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "comparator", "rk4"])
     ap.add_argument("--programs", type=int, default=None, help="development only: shrink the population")
     ap.add_argument("--rows", type=int, default=None, help="development only: shrink the dataset")
+    ap.add_argument("--no-cpu", action="store_true", help="development only: skip the CPU baseline and the parity spot check")
     args = ap.parse_args()
     w = dict(WORKLOAD)
     if args.programs:

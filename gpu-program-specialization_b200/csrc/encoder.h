@@ -29,11 +29,19 @@ struct ProgramRules {
      * belong to the integrator and program temporaries start after them. */
     bool columns_are_slots = false;
     unsigned reserved_slots = 0;
-    /* Move bank-independent sub-expressions into a prelude (record.h, SbProgram::main_off);
-     * at most max_hoisted values are parked.  Values and rounding are unchanged: the same
-     * operations run on the same operands, once per row instead of once per (row, bank). */
-    bool hoist_invariants = false;
-    unsigned max_hoisted = 3;
+    /* Records for the population evaluator are split into a bank part, a row prelude and a main
+     * part (record.h, SbProgram) and address constants through a per-program table the bank part
+     * fills.  Without split_parts (the rollout kernel) a record is one main part that addresses
+     * source constants directly. */
+    bool split_parts = false;
+    /* hoist_bank: sub-expressions that depend on the coefficient bank only (or on nothing) are
+     * computed in the bank part, once per bank.  hoist_row: sub-expressions that depend on the row
+     * only are computed in the row prelude, once per row; at most max_hoisted values are kept, the
+     * costliest first.  Values and rounding are unchanged: the same operations run on the same
+     * operands, only less often. */
+    bool hoist_bank = false;
+    bool hoist_row = false;
+    unsigned max_hoisted = 4;
 };
 
 /* Encoded records of a contiguous group of programs, ready to upload as five arrays. */
@@ -48,6 +56,9 @@ struct EncodedBatch {
     unsigned max_slots = 0;     /* largest n_slots */
     unsigned max_patch = 0;
     unsigned max_hoisted = 0;   /* largest n_hoisted */
+    unsigned max_cst = 0;       /* largest n_cst */
+    unsigned max_btmp = 0;      /* largest n_btmp */
+    bool uses_scratch = false;  /* some program runs an FMA over the scratch slot */
     void clear();
 };
 

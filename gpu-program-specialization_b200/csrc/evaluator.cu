@@ -35,21 +35,6 @@ namespace sb {
 
 namespace {
 
-struct Geom {
-    uint32_t tile_rows;      /* floats between consecutive columns of the tile */
-    uint32_t programs_per_cta;
-    uint32_t row_splits;
-    uint32_t exec_bytes;     /* per-warp regions, each a multiple of 16 bytes */
-    uint32_t cst_bytes;
-    uint32_t tacc_bytes;
-    uint32_t hoist_bytes;    /* per-row values left by the prelude: max_hoisted x tile_rows floats */
-    uint32_t warp_bytes;
-    uint32_t tile_bytes;
-    unsigned long long rows_per_split;
-    uint32_t groups_per_item; /* configuration groups one queue item covers */
-    uint32_t scratch_slot;    /* spill slot reserved for the out-of-line unary functions */
-};
-
 template <int OP>
 __device__ __forceinline__ float binop(float a, float x) {
     if (OP == SB_BIN_ADD) return __fadd_rn(a, x);
@@ -66,19 +51,6 @@ template <int OP>
 __device__ __forceinline__ float unop(float a) {
     if (OP == SB_UN_NEG) return -a;
     return fabsf(a);
-}
-
-/* Unary functions that are rare in scoring workloads and bulky when unrolled over the whole
- * register tile.  They run element by element over a copy of the tile in shared memory,
- * so their bodies exist once in the kernel. */
-__device__ __noinline__ float rare_unop(unsigned op, float a) {
-    switch (op) {
-    case SB_UN_SQRT: return __fsqrt_rn(a);
-    case SB_UN_RCP: return __frcp_rn(a);
-    case SB_UN_RSQRT: return __frcp_rn(__fsqrt_rn(a)); /* host: 1 / sqrtf(x), two roundings */
-    case SB_UN_LG2: return log2f(a);
-    default: return tanhf(a);
-    }
 }
 
 /* FMA_F32 takes three arbitrary operands.  It is rare in scoring workloads, so it runs
@@ -100,25 +72,17 @@ __device__ __noinline__ void fma_over_scratch(uint2 ins, const float* rowp, cons
             const unsigned kind = (kinds >> (2 * i)) & 3u;
             const uint32_t index = (ins.y >> (10 * i)) & 1023u;
             const int r = k / RC, c = k % RC;
-            if (kind == SB_KIND_ROW) v[i] = ((index & SB_ROW_HOISTED) ? hrowp : rowp)[(size_t)(index & 0x7fu) * tile_ld + (r / 4) * 128 + (r % 4)];
-            else if (kind == SB_KIND_CST) v[i] = cst[index * RC + c];
+            if (kind == SB_KIND_ROW) {
+                const float* q = (index & SB_FMA_ROW_HOISTED) ? hrowp + (size_t)(index & (SB_FMA_ROW_HOISTED - 1u)) * (32 * RR)
+                                                              : rowp + (size_t)index * tile_ld;
+                v[i] = q[(r / 4) * 128 + (r % 4)];
+            } else if (kind == SB_KIND_CST) v[i] = cst[index * RC + c];
             else {
                 const uint32_t slot = kind == SB_FMA_ACC ? scratch_slot : index;
                 v[i] = reinterpret_cast<const float*>(slots + (size_t)slot * (V / 4) * 32)[(k >> 2) * 128 + (k & 3)];
             }
         }
         out[(k >> 2) * 128 + (k & 3)] = __fmaf_rn(v[0], v[1], v[2]);
-    }
-}
-
-/* Applies a rare unary function to every element of the tile parked in the scratch slot. */
-template <int V>
-__device__ __noinline__ void rare_over_scratch(unsigned op, float4* slots, uint32_t scratch_slot) {
-    float* flat = reinterpret_cast<float*>(slots + (size_t)scratch_slot * (V / 4) * 32);
-#pragma unroll 1
-    for (int k = 0; k < V; ++k) {
-        float* p = flat + (k >> 2) * 128 + (k & 3);
-        *p = rare_unop(op, *p);
     }
 }
 
@@ -130,16 +94,20 @@ struct Machine {
 
     float acc[RR][RC];
 
-    /* one float per row: a dataset column from the staged tile, or (index bit 7) a value the
-     * prelude left in the warp's hoist buffer; both are laid out [column][row of the chunk] */
-    __device__ __forceinline__ void fetch_row(const float* rowp, const float* hrowp, uint32_t tile_ld, uint32_t col,
-                                              float (&x)[RR]) const {
-        const float* q = ((col & SB_ROW_HOISTED) ? hrowp : rowp) + (size_t)(col & 0x7fu) * tile_ld;
+    /* one float per row, starting at the thread's first row of a column laid out [row of the pass] */
+    __device__ __forceinline__ void fetch_column(const float* q, float (&x)[RR]) const {
 #pragma unroll
         for (int g = 0; g < GROUPS; ++g) {
             const float4 v = *reinterpret_cast<const float4*>(q + g * 128);
             x[4 * g + 0] = v.x; x[4 * g + 1] = v.y; x[4 * g + 2] = v.z; x[4 * g + 3] = v.w;
         }
+    }
+    /* ROW operand: a dataset column of the staged tile, or (SB_ROW_HOISTED) a value the row prelude
+     * left in the warp's hoist buffer, which holds PASS floats per value */
+    __device__ __forceinline__ void fetch_row(const float* rowp, const float* hrowp, uint32_t tile_ld, uint32_t col,
+                                              float (&x)[RR]) const {
+        const float* q = (col & SB_ROW_HOISTED) ? hrowp + (size_t)(col & (SB_ROW_HOISTED - 1u)) * PASS : rowp + (size_t)col * tile_ld;
+        fetch_column(q, x);
     }
     __device__ __forceinline__ void fetch_cst(const float* cst, uint32_t entry, float (&x)[RC]) const {
         const float* q = cst + entry * RC;
@@ -200,11 +168,11 @@ struct Machine {
         }                                                                                            \
     }
 
-    /* Runs the warp's program once over the RR*32 rows starting at rowp. */
+    /* Runs one instruction run of the warp's program over the RR*32 rows starting at rowp. */
     __device__ __forceinline__ void run(const SbInsn* exec, const float* rowp, uint32_t tile_ld, const float* cst,
                                         float4* slots, uint32_t scratch_slot, float* hrowp = nullptr) {
         const uint2* ip = reinterpret_cast<const uint2*>(exec);
-        uint2 next = *ip++; /* the buffer holds one padding entry after END */
+        uint2 next = *ip++; /* the buffer holds one padding entry after the last END */
 #pragma unroll 1
         for (;;) {
             const uint2 ins = next;
@@ -228,7 +196,7 @@ struct Machine {
                 store_slot(slots, idx);
                 break;
             case SB_CASE_STOREH: { /* bank-independent value: every bank column holds the same number */
-                float* q = hrowp + (size_t)idx * tile_ld;
+                float* q = hrowp + (size_t)idx * PASS;
 #pragma unroll
                 for (int g = 0; g < GROUPS; ++g)
                     *reinterpret_cast<float4*>(q + g * 128) = make_float4(acc[4 * g][0], acc[4 * g + 1][0], acc[4 * g + 2][0], acc[4 * g + 3][0]);
@@ -237,7 +205,7 @@ struct Machine {
             SB_BIN_CASES(SB_BIN_SUB)
             SB_BIN_CASES(SB_BIN_RSUB)
             SB_BIN_CASES(SB_BIN_MUL)
-            /* IEEE division is ~10 instructions per element: the eight operand-kind cases
+            /* IEEE division is ~10 instructions per element: the six operand-kind cases
              * only expand the operand, then share one body per direction. */
             case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_ROW:
             case SB_CASE_BIN + SB_BIN_RDIV * SB_NUM_KINDS + SB_KIND_ROW:
@@ -301,16 +269,11 @@ struct Machine {
             case SB_CASE_UN + SB_UN_RCP:
             case SB_CASE_UN + SB_UN_LG2:
             case SB_CASE_UN + SB_UN_RSQRT:
-            case SB_CASE_UN + SB_UN_TANH:
-                if (FAST) {
-                    const unsigned op = (ins.x & 0xffu) - SB_CASE_UN;
-                    SB_FOR_TILE acc[r][c] = sbm::fast_unary(op, acc[r][c]);
-                    break;
-                }
-                store_slot(slots, scratch_slot);
-                rare_over_scratch<V>((ins.x & 0xffu) - SB_CASE_UN, slots, scratch_slot);
-                fetch_slot(slots, scratch_slot, acc);
-                break;
+            case SB_CASE_UN + SB_UN_TANH: {
+                const unsigned op = (ins.x & 0xffu) - SB_CASE_UN;
+                if (FAST) { SB_FOR_TILE acc[r][c] = sbm::fast_unary(op, acc[r][c]); }
+                else SB_FOR_QUADS(sbm::rare4(in, op))
+                break; }
             case SB_CASE_FMA:
                 store_slot(slots, scratch_slot);
                 fma_over_scratch<RR, RC>(ins, rowp, hrowp, tile_ld, cst, slots, scratch_slot);
@@ -329,124 +292,287 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-/* 16-value tiles run 16 warps per CTA within 128 registers; 32-value tiles need more
+/* Sums RC per-lane values over the warp, one total per value, in a fixed order: halves of the warp
+ * trade values so that every step adds pairs, and value c ends in lane c * (32 / RC). */
+template <int RC>
+__device__ __forceinline__ float column_totals(const float (&p)[RC], int lane) {
+    float k;
+    if (RC == 4) {
+        const bool hi = lane & 16, hi8 = lane & 8;
+        float k0 = hi ? p[2 % RC] : p[0], k1 = hi ? p[3 % RC] : p[1 % RC];
+        const float s0 = hi ? p[0] : p[2 % RC], s1 = hi ? p[1 % RC] : p[3 % RC];
+        k0 = __fadd_rn(k0, __shfl_xor_sync(0xffffffffu, s0, 16));
+        k1 = __fadd_rn(k1, __shfl_xor_sync(0xffffffffu, s1, 16));
+        k = hi8 ? k1 : k0;
+        k = __fadd_rn(k, __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k1, 8));
+    } else if (RC == 2) {
+        const bool hi = lane & 16;
+        k = hi ? p[1 % RC] : p[0];
+        k = __fadd_rn(k, __shfl_xor_sync(0xffffffffu, hi ? p[0] : p[1 % RC], 16));
+        k = __fadd_rn(k, __shfl_xor_sync(0xffffffffu, k, 8));
+    } else {
+        k = __fadd_rn(p[0], __shfl_xor_sync(0xffffffffu, p[0], 16));
+        k = __fadd_rn(k, __shfl_xor_sync(0xffffffffu, k, 8));
+    }
+    k = __fadd_rn(k, __shfl_xor_sync(0xffffffffu, k, 4));
+    k = __fadd_rn(k, __shfl_xor_sync(0xffffffffu, k, 2));
+    k = __fadd_rn(k, __shfl_xor_sync(0xffffffffu, k, 1));
+    return k;
+}
+
+/* ---- the bank part: a scalar machine, one lane per coefficient bank ------------------------- */
+
+struct BankSource {
+    const float* banks;      /* this program's table, [bank][slot] */
+    size_t bank_stride;
+    uint32_t num_banks, K, n_affine;
+    const SbAffine* affines; /* of this program */
+    const float* lits;       /* of this program */
+};
+
+template <bool FAST>
+__device__ __forceinline__ float scalar_unary(unsigned op, float a) {
+    if (op == SB_UN_NEG) return -a;
+    if (op == SB_UN_ABS) return fabsf(a);
+    if (FAST) return sbm::fast_unary(op, a);
+    const float4 v = make_float4(a, a, a, a);
+    switch (op) {
+    case SB_UN_SIN: return sbm::sincos4(v, 0).x;
+    case SB_UN_COS: return sbm::sincos4(v, 1).x;
+    case SB_UN_EX2: return sbm::exp2_4(v).x;
+    case SB_UN_EXP: return sbm::exp4(v).x;
+    case SB_UN_LOG: return sbm::log4(v).x;
+    default: return sbm::rare4(v, op).x;
+    }
+}
+template <bool FAST>
+__device__ __forceinline__ float scalar_binary(unsigned op, float a, float x) {
+    switch (op) {
+    case SB_BIN_ADD: return __fadd_rn(a, x);
+    case SB_BIN_SUB: return __fsub_rn(a, x);
+    case SB_BIN_RSUB: return __fsub_rn(x, a);
+    case SB_BIN_MUL: return __fmul_rn(a, x);
+    case SB_BIN_DIV: return FAST ? sbm::fast_div(a, x) : sbm::div4(make_float4(a, a, a, a), make_float4(x, x, x, x)).x;
+    case SB_BIN_RDIV: return FAST ? sbm::fast_div(x, a) : sbm::div4(make_float4(x, x, x, x), make_float4(a, a, a, a)).x;
+    case SB_BIN_MIN: return fminf(a, x);
+    default: return fmaxf(a, x);
+    }
+}
+
+/* Runs the bank part of the warp's program for the `count` banks starting at `first_bank` (count is
+ * a multiple of RC; banks past the table's end are padding and read zeros).  Lane l handles banks
+ * l, l + 32, ...  Results go to the warp's constant table laid out [bank group][entry][bank of the
+ * group], `entries` entries per group; temporaries live in `tmp`, 32 floats apart.  The same
+ * functions as the tile machine are called, so a value computed here has the bits it would have
+ * had in the main part. */
+template <int RC, bool FAST>
+__device__ __noinline__ void run_bank_part(const SbInsn* exec, uint32_t first_bank, uint32_t count, uint32_t entries, float* table,
+                                           float* tmp, const BankSource src, int lane) {
+    for (uint32_t b0 = 0; b0 < count; b0 += 32) {
+        const uint32_t b = b0 + lane, bank = first_bank + b;
+        const bool live = b < count, real = live && bank < src.num_banks;
+        float* const mine = table + ((size_t)(b / RC) * entries) * RC + (b % RC);
+        const float* const row = src.banks + (size_t)bank * src.bank_stride;
+        auto operand = [&](unsigned kind, uint32_t idx) -> float {
+            if (kind == SB_KIND_ROW) return live ? mine[(size_t)idx * RC] : 0.0f;
+            if (kind == SB_KIND_SLOT) return tmp[idx * 32 + lane];
+            if (idx < src.K) return real ? __ldg(row + idx) : 0.0f;
+            if (idx < src.K + src.n_affine) {
+                const SbAffine a = src.affines[idx - src.K];
+                return real ? __fadd_rn(__fmul_rn(__ldg(row + a.slot), a.scale), a.offset) : 0.0f;
+            }
+            return __ldg(src.lits + (idx - src.K - src.n_affine));
+        };
+        const uint2* ip = reinterpret_cast<const uint2*>(exec);
+        float acc = 0.0f;
+#pragma unroll 1
+        for (;;) {
+            const uint2 ins = *ip++;
+            const unsigned cs = ins.x & 0xffu;
+            const uint32_t idx = ins.x >> 16;
+            if (cs == SB_CASE_END) break;
+            if (cs < SB_CASE_STORE) acc = operand(cs - SB_CASE_LOAD, idx);
+            else if (cs == SB_CASE_STORE) tmp[idx * 32 + lane] = acc;
+            else if (cs == SB_CASE_STOREH) { if (live) mine[(size_t)idx * RC] = acc; }
+            else if (cs < SB_CASE_UN) {
+                const unsigned rel = cs - SB_CASE_BIN;
+                acc = scalar_binary<FAST>(rel / SB_NUM_KINDS, acc, operand(rel % SB_NUM_KINDS, idx));
+            } else if (cs < SB_CASE_FMA) acc = scalar_unary<FAST>(cs - SB_CASE_UN, acc);
+            else if (cs == SB_CASE_FMA) {
+                const unsigned kinds = (ins.x >> 8) & 0x3fu;
+                float v[3];
+#pragma unroll
+                for (int i = 0; i < 3; ++i) {
+                    const unsigned kind = (kinds >> (2 * i)) & 3u;
+                    v[i] = kind == SB_FMA_ACC ? acc : operand(kind, (ins.y >> (10 * i)) & 1023u);
+                }
+                acc = __fmaf_rn(v[0], v[1], v[2]);
+            } else break;
+        }
+    }
+}
+
+/* ---- tile staging ----------------------------------------------------------------------- */
+
+__device__ __forceinline__ void cp_async_16(float* dst, const float* src, uint32_t src_bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+/* Starts the asynchronous copy of rows [c0, c0 + rows) of every column into a tile buffer laid out
+ * [column][tile_ld]; rows up to `padded` are zero-filled.  A column whose first row is 16-byte
+ * aligned moves as 16-byte copies, any other as 4-byte copies (callers only promise 4-byte
+ * alignment of their matrices).  Completion: cp_async_wait_all() by every thread, then a barrier. */
+__device__ __forceinline__ void stage_tile(float* tile, uint32_t tile_ld, const EvalProblem& prob, uint32_t ncols, size_t c0,
+                                           uint32_t rows, uint32_t padded) {
+    for (uint32_t col = 0; col < ncols; ++col) {
+        const float* src = (col < prob.num_inputs ? prob.input + (size_t)col * prob.input_ld
+                                                  : prob.targets + (size_t)(col - prob.num_inputs) * prob.targets_ld) + c0;
+        float* dst = tile + (size_t)col * tile_ld;
+        if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+            for (uint32_t i = threadIdx.x * 4; i < padded; i += blockDim.x * 4) {
+                if (i < rows) cp_async_16(dst + i, src + i, min(16u, (rows - i) * 4u)); /* short copies zero-fill their tail */
+                else *reinterpret_cast<float4*>(dst + i) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+        } else {
+            for (uint32_t i = threadIdx.x; i < padded; i += blockDim.x) {
+                if (i < rows) cp_async_4(dst + i, src + i);
+                else dst[i] = 0.0f;
+            }
+        }
+    }
+    cp_async_commit();
+}
+
+/* 16-value tiles run 20 warps per CTA within 96 registers; 32-value tiles need more
  * registers per thread and run 12 warps. */
 template <int RR, int RC, bool FAST>
 __global__ void __launch_bounds__(RR * RC > 16 ? 384 : 640, 1)
-eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
+eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, float* __restrict__ partial) {
     using M = Machine<RR, RC, FAST>;
     extern __shared__ __align__(16) unsigned char smem[];
-    float* const tile = reinterpret_cast<float*>(smem);
-    unsigned int* const queue = reinterpret_cast<unsigned int*>(smem + geom.tile_bytes);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    unsigned char* const warea = smem + geom.tile_bytes + 16 + (size_t)warp * geom.warp_bytes;
+    float* const tiles = reinterpret_cast<float*>(smem);
+    unsigned int* const queue = reinterpret_cast<unsigned int*>(smem + (size_t)geom.tile_bytes * geom.tile_buffers);
+    unsigned char* const warea = smem + (size_t)geom.tile_bytes * geom.tile_buffers + 16 + (size_t)warp * geom.warp_bytes;
     SbInsn* const exec = reinterpret_cast<SbInsn*>(warea);
-    float* const cst = reinterpret_cast<float*>(warea + geom.exec_bytes);
-    float* const tacc = reinterpret_cast<float*>(warea + geom.exec_bytes + geom.cst_bytes);
-    float* const hoist = reinterpret_cast<float*>(warea + geom.exec_bytes + geom.cst_bytes + geom.tacc_bytes);
-    float4* const slots = reinterpret_cast<float4*>(warea + geom.exec_bytes + geom.cst_bytes + geom.tacc_bytes + geom.hoist_bytes) + lane;
+    float* const table = reinterpret_cast<float*>(warea + geom.exec_bytes);
+    float* const hoist = reinterpret_cast<float*>(warea + geom.exec_bytes + geom.table_bytes);
+    float* const slot_base = reinterpret_cast<float*>(warea + geom.exec_bytes + geom.table_bytes + geom.hoist_bytes);
+    float4* const slots = reinterpret_cast<float4*>(slot_base) + lane;
+    float* const psum = reinterpret_cast<float*>(warea + geom.exec_bytes + geom.table_bytes + geom.hoist_bytes + geom.slot_bytes);
 
     const uint32_t group = blockIdx.x / geom.row_splits, split = blockIdx.x % geom.row_splits;
-    const uint32_t prog_begin = group * geom.programs_per_cta;
-    const uint32_t prog_count = min(geom.programs_per_cta, batch.num_programs - prog_begin);
+    /* this CTA's programs: group, group + num_groups, ... (the batch is sorted by cost) */
+    const uint32_t prog_count = (batch.num_programs - group + geom.num_groups - 1) / geom.num_groups;
     const size_t row_begin = (size_t)split * geom.rows_per_split;
     const size_t row_end = min(prob.num_rows, row_begin + (size_t)geom.rows_per_split);
     const bool materialize = prob.mode == EVAL_MATERIALIZE;
     const uint32_t ncols = prob.num_inputs + (materialize ? 0u : prob.num_targets);
     const uint32_t tile_ld = geom.tile_rows;
-    const uint32_t K = prob.num_constants;
     const uint32_t T = prob.num_targets;
+    const uint32_t nq = prob.mode == EVAL_AFFINE_STATS ? T + 2 : T;
+    const uint32_t gpi = geom.groups_per_item;
     /* configuration groups of one program: permutation-major, RC banks per group */
     const uint32_t bank_groups = materialize ? 1u : (prob.num_banks + RC - 1) / RC;
-    const unsigned long long cfg_groups = materialize ? 1ull : ((unsigned long long)bank_groups << prob.toggle_bits);
-    const unsigned long long items_per_program = (cfg_groups + geom.groups_per_item - 1) / geom.groups_per_item;
-    const unsigned long long num_items = items_per_program * prog_count;
+    const unsigned long long items_per_program = materialize ? 1ull : ((unsigned long long)(bank_groups / gpi) << prob.toggle_bits);
+    const unsigned int num_items = (unsigned int)(items_per_program * prog_count); /* the planner keeps this below 2^32 - 256 */
+    const unsigned long long configs = (unsigned long long)prob.num_banks << prob.toggle_bits;
+    const size_t tile_floats = geom.tile_bytes / 4;
+    const uint32_t num_tiles = (uint32_t)((row_end - row_begin + geom.tile_rows - 1) / geom.tile_rows);
 
-    for (size_t c0 = row_begin; c0 < row_end; c0 += geom.tile_rows) {
+    if (threadIdx.x == 0) queue[0] = 0u;
+    {
+        const uint32_t rows0 = (uint32_t)min((size_t)geom.tile_rows, row_end - row_begin);
+        stage_tile(tiles, tile_ld, prob, ncols, row_begin, rows0, (rows0 + M::PASS - 1) / M::PASS * M::PASS);
+    }
+    for (uint32_t t = 0; t < num_tiles; ++t) {
+        const size_t c0 = row_begin + (size_t)t * geom.tile_rows;
         const uint32_t chunk_rows = (uint32_t)min((size_t)geom.tile_rows, row_end - c0);
-        const uint32_t padded = (chunk_rows + M::PASS - 1) / M::PASS * M::PASS;
-        const uint32_t npass = padded / M::PASS;
-        __syncthreads();
-        for (uint32_t col = 0; col < ncols; ++col) {
-            const float* src = col < prob.num_inputs ? prob.input + (size_t)col * prob.input_ld
-                                                     : prob.targets + (size_t)(col - prob.num_inputs) * prob.targets_ld;
-            float* dst = tile + (size_t)col * tile_ld;
-            for (uint32_t i = threadIdx.x; i < padded; i += blockDim.x) dst[i] = i < chunk_rows ? __ldg(src + c0 + i) : 0.0f;
+        const uint32_t npass = (chunk_rows + M::PASS - 1) / M::PASS;
+        const float* const tile = tiles + (size_t)(t & 1u) * tile_floats;
+        unsigned int* const q = queue + (t & 1u);
+        cp_async_wait_all();
+        __syncthreads(); /* tile t has landed; every warp has left tile t - 1 */
+        if (threadIdx.x == 0) queue[(t + 1) & 1u] = 0u;
+        if (t + 1 < num_tiles) { /* fetch the next tile into the other buffer while this one is used */
+            const size_t n0 = c0 + geom.tile_rows;
+            const uint32_t nrows = (uint32_t)min((size_t)geom.tile_rows, row_end - n0);
+            stage_tile(tiles + (size_t)((t + 1) & 1u) * tile_floats, tile_ld, prob, ncols, n0, nrows, (nrows + M::PASS - 1) / M::PASS * M::PASS);
         }
-        if (threadIdx.x == 0) *queue = 0u;
-        __syncthreads();
 
-        uint32_t loaded = 0xffffffffu; /* program currently held in this warp's exec buffer */
-        SbProgram pr;
         for (;;) {
             unsigned int item = 0;
-            if (lane == 0) item = atomicAdd(queue, 1u);
+            if (lane == 0) item = atomicAdd(q, 1u);
             item = __shfl_sync(0xffffffffu, item, 0);
             if (item >= num_items) break;
             const uint32_t pi = (uint32_t)(item / items_per_program);
-            const unsigned long long first_group = (item % items_per_program) * geom.groups_per_item;
-            const unsigned long long last_group = min(cfg_groups, first_group + geom.groups_per_item);
-            const uint32_t lp = prog_begin + pi;           /* index inside the batch */
-            __syncwarp();
-            if (lp != loaded) {
-                pr = batch.programs[lp];
-                for (uint32_t i = lane; i < pr.n_insn; i += 32) exec[i] = batch.insns[pr.insn_off + i];
-                if (lane == 0) exec[pr.n_insn] = SbInsn{0u, 0u}; /* padding read by the instruction prefetch */
-                for (uint32_t i = lane; i < (uint32_t)pr.n_lits * RC; i += 32)
-                    cst[(K + pr.n_affine) * RC + i] = batch.lits[pr.lit_off + i / RC];
-                loaded = lp;
+            const unsigned long long first_group = (item % items_per_program) * gpi; /* among the program's configuration groups */
+            const uint32_t lp = group + pi * geom.num_groups;                        /* index inside the batch */
+            const SbProgram* const hp = batch.programs + lp;
+            const uint32_t n_insn = hp->n_insn, pre_off = hp->pre_off, main_off = hp->main_off, n_cst = hp->n_cst;
+            const uint32_t n_patch = hp->n_patch, flags = hp->flags;
+            __syncwarp(); /* the previous item's reads of exec, table and psum are done */
+            {
+                const SbInsn* code = batch.insns + hp->insn_off;
+                for (uint32_t i = lane; i < n_insn; i += 32) exec[i] = code[i];
+                if (lane == 0) exec[n_insn] = SbInsn{0u, 0u}; /* padding read by the instruction prefetch */
             }
-            const size_t gp = prob.first_program + pr.index; /* position in the run: output row, bank table */
-            const float* bank_base = prob.banks ? prob.banks + gp * prob.program_bank_stride : nullptr;
             /* an item never straddles permutations: toggles are patched once per item */
             const unsigned long long perm = materialize ? prob.fixed_permutation : first_group / bank_groups;
-            if (pr.n_patch) {
+            const uint32_t first_bg = materialize ? 0u : (uint32_t)(first_group % bank_groups);
+            const uint32_t ngroups = materialize ? 1u : min(gpi, bank_groups - first_bg);
+            if (n_patch) {
                 __syncwarp(); /* the copy above and the patches below touch the same words from different lanes */
-                for (uint32_t i = lane; i < pr.n_patch; i += 32) {
-                    const SbPatch* p = batch.patches + pr.patch_off + i;
+                const SbPatch* patches = batch.patches + hp->patch_off;
+                for (uint32_t i = lane; i < n_patch; i += 32) {
+                    const SbPatch* p = patches + i;
                     unsigned choice = (unsigned)(perm >> p->bit0) & 1u;
                     if (p->bit1 != 0xffu) choice |= ((unsigned)(perm >> p->bit1) & 1u) << 1;
                     exec[p->insn] = p->alt[choice];
                 }
             }
-            /* iteration -1 (only when the program has a prelude) evaluates the bank-independent
-             * sub-expressions once per row; iterations 0.. evaluate the main part per bank group */
-            const long long steps = (long long)(last_group - first_group);
-            for (long long step = pr.main_off ? -1 : 0; step < steps; ++step) {
-                const bool prelude = step < 0;
-                const uint32_t bg = prelude ? 0u : (uint32_t)((first_group + (unsigned long long)step) % bank_groups);
+            for (uint32_t e = lane; e < nq * gpi * RC; e += 32) psum[e] = 0.0f;
+            __syncwarp();
+            const size_t gp = prob.first_program + hp->index; /* position in the run: output row, bank table */
+            if (pre_off) {
+                BankSource src;
+                src.banks = prob.banks ? prob.banks + gp * prob.program_bank_stride : nullptr;
+                src.bank_stride = prob.bank_stride;
+                src.num_banks = prob.banks ? prob.num_banks : 0u; /* without a table every bank constant reads zero */
+                src.K = prob.num_constants;
+                src.n_affine = hp->n_affine;
+                src.affines = batch.affines + hp->affine_off;
+                src.lits = batch.lits + hp->lit_off;
+                run_bank_part<RC, FAST>(exec, first_bg * RC, ngroups * RC, n_cst, table, slot_base, src, lane);
                 __syncwarp();
-                if (!prelude)
-                for (uint32_t e = lane; e < (K + pr.n_affine) * RC; e += 32) {
-                    const uint32_t entry = e / RC, c = e % RC, bank = bg * RC + c;
-                    float v = 0.0f;
-                    if (bank < prob.num_banks) {
-                        if (entry < K) {
-                            v = __ldg(bank_base + (size_t)bank * prob.bank_stride + entry);
-                        } else {
-                            const SbAffine a = batch.affines[pr.affine_off + entry - K];
-                            v = __fadd_rn(__fmul_rn(__ldg(bank_base + (size_t)bank * prob.bank_stride + a.slot), a.scale), a.offset);
-                        }
-                    }
-                    cst[e] = v;
-                }
-                if (!prelude && (T > 1 || prob.mode == EVAL_AFFINE_STATS))
-                    for (uint32_t e = lane; e < (T + 2) * RC; e += 32) tacc[e] = 0.0f;
-                __syncwarp();
+            }
+            const bool has_prelude = main_off > pre_off;
+            const uint32_t eval_groups = (flags & SB_PROG_BANK_INDEPENDENT) ? 1u : ngroups;
+            const uint32_t table_stride = n_cst * RC;
 
-                M m;
-                float part[RC];
-#pragma unroll
-                for (int c = 0; c < RC; ++c) part[c] = 0.0f;
-
+            M m;
 #pragma unroll 1
-                for (uint32_t pass = 0; pass < npass; ++pass) {
-                    const float* rowp = tile + pass * M::PASS + lane * 4;
-                    m.run(exec + (prelude ? 0u : (uint32_t)pr.main_off), rowp, tile_ld, cst, slots, geom.scratch_slot,
-                          hoist + pass * M::PASS + lane * 4);
+            for (uint32_t pass = 0; pass < npass; ++pass) {
+                const float* rowp = tile + pass * M::PASS + lane * 4;
+                float* const hrowp = hoist + lane * 4;
+                const uint32_t row0 = pass * M::PASS + lane * 4; /* first row of this thread in the tile */
+                const bool full = (pass + 1) * M::PASS <= chunk_rows;
+                /* iteration -1 (only when the program has a row prelude) evaluates the bank-independent
+                 * sub-expressions once for the pass; iterations 0.. evaluate the main part per bank group.
+                 * One call site: a second inlined copy of the interpreter would not fit the instruction caches. */
+#pragma unroll 1
+                for (int g = has_prelude ? -1 : 0; g < (int)eval_groups; ++g) {
+                    const bool prelude = g < 0;
+                    m.run(exec + (prelude ? pre_off : main_off), rowp, tile_ld, table + (prelude ? 0u : (uint32_t)g * table_stride), slots,
+                          geom.scratch_slot, hrowp);
                     if (prelude) continue;
-                    const uint32_t row0 = pass * M::PASS + lane * 4; /* first row of this thread in the chunk */
-                    const bool full = (pass + 1) * M::PASS <= chunk_rows;
                     if (materialize) {
                         float* out = prob.output + gp * prob.out_program_stride + c0;
 #pragma unroll
@@ -455,14 +581,16 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
                             if (row < chunk_rows) out[row] = m.acc[r][0];
                         }
                     } else if (prob.mode == EVAL_SSE && T == 1) {
-                        float t[RR];
-                        m.fetch_row(rowp, rowp, tile_ld, prob.num_inputs, t);
+                        float tv[RR], part[RC];
+                        m.fetch_column(rowp + (size_t)prob.num_inputs * tile_ld, tv);
+#pragma unroll
+                        for (int c = 0; c < RC; ++c) part[c] = 0.0f;
                         if (full) {
 #pragma unroll
                             for (int r = 0; r < RR; ++r)
 #pragma unroll
                                 for (int c = 0; c < RC; ++c) {
-                                    const float e = __fsub_rn(m.acc[r][c], t[r]);
+                                    const float e = __fsub_rn(m.acc[r][c], tv[r]);
                                     part[c] = __fmaf_rn(e, e, part[c]);
                                 }
                         } else {
@@ -471,20 +599,20 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
                                 const bool ok = row0 + (r / 4) * 128 + (r % 4) < chunk_rows;
 #pragma unroll
                                 for (int c = 0; c < RC; ++c) {
-                                    const float e = ok ? __fsub_rn(m.acc[r][c], t[r]) : 0.0f;
+                                    const float e = ok ? __fsub_rn(m.acc[r][c], tv[r]) : 0.0f;
                                     part[c] = __fmaf_rn(e, e, part[c]);
                                 }
                             }
                         }
+                        const float total = column_totals<RC>(part, lane);
+                        if ((lane & (32 / RC - 1)) == 0) psum[g * RC + lane / (32 / RC)] += total;
                     } else {
-                        /* several targets, or affine statistics: per-pass warp reduction into
-                         * the warp's shared accumulators tacc[quantity][bank] */
-                        const uint32_t nq = prob.mode == EVAL_AFFINE_STATS ? T + 2 : T;
-                        for (uint32_t q = 0; q < nq; ++q) {
-                            float t[RR];
-                            const bool is_target = prob.mode == EVAL_SSE || q >= 2;
-                            const uint32_t tcol = prob.num_inputs + (prob.mode == EVAL_SSE ? q : q - 2);
-                            if (is_target) m.fetch_row(rowp, rowp, tile_ld, tcol, t);
+                        /* several targets, or affine statistics: quantity q of bank group g lives in psum[(q * gpi + g) * RC + c] */
+                        for (uint32_t qn = 0; qn < nq; ++qn) {
+                            float tv[RR];
+                            const bool is_target = prob.mode == EVAL_SSE || qn >= 2;
+                            const uint32_t tcol = prob.num_inputs + (prob.mode == EVAL_SSE ? qn : qn - 2);
+                            if (is_target) m.fetch_column(rowp + (size_t)tcol * tile_ld, tv);
                             float s[RC];
 #pragma unroll
                             for (int c = 0; c < RC; ++c) s[c] = 0.0f;
@@ -495,49 +623,55 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom) {
                                 for (int c = 0; c < RC; ++c) {
                                     const float p = m.acc[r][c];
                                     float term;
-                                    if (prob.mode == EVAL_SSE) { const float e = __fsub_rn(p, t[r]); term = __fmul_rn(e, e); }
-                                    else if (q == 0) term = p;
-                                    else if (q == 1) term = __fmul_rn(p, p);
-                                    else term = __fmul_rn(p, t[r]);
+                                    if (prob.mode == EVAL_SSE) { const float e = __fsub_rn(p, tv[r]); term = __fmul_rn(e, e); }
+                                    else if (qn == 0) term = p;
+                                    else if (qn == 1) term = __fmul_rn(p, p);
+                                    else term = __fmul_rn(p, tv[r]);
                                     s[c] = __fadd_rn(s[c], ok ? term : 0.0f);
                                 }
                             }
-#pragma unroll
-                            for (int c = 0; c < RC; ++c) {
-                                const float total = warp_sum(s[c]);
-                                if (lane == 0) tacc[q * RC + c] += total;
-                            }
-                        }
-                    }
-                }
-
-                if (prelude) continue;
-                if (prob.mode == EVAL_SSE && T == 1) {
-                    float mine = 0.0f;
-#pragma unroll
-                    for (int c = 0; c < RC; ++c) {
-                        const float total = warp_sum(part[c]);
-                        if (lane == c) mine = total;
-                    }
-                    const uint32_t bank = bg * RC + lane;
-                    if (lane < RC && bank < prob.num_banks) {
-                        float* dst = prob.output + gp * prob.out_program_stride + ((size_t)bank << prob.toggle_bits) + perm;
-                        atomicAdd(dst, mine); /* result unused: a reduction that never stalls the warp */
-                    }
-                } else if (!materialize) {
-                    __syncwarp();
-                    const uint32_t nq = prob.mode == EVAL_AFFINE_STATS ? T + 2 : T;
-                    for (uint32_t e = lane; e < nq * RC; e += 32) {
-                        const uint32_t q = e / RC, c = e % RC, bank = bg * RC + c;
-                        if (bank < prob.num_banks) {
-                            float* dst = prob.output + gp * prob.out_program_stride + (size_t)q * prob.out_target_stride +
-                                         ((size_t)bank << prob.toggle_bits) + perm;
-                            atomicAdd(dst, tacc[e]);
+                            const float total = column_totals<RC>(s, lane);
+                            if ((lane & (32 / RC - 1)) == 0) psum[(qn * gpi + g) * RC + lane / (32 / RC)] += total;
                         }
                     }
                 }
             }
+            if (materialize) continue;
+            __syncwarp();
+            /* this CTA's partial sums of the item: stored on its first tile, added to afterwards (only this
+             * CTA touches them, and a barrier separates its tiles) */
+            {
+                const bool independent = (flags & SB_PROG_BANK_INDEPENDENT) != 0;
+                float* const mine = partial + ((size_t)split * batch.num_programs + lp) * nq * configs + perm;
+                const uint32_t per_q = ngroups * RC;
+                for (uint32_t e = lane; e < nq * per_q; e += 32) {
+                    const uint32_t qn = e / per_q, rem = e % per_q, g = rem / RC, c = rem % RC;
+                    const uint32_t bank = (first_bg + g) * RC + c;
+                    if (bank >= prob.num_banks) continue;
+                    const float v = independent ? psum[qn * gpi * RC] : psum[(qn * gpi + g) * RC + c];
+                    float* dst = mine + (size_t)qn * configs + ((size_t)bank << prob.toggle_bits);
+                    *dst = t == 0 ? v : __fadd_rn(*dst, v);
+                }
+            }
         }
+    }
+    cp_async_wait_all();
+}
+
+/* Adds the per-split partial sums of every (program, quantity, configuration) in split order and
+ * writes the total to the caller's grid (only active bins are written: padding keeps its contents). */
+__global__ void combine_kernel(const DeviceBatch batch, const EvalProblem prob, const float* __restrict__ partial, uint32_t splits,
+                               uint32_t nq, unsigned long long configs) {
+    const unsigned long long per_program = (unsigned long long)nq * configs;
+    const unsigned long long total = per_program * batch.num_programs;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (unsigned long long)gridDim.x * blockDim.x) {
+        float sum = partial[i];
+        for (uint32_t s = 1; s < splits; ++s) sum = __fadd_rn(sum, partial[(unsigned long long)s * total + i]);
+        const uint32_t lp = (uint32_t)(i / per_program);
+        const unsigned long long rem = i % per_program, qn = rem / configs, cfg = rem % configs;
+        const size_t gp = prob.first_program + batch.programs[lp].index;
+        prob.output[gp * prob.out_program_stride + (size_t)qn * prob.out_target_stride + cfg] = sum;
     }
 }
 
@@ -764,147 +898,18 @@ __global__ void rk4_validate_kernel(const Rk4Problem prob) {
 
 template <int RR, int RC>
 cudaError_t launch_variant(const DeviceBatch& batch, const EvalProblem& prob, const Geom& geom, const LaunchPlan& plan,
-                           cudaStream_t stream) {
+                           float* partial, cudaStream_t stream) {
     /* approximate math exists for the 16-value tiles, which are the ones the planner picks */
     if (RR * RC <= 16 && prob.fast_math)
-        eval_kernel<RR, RC, (RR * RC <= 16)><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom);
+        eval_kernel<RR, RC, (RR * RC <= 16)><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom, partial);
     else
-    eval_kernel<RR, RC, false><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom);
+        eval_kernel<RR, RC, false><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom, partial);
     return cudaGetLastError();
 }
 
-/* register-tile variants: rows x banks per thread */
-constexpr int kNumVariants = 6;
-constexpr int kVariantRows[kNumVariants] = {4, 8, 16, 8, 16, 32};
-constexpr int kVariantBanks[kNumVariants] = {4, 2, 1, 4, 2, 1};
-
 uint32_t round16(size_t v) { return (uint32_t)((v + 15) / 16 * 16); }
 
-Geom make_geom(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPlan& plan) {
-    const int rr = kVariantRows[plan.variant], rc = kVariantBanks[plan.variant];
-    const uint32_t ncols = prob.num_inputs + (prob.mode == EVAL_MATERIALIZE ? 0u : prob.num_targets);
-    Geom g;
-    g.tile_rows = plan.tile_rows;
-    g.programs_per_cta = plan.programs_per_cta;
-    g.row_splits = plan.row_splits;
-    g.exec_bytes = round16(((size_t)batch.max_insn + 1) * sizeof(SbInsn));
-    g.cst_bytes = round16(((size_t)prob.num_constants + batch.max_extra) * rc * 4 + 16);
-    g.tacc_bytes = round16(((size_t)prob.num_targets + 2) * rc * 4);
-    g.scratch_slot = batch.max_slots; /* one slot beyond what the programs use */
-    g.hoist_bytes = round16((size_t)batch.max_hoisted * plan.tile_rows * 4);
-    g.warp_bytes = g.exec_bytes + g.cst_bytes + g.tacc_bytes + g.hoist_bytes + ((uint32_t)batch.max_slots + 1u) * rr * rc * 128u;
-    g.tile_bytes = round16((size_t)ncols * plan.tile_rows * 4);
-    g.rows_per_split = plan.rows_per_split;
-    g.groups_per_item = plan.groups_per_item ? plan.groups_per_item : 1u;
-    return g;
-}
-
 }  // namespace
-
-LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm_count, size_t smem_limit, int forced_variant) {
-    LaunchPlan plan;
-    plan.ok = false;
-    plan.groups_per_item = 1;
-    int variant = prob.num_banks >= 4 ? 0 : prob.num_banks >= 2 ? 1 : 2;
-    uint32_t forced_warps = 0;
-    if (forced_variant >= 0) { forced_warps = (uint32_t)forced_variant >> 8; forced_variant &= 0xff; } /* tuning hook */
-    if (forced_variant >= 0 && forced_variant < kNumVariants) variant = forced_variant;
-    if (prob.mode == EVAL_MATERIALIZE) variant = 2;
-    plan.variant = variant;
-    const int rr = kVariantRows[variant], rc = kVariantBanks[variant];
-    const uint32_t pass = 32u * rr;
-    const uint32_t ncols = prob.num_inputs + (prob.mode == EVAL_MATERIALIZE ? 0u : prob.num_targets);
-
-    /* rows staged per chunk: as many passes as fit in about a third of shared memory,
-     * never more than the data has */
-    const size_t rows_padded = (prob.num_rows + pass - 1) / pass * pass;
-    size_t tile_rows = ncols ? (smem_limit / 3) / ((size_t)ncols * 4) / pass * pass : rows_padded;
-    if (tile_rows > 4096) tile_rows = 4096 / pass * pass;
-    if (tile_rows < pass) tile_rows = pass;
-    if (tile_rows > rows_padded) tile_rows = rows_padded;
-
-    /* Warps per CTA: 20 when that costs no tile rows (register budget 96 at 640 threads; measured
-     * +8 % over 16 warps, while 22 and 24 warps lose to spills and smaller tiles), else 16, then
-     * whatever still fits.  The 32-value tiles need 168 registers and stop at 12 warps. */
-    static const uint32_t kSmallTile[] = {20, 16, 12, 8, 4, 2, 1, 0}, kLargeTile[] = {12, 8, 4, 2, 1, 0};
-    if (forced_warps > (rr * rc > 16 ? 12u : 20u)) forced_warps = rr * rc > 16 ? 12u : 20u; /* launch bounds */
-    const uint32_t forced_list[] = {forced_warps, 0};
-    const uint32_t* candidates = forced_warps ? forced_list : (rr * rc > 16 ? kLargeTile : kSmallTile);
-    for (; *candidates; ++candidates) {
-        const uint32_t warps = *candidates;
-        LaunchPlan trial = plan;
-        trial.ok = false;
-        trial.warps = warps;
-        trial.tile_rows = (uint32_t)tile_rows;
-        trial.programs_per_cta = 1;
-        trial.row_splits = 1;
-        trial.rows_per_split = prob.num_rows;
-        Geom g = make_geom(batch, prob, trial);
-        size_t need = (size_t)g.tile_bytes + 16 + (size_t)g.warp_bytes * warps;
-        while (need > smem_limit && trial.tile_rows > pass) {
-            trial.tile_rows = (trial.tile_rows / 2 + pass - 1) / pass * pass;
-            g = make_geom(batch, prob, trial);
-            need = (size_t)g.tile_bytes + 16 + (size_t)g.warp_bytes * warps;
-        }
-        if (need > smem_limit) continue;
-        trial.smem_bytes = need;
-        trial.ok = true;
-        if (!plan.ok) {
-            plan = trial;
-            if (warps != 20 || forced_warps) break;
-            continue; /* look at 16 warps too */
-        }
-        if (trial.tile_rows > plan.tile_rows) plan = trial; /* 16 warps keep a larger tile: prefer them */
-        break;
-    }
-    if (!plan.ok) return plan;
-
-    /* Queue items: an item covers up to sixteen bank groups of one permutation, so the prelude of
-     * a program is amortised over them, and never straddles permutations (toggles are patched
-     * per item). */
-    unsigned long long items_per_program = 1;
-    if (prob.mode != EVAL_MATERIALIZE) {
-        const unsigned long long bank_groups = (prob.num_banks + rc - 1) / rc;
-        const unsigned long long cfg_groups = bank_groups << prob.toggle_bits;
-        unsigned long long gpi = bank_groups < 16 ? bank_groups : 16;
-        while (bank_groups % gpi) --gpi;
-        plan.groups_per_item = (uint32_t)gpi;
-        items_per_program = cfg_groups / gpi;
-    }
-    /* Programs per CTA: enough CTAs to fill the machine several times over, and at least
-     * 32 queue items per warp so that the warps of a CTA reach the chunk barrier together
-     * (measured on the benchmark mix: 8 items per warp 2.06e11 row-evals/s, 16: 2.13, 32: 2.16, 64: 2.18). */
-    const uint32_t P = batch.num_programs;
-    const uint32_t target_ctas = (uint32_t)sm_count * 8u;
-    uint32_t ppc = (P + target_ctas - 1) / target_ctas;
-    unsigned long long min_ppc = ((unsigned long long)plan.warps * 32 + items_per_program - 1) / items_per_program;
-    if (min_ppc < 4) min_ppc = 4;
-    if (ppc < min_ppc) ppc = (uint32_t)min_ppc;
-    if (ppc > P) ppc = P;
-    while (items_per_program * ppc > 0xfffffff0ull && ppc > 1) ppc /= 2; /* item ids are 32-bit */
-    const uint32_t groups = (P + ppc - 1) / ppc;
-    plan.programs_per_cta = ppc;
-    /* Split the rows across CTAs as well until the grid is many waves deep: a CTA that walks
-     * every row of a large dataset runs for seconds, and the last partial wave of such CTAs
-     * leaves most of the GPU idle.  Sums are combined with atomic adds either way.  A split
-     * keeps at least eight chunks unless the program groups alone cannot fill the GPU. */
-    uint32_t splits = 1;
-    const size_t chunks = (prob.num_rows + plan.tile_rows - 1) / plan.tile_rows;
-    if (prob.mode != EVAL_MATERIALIZE) {
-        const uint32_t want_ctas = (uint32_t)sm_count * 32u;
-        size_t most = groups < (uint32_t)sm_count * 2u ? chunks : chunks / 8;
-        const size_t fill = ((size_t)sm_count * 2 + groups - 1) / groups; /* splits that fill the GPU twice */
-        if (most < fill) most = fill < chunks ? fill : chunks;
-        splits = (want_ctas + groups - 1) / groups;
-        if (splits > most) splits = (uint32_t)most;
-        if (splits < 1) splits = 1;
-    }
-    const size_t chunks_per_split = (chunks + splits - 1) / splits;
-    plan.rows_per_split = chunks_per_split * plan.tile_rows;
-    plan.row_splits = (uint32_t)((prob.num_rows + plan.rows_per_split - 1) / plan.rows_per_split);
-    plan.grid_x = groups * plan.row_splits;
-    return plan;
-}
 
 #define SB_FOR_VARIANTS(X) X(4, 4) X(8, 2) X(16, 1) X(8, 4) X(16, 2) X(32, 1)
 
@@ -949,16 +954,29 @@ cudaError_t launch_rk4(const DeviceBatch& batch, const Rk4Problem& prob, size_t 
     return cudaGetLastError();
 }
 
-cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPlan& plan, cudaStream_t stream) {
+cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPlan& plan, float* partial,
+                        cudaStream_t stream, unsigned* launches) {
     const Geom geom = make_geom(batch, prob, plan);
+    cudaError_t e;
     switch (plan.variant) {
-    case 0: return launch_variant<4, 4>(batch, prob, geom, plan, stream);
-    case 1: return launch_variant<8, 2>(batch, prob, geom, plan, stream);
-    case 2: return launch_variant<16, 1>(batch, prob, geom, plan, stream);
-    case 3: return launch_variant<8, 4>(batch, prob, geom, plan, stream);
-    case 4: return launch_variant<16, 2>(batch, prob, geom, plan, stream);
-    default: return launch_variant<32, 1>(batch, prob, geom, plan, stream);
+    case 0: e = launch_variant<4, 4>(batch, prob, geom, plan, partial, stream); break;
+    case 1: e = launch_variant<8, 2>(batch, prob, geom, plan, partial, stream); break;
+    case 2: e = launch_variant<16, 1>(batch, prob, geom, plan, partial, stream); break;
+    case 3: e = launch_variant<8, 4>(batch, prob, geom, plan, partial, stream); break;
+    case 4: e = launch_variant<16, 2>(batch, prob, geom, plan, partial, stream); break;
+    default: e = launch_variant<32, 1>(batch, prob, geom, plan, partial, stream); break;
     }
+    if (e != cudaSuccess) return e;
+    *launches = 1;
+    if (prob.mode == EVAL_MATERIALIZE) return cudaSuccess;
+    const uint32_t nq = prob.mode == EVAL_AFFINE_STATS ? prob.num_targets + 2u : prob.num_targets;
+    const unsigned long long configs = (unsigned long long)prob.num_banks << prob.toggle_bits;
+    const unsigned long long total = (unsigned long long)nq * configs * batch.num_programs;
+    const unsigned blocks = (unsigned)std::min<unsigned long long>((total + 255) / 256, 148ull * 16ull);
+    combine_kernel<<<blocks ? blocks : 1u, 256, 0, stream>>>(batch, prob, partial, plan.row_splits, nq, configs);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) *launches = 2;
+    return e;
 }
 
 }  // namespace sb

@@ -33,9 +33,12 @@ struct DeviceBatch {
     const float* lits;
     uint32_t num_programs;
     uint32_t max_insn;    /* largest instruction count in the batch */
-    uint32_t max_extra;   /* largest n_affine + n_lits */
+    uint32_t max_extra;   /* largest n_affine + n_lits (rollout records address source constants directly) */
     uint32_t max_slots;   /* largest spill-slot count */
-    uint32_t max_hoisted; /* largest number of prelude values */
+    uint32_t max_hoisted; /* largest number of row-prelude values */
+    uint32_t max_cst;     /* largest constant table */
+    uint32_t max_btmp;    /* largest number of bank-part temporaries */
+    uint32_t uses_scratch; /* some program needs the scratch spill slot */
 };
 
 struct EvalProblem {
@@ -65,22 +68,52 @@ struct EvalProblem {
 struct LaunchPlan {
     int variant;              /* rows x banks per thread: 0: 4x4, 1: 8x2, 2: 16x1, 3: 8x4, 4: 16x2, 5: 32x1 */
     uint32_t warps;           /* per CTA */
-    uint32_t tile_rows;       /* rows staged per chunk, multiple of the pass size */
-    uint32_t programs_per_cta;
-    uint32_t groups_per_item; /* configuration groups handed to a warp at a time */
+    uint32_t tile_rows;       /* rows staged per tile, multiple of the pass size */
+    uint32_t tile_buffers;    /* 2 when a CTA walks more than one tile: the next tile is fetched while this one is used */
+    uint32_t num_groups;      /* CTAs along the programs; group g owns programs g, g + num_groups, ... */
+    uint32_t groups_per_item; /* bank groups of one permutation a warp handles per queue item */
     uint32_t row_splits;      /* CTAs sharing one program group, each with a row range */
     size_t rows_per_split;
     size_t smem_bytes;
+    size_t partial_elements;  /* floats of per-split partial sums the launch needs (0: materialize) */
     uint32_t grid_x;
     bool ok;
+    bool overflow;            /* !ok because a count does not fit the kernel's 32-bit indices */
 };
+
+/* Shared-memory layout and loop bounds of one launch, derived from the plan. */
+struct Geom {
+    uint32_t tile_rows;       /* floats between consecutive columns of a staged tile */
+    uint32_t tile_buffers;
+    uint32_t tile_bytes;      /* one buffer */
+    uint32_t num_groups;
+    uint32_t row_splits;
+    uint32_t groups_per_item;
+    uint32_t exec_bytes;      /* per-warp regions, each a multiple of 16 bytes */
+    uint32_t table_bytes;
+    uint32_t hoist_bytes;
+    uint32_t slot_bytes;
+    uint32_t psum_bytes;
+    uint32_t warp_bytes;
+    uint32_t scratch_slot;    /* spill slot reserved for the element-by-element FMA */
+    unsigned long long rows_per_split;
+};
+
+constexpr int kNumVariants = 6;
+constexpr int kVariantRows[kNumVariants] = {4, 8, 16, 8, 16, 32};
+constexpr int kVariantBanks[kNumVariants] = {4, 2, 1, 4, 2, 1};
+
+Geom make_geom(const DeviceBatch& batch, const EvalProblem& problem, const LaunchPlan& plan);
 
 LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& problem, int sm_count, size_t smem_limit,
                        int forced_variant /* -1 = automatic */);
 
-/* Enqueues the evaluation of one batch on `stream`.  The output range must have been
- * cleared beforehand for the accumulating modes.  Returns the CUDA status of the launch. */
-cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem& problem, const LaunchPlan& plan, cudaStream_t stream);
+/* Enqueues the evaluation of one batch on `stream`: the evaluator kernel writes per-split partial
+ * sums into `partial` (plan.partial_elements floats, private to the stream until the launch has
+ * finished) and a second kernel adds them in a fixed order into the output, so a result does
+ * not depend on the order CTAs ran in.  Returns the CUDA status of the launches. */
+cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem& problem, const LaunchPlan& plan, float* partial,
+                        cudaStream_t stream, unsigned* launches);
 
 /* Fixed-step RK4 rollout scoring of S-state systems whose right-hand sides are programs. */
 struct Rk4Problem {

@@ -25,13 +25,17 @@
 /* Operand kinds.  Few kinds means few interpreter cases, and the interpreter's hot code has to
  * stay small enough for the instruction caches:
  *   ROW   one float per row: a dataset column (index < SB_ROW_HOISTED) or a bank-independent
- *         value left by the program's prelude (index = SB_ROW_HOISTED | n)
- *   CST   one float per bank: a bank slot, a derived affine entry or a literal of the program
- *   SLOT  one float per (row, bank): a spill slot */
+ *         value left by the program's row prelude (index = SB_ROW_HOISTED | n)
+ *   CST   one float per bank: entry `index` of the program's constant table
+ *   SLOT  one float per (row, bank): a spill slot
+ * Inside the bank part of a program (see SbProgram) the same three codes address the scalar
+ * machine that runs once per coefficient bank: ROW = an entry of the constant table written
+ * earlier in the bank part, CST = a source constant (bank slot k for k < K, then the program's
+ * affine entries, then its literals), SLOT = a scalar temporary. */
 enum { SB_KIND_ROW = 0, SB_KIND_CST = 1, SB_KIND_SLOT = 2, SB_NUM_KINDS = 3 };
-enum { SB_ROW_HOISTED = 0x80 };
-/* For FMA operand descriptors kind 3 means "the accumulator". */
-enum { SB_FMA_ACC = 3 };
+enum { SB_ROW_HOISTED = 0x8000 };
+/* FMA operand descriptors: kind 3 means "the accumulator"; 10-bit indices, bit 9 = hoisted row value. */
+enum { SB_FMA_ACC = 3, SB_FMA_ROW_HOISTED = 0x200 };
 
 /* Binary operations; R* = operand on the left, accumulator on the right. */
 enum { SB_BIN_ADD = 0, SB_BIN_SUB, SB_BIN_RSUB, SB_BIN_MUL, SB_BIN_DIV, SB_BIN_RDIV, SB_BIN_MIN, SB_BIN_MAX, SB_NUM_BIN };
@@ -43,7 +47,7 @@ enum {
     SB_CASE_END = 0,
     SB_CASE_LOAD = 1,                                  /* + kind           : acc = X            */
     SB_CASE_STORE = SB_CASE_LOAD + SB_NUM_KINDS,       /* slot[index] = acc                     */
-    SB_CASE_STOREH = SB_CASE_STORE + 1,                /* hoisted[index] = acc (row part only)  */
+    SB_CASE_STOREH = SB_CASE_STORE + 1,                /* row prelude: hoisted[index] = acc; bank part: table[index] = acc */
     SB_CASE_BIN = SB_CASE_STOREH + 1,                  /* + op * 3 + kind  : acc = acc (op) X   */
     SB_CASE_UN = SB_CASE_BIN + SB_NUM_BIN * SB_NUM_KINDS, /* + op          : acc = f(acc)       */
     SB_CASE_FMA = SB_CASE_UN + SB_NUM_UN,              /* acc = fma(A, B, C), generic operands  */
@@ -70,35 +74,51 @@ typedef struct SbPatch {
     SbInsn alt[4];
 } SbPatch;
 
-/* A derived constant-area entry: bank[slot] * scale + offset, both operations rounded. */
+/* A derived source constant: bank[slot] * scale + offset, both operations rounded. */
 typedef struct SbAffine {
     uint32_t slot;
     float scale;
     float offset;
 } SbAffine;
 
+enum {
+    SB_PROG_BANK_INDEPENDENT = 1, /* the value does not depend on the coefficient bank: every bank scores alike */
+    SB_PROG_USES_SCRATCH = 2      /* an FMA runs over the scratch spill slot */
+};
+
 /* Per-program header; offsets index the pools of the batch the program belongs to.
- * Constant-area entries are laid out [0, K) bank slots, [K, K + n_affine) derived
- * entries, [K + n_affine, K + n_affine + n_lits) the program's literals. */
+ *
+ * A program is up to three instruction runs, each closed by END:
+ *   [0, pre_off)         bank part: everything that depends on the coefficient bank but not on
+ *                        the row (and every constant the other parts read) is computed once per
+ *                        bank by a scalar machine and left in the program's constant table of
+ *                        n_cst entries per bank (STOREH);
+ *   [pre_off, main_off)  row prelude: sub-expressions that depend on the row but not on the bank,
+ *                        evaluated once per row and kept as per-row values (STOREH), which the
+ *                        main part reads as ROW operands with SB_ROW_HOISTED set;
+ *   [main_off, n_insn)   main part, run once per (row tile, bank group).
+ * Values and rounding are those of the plain postfix evaluation: the same operations run on the
+ * same operands, only less often.  Records made for the rollout kernel have a main part only
+ * (pre_off = main_off = 0) and address source constants directly. */
 typedef struct SbProgram {
     uint32_t insn_off;
     uint32_t patch_off;
     uint32_t affine_off;
     uint32_t lit_off;
-    uint16_t n_insn; /* including the END instruction */
+    uint16_t n_insn; /* all parts, including their END instructions */
     uint16_t n_patch;
     uint16_t n_affine;
     uint16_t n_lits;
     uint16_t n_slots;
     uint16_t n_ops; /* arithmetic nodes after routine inlining, for work accounting */
-    /* Instructions [0, main_off) form the prelude: sub-expressions that do not depend on the
-     * coefficient bank, evaluated once per row chunk and kept as per-row values (STOREH); the
-     * main part starting at main_off runs once per bank group and reads them back as ROW
-     * operands with SB_ROW_HOISTED set.  0 = no prelude. */
+    uint16_t pre_off;
     uint16_t main_off;
-    uint16_t n_hoisted;
-    uint32_t index;    /* position of the program in the run (output row, bank table) */
-    uint32_t reserved;
+    uint16_t n_hoisted; /* per-row values the prelude leaves */
+    uint16_t n_cst;     /* constant-table entries per bank */
+    uint16_t n_btmp;    /* scalar temporaries of the bank part */
+    uint16_t flags;     /* SB_PROG_* */
+    uint32_t index;     /* position of the program in the run (output row, bank table) */
+    uint32_t cost;      /* scheduling weight: bits 0..15 main part per bank group, bits 16..31 row prelude */
 } SbProgram;
 
 #endif

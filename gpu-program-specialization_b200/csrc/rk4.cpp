@@ -113,6 +113,7 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
     cudaError_t e = cudaMemcpy(d, host.data(), total, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) {
         DeviceBatch db;
+        std::memset(&db, 0, sizeof(db));
         db.programs = reinterpret_cast<const SbProgram*>(d);
         db.insns = reinterpret_cast<const SbInsn*>(d + o_insn);
         db.patches = reinterpret_cast<const SbPatch*>(d + o_patch);

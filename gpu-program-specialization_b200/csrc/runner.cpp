@@ -86,6 +86,8 @@ struct SecantCubinRunnerImpl {
     int device = 0, sm_count = 0;
     size_t smem_limit = 0;
     std::vector<cudaStream_t> streams;
+    std::vector<void*> scratch;      /* per compute stream: partial sums of the launch in flight */
+    std::vector<size_t> scratch_cap;
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t ev_cleared = nullptr, ev_start = nullptr, ev_stop = nullptr;
     std::vector<Slot> slots;
@@ -188,6 +190,8 @@ SecantResult runner_init(SecantCubinRunnerImpl* r, const SecantCubinRunnerOption
     SB_CUDA(configure_kernels(), "kernel attributes");
     r->streams.resize(options->num_streams);
     for (auto& s : r->streams) SB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "cudaStreamCreate");
+    r->scratch.assign(r->streams.size(), nullptr);
+    r->scratch_cap.assign(r->streams.size(), 0);
     SB_CUDA(cudaStreamCreateWithFlags(&r->copy_stream, cudaStreamNonBlocking), "cudaStreamCreate");
     SB_CUDA(cudaEventCreateWithFlags(&r->ev_cleared, cudaEventDisableTiming), "cudaEventCreate");
     SB_CUDA(cudaEventCreate(&r->ev_start), "cudaEventCreate");
@@ -230,6 +234,7 @@ SecantResult runner_teardown(SecantCubinRunnerImpl* r) {
         for (auto& e : s.done) if (e) check(cudaEventDestroy(e));
         s.pinned = s.device = nullptr; s.uploaded = nullptr; s.done.clear();
     }
+    for (auto& p : r->scratch) if (p) { check(cudaFree(p)); p = nullptr; }
     for (auto& s : r->streams) if (s) { check(cudaStreamDestroy(s)); s = nullptr; }
     if (r->copy_stream) { check(cudaStreamDestroy(r->copy_stream)); r->copy_stream = nullptr; }
     if (r->ev_cleared) { check(cudaEventDestroy(r->ev_cleared)); r->ev_cleared = nullptr; }
@@ -266,28 +271,32 @@ SecantResult create_common(SecantCubinRunnerImpl* r, const SecantCubinRunnerOpti
     return SECANT_SUCCESS;
 }
 
+/* Programs whose per-warp working set (spill slots, constant table, hoisted row values) is larger
+ * than this are launched separately, so that the shared-memory budget of the common case is not
+ * sized by rare programs. */
+constexpr unsigned kLightSlots = 2, kLightTable = 8, kLightHoisted = 4;
+
+bool is_light(const SbProgram& p) { return p.n_slots <= kLightSlots && p.n_cst <= kLightTable && p.n_hoisted <= kLightHoisted; }
+
+/* scheduling weight of a program: one row pass over sixteen bank groups */
+uint64_t schedule_cost(const SbProgram& p) {
+    const uint64_t main_part = p.cost & 0xffffu, prelude = p.cost >> 16;
+    return main_part * ((p.flags & SB_PROG_BANK_INDEPENDENT) ? 1u : 16u) + prelude;
+}
+
 /* Copies an encoded batch into the slot's pinned buffer, grows the device buffer when
  * needed, and enqueues the upload.  Layout: programs | insns | patches | affines | lits. */
-/* Programs that need more than this many spill slots are launched separately, so that the
- * shared-memory budget of the common case (16 warps per CTA) is not sized by rare programs. */
-constexpr unsigned kLightSlots = 2;
-
 SecantResult upload_batch(SecantCubinRunnerImpl* r, Slot& s, std::vector<DeviceBatch>* views) {
     EncodedBatch& e = s.enc;
     /* light programs first, heavy ones after them; SbProgram::index keeps their place in the run */
-    std::stable_partition(e.programs.begin(), e.programs.end(), [](const SbProgram& p) { return p.n_slots <= kLightSlots; });
-    /* inside each group, costly programs first: CTAs then start with the long work and the
-     * items dealt round-robin to the warp teams of a CTA are of similar cost */
-    const auto light_end = std::find_if(e.programs.begin(), e.programs.end(), [](const SbProgram& p) { return p.n_slots > kLightSlots; });
-    const auto by_cost = [](const SbProgram& a, const SbProgram& b) { return a.n_insn > b.n_insn; };
+    std::stable_partition(e.programs.begin(), e.programs.end(), is_light);
+    /* inside each group, costly programs first: every CTA takes a strided subset, so its queue runs
+     * from its costliest item to its cheapest and its warps finish a tile close together */
+    const auto light_end = std::find_if(e.programs.begin(), e.programs.end(), [](const SbProgram& p) { return !is_light(p); });
+    const auto by_cost = [](const SbProgram& a, const SbProgram& b) { return schedule_cost(a) > schedule_cost(b); };
     std::stable_sort(e.programs.begin(), light_end, by_cost);
     std::stable_sort(light_end, e.programs.end(), by_cost);
-    size_t num_light = 0;
-    unsigned light_slots = 0, heavy_slots = 0;
-    for (const auto& p : e.programs) {
-        if (p.n_slots <= kLightSlots) { ++num_light; light_slots = std::max<unsigned>(light_slots, p.n_slots); }
-        else heavy_slots = std::max<unsigned>(heavy_slots, p.n_slots);
-    }
+    const size_t num_light = (size_t)(light_end - e.programs.begin());
     const size_t o_prog = 0;
     const size_t o_insn = align256(o_prog + e.programs.size() * sizeof(SbProgram));
     const size_t o_patch = align256(o_insn + e.insns.size() * sizeof(SbInsn));
@@ -315,25 +324,29 @@ SecantResult upload_batch(SecantCubinRunnerImpl* r, Slot& s, std::vector<DeviceB
     SB_CUDA(cudaMemcpyAsync(s.device, s.pinned, total, cudaMemcpyHostToDevice, r->copy_stream), "program upload");
     SB_CUDA(cudaEventRecord(s.uploaded, r->copy_stream), "cudaEventRecord");
     const char* d = static_cast<const char*>(s.device);
-    DeviceBatch db;
-    db.insns = reinterpret_cast<const SbInsn*>(d + o_insn);
-    db.patches = reinterpret_cast<const SbPatch*>(d + o_patch);
-    db.affines = reinterpret_cast<const SbAffine*>(d + o_aff);
-    db.lits = reinterpret_cast<const float*>(d + o_lit);
-    db.max_insn = e.max_insn;
-    db.max_extra = e.max_extra;
-    db.max_hoisted = e.max_hoisted;
     views->clear();
-    if (num_light) {
-        db.programs = reinterpret_cast<const SbProgram*>(d + o_prog);
-        db.num_programs = (uint32_t)num_light;
-        db.max_slots = light_slots;
-        views->push_back(db);
-    }
-    if (num_light < e.programs.size()) {
-        db.programs = reinterpret_cast<const SbProgram*>(d + o_prog) + num_light;
-        db.num_programs = (uint32_t)(e.programs.size() - num_light);
-        db.max_slots = heavy_slots;
+    const size_t bounds[3] = {0, num_light, e.programs.size()};
+    for (int k = 0; k < 2; ++k) {
+        if (bounds[k] == bounds[k + 1]) continue;
+        DeviceBatch db;
+        std::memset(&db, 0, sizeof(db));
+        db.insns = reinterpret_cast<const SbInsn*>(d + o_insn);
+        db.patches = reinterpret_cast<const SbPatch*>(d + o_patch);
+        db.affines = reinterpret_cast<const SbAffine*>(d + o_aff);
+        db.lits = reinterpret_cast<const float*>(d + o_lit);
+        db.programs = reinterpret_cast<const SbProgram*>(d + o_prog) + bounds[k];
+        db.num_programs = (uint32_t)(bounds[k + 1] - bounds[k]);
+        db.max_insn = 1;
+        for (size_t i = bounds[k]; i < bounds[k + 1]; ++i) {
+            const SbProgram& p = e.programs[i];
+            db.max_insn = std::max<uint32_t>(db.max_insn, p.n_insn);
+            db.max_extra = std::max<uint32_t>(db.max_extra, (uint32_t)p.n_affine + p.n_lits);
+            db.max_slots = std::max<uint32_t>(db.max_slots, p.n_slots);
+            db.max_hoisted = std::max<uint32_t>(db.max_hoisted, p.n_hoisted);
+            db.max_cst = std::max<uint32_t>(db.max_cst, p.n_cst);
+            db.max_btmp = std::max<uint32_t>(db.max_btmp, p.n_btmp);
+            db.uses_scratch |= (p.flags & SB_PROG_USES_SCRATCH) ? 1u : 0u;
+        }
         views->push_back(db);
     }
     return SECANT_SUCCESS;
@@ -373,29 +386,56 @@ EvalProblem make_problem(const SecantCubinPlan& plan, const UnpackedRun& run, si
     return p;
 }
 
+/* Per-stream scratch for the evaluator's per-split partial sums.  Launches on one stream run in
+ * order, so the evaluator and the kernel that folds its partial sums may reuse the buffer of the
+ * launch before them; growing it waits for the stream first. */
+SecantResult stream_scratch(SecantCubinRunnerImpl* r, size_t k, size_t elements, float** out) {
+    const size_t bytes = elements * sizeof(float);
+    if (elements > SIZE_MAX / sizeof(float)) return SECANT_ERROR_OVERFLOW;
+    if (r->scratch_cap[k] < bytes) {
+        SB_CUDA(cudaStreamSynchronize(r->streams[k]), "cudaStreamSynchronize");
+        if (r->scratch[k]) SB_CUDA(cudaFree(r->scratch[k]), "cudaFree");
+        r->scratch[k] = nullptr; r->scratch_cap[k] = 0;
+        const size_t want = bytes + bytes / 4;
+        if (cudaMalloc(&r->scratch[k], want) != cudaSuccess) {
+            (void)cudaGetLastError();
+            r->last_error = "no device memory for the partial sums of a launch";
+            return SECANT_ERROR_ALLOCATION_FAILED;
+        }
+        r->scratch_cap[k] = want;
+    }
+    *out = static_cast<float*>(r->scratch[k]);
+    return SECANT_SUCCESS;
+}
+
 /* Enqueues the evaluation of one device-resident batch for every run entry, spreading
  * entries over the compute streams.  `after` (optional) is an event each stream waits on
  * first; `done`/`used` (optional) receive one completion event per touched stream. */
-SecantResult launch_batch(SecantCubinRunnerImpl* r, const DeviceBatch& db, size_t first_program,
-                          const std::vector<UnpackedRun>& runs, size_t* stream_cursor, cudaEvent_t after,
-                          std::vector<cudaEvent_t>* done, std::vector<char>* used) {
+SecantResult launch_batch(SecantCubinRunnerImpl* r, const DeviceBatch& db, const std::vector<UnpackedRun>& runs,
+                          size_t* stream_cursor, cudaEvent_t after, std::vector<cudaEvent_t>* done, std::vector<char>* used) {
     const SecantCubinPlan& plan = *r->plan;
     for (size_t e = 0; e < runs.size(); ++e) {
         const size_t k = (*stream_cursor)++ % r->streams.size();
         cudaStream_t stream = r->streams[k];
-        EvalProblem prob = make_problem(plan, runs[e], 0);
+        EvalProblem prob = make_problem(plan, runs[e], 0); /* SbProgram::index already places every program in the run */
         prob.fast_math = r->fast_math;
-        (void)first_program; /* SbProgram::index already places every program in the run */
         if (runs[e].program_bank_stride)
             prob.banks = reinterpret_cast<const float*>(runs[e].banks.address) + runs[e].first_program_index * runs[e].program_bank_stride;
         const LaunchPlan lp = plan_launch(db, prob, r->sm_count, r->smem_limit, r->forced_variant);
-        if (!lp.ok) { r->last_error = "program batch does not fit shared memory"; return SECANT_ERROR_REGISTER_OVERFLOW; }
-        cudaError_t ce = after ? cudaStreamWaitEvent(stream, after, 0) : cudaSuccess;
-        if (ce == cudaSuccess) ce = launch_eval(db, prob, lp, stream);
-        if (ce == cudaSuccess) {
-            g_kernel_launches.fetch_add(1);
-            if (done) ce = cudaEventRecord((*done)[k], stream);
+        if (!lp.ok) {
+            r->last_error = lp.overflow ? "configuration count beyond the evaluator's 32-bit item index" : "program batch does not fit shared memory";
+            return lp.overflow ? SECANT_ERROR_OVERFLOW : SECANT_ERROR_REGISTER_OVERFLOW;
         }
+        float* partial = nullptr;
+        if (lp.partial_elements) {
+            const SecantResult a = stream_scratch(r, k, lp.partial_elements, &partial);
+            if (a != SECANT_SUCCESS) return a;
+        }
+        unsigned launches = 0;
+        cudaError_t ce = after ? cudaStreamWaitEvent(stream, after, 0) : cudaSuccess;
+        if (ce == cudaSuccess) ce = launch_eval(db, prob, lp, partial, stream, &launches);
+        g_kernel_launches.fetch_add(launches);
+        if (ce == cudaSuccess && done) ce = cudaEventRecord((*done)[k], stream);
         if (ce != cudaSuccess) return cuda_fail(r, ce, "kernel launch");
         if (used) (*used)[k] = 1;
     }
@@ -480,7 +520,7 @@ SecantResult execute(SecantCubinRunnerImpl* r, const std::vector<UnpackedRun>& r
         upload_seconds += now_seconds() - t_up;
         if (result != SECANT_SUCCESS) break;
         for (const DeviceBatch& db : views) {
-            result = launch_batch(r, db, slot->first_program, runs, &stream_cursor, slot->uploaded, &slot->done, &slot->used);
+            result = launch_batch(r, db, runs, &stream_cursor, slot->uploaded, &slot->done, &slot->used);
             if (result != SECANT_SUCCESS) break;
         }
         in_flight.push_back(slot);
@@ -710,7 +750,7 @@ SecantResult execute_resident(SecantCubinRunnerImpl* r, SecantB200PopulationImpl
     SecantResult result = SECANT_SUCCESS;
     for (auto& b : pop->batches) {
         for (const DeviceBatch& db : b.views) {
-            result = launch_batch(r, db, b.first, runs, &cursor, nullptr, nullptr, nullptr);
+            result = launch_batch(r, db, runs, &cursor, nullptr, nullptr, nullptr);
             if (result != SECANT_SUCCESS) break;
         }
         if (result != SECANT_SUCCESS) break;
@@ -761,7 +801,9 @@ SecantResult secant_b200_population_create(SecantCubinRunner r, const SecantAstP
     rules.num_constants = plan.num_constants;
     rules.banks_allowed = plan.shape == SECANT_KERNEL_SHAPE_TOGGLE_SSE_F32;
     rules.toggle_bits = rules.banks_allowed ? toggle_bits : 0;
-    rules.hoist_invariants = rules.banks_allowed; /* a population is usually scored against many banks */
+    rules.split_parts = true;
+    rules.hoist_bank = true;
+    rules.hoist_row = rules.banks_allowed; /* a population is usually scored against many banks */
     for (size_t i = 0; i < programs->routines.count; ++i) {
         const SecantResult s = preflight(programs->routines.items[i], rules);
         if (s != SECANT_SUCCESS) return s;

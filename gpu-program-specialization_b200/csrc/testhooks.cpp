@@ -10,6 +10,7 @@
  */
 #include "encoder.h"
 
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <new>
@@ -26,10 +27,12 @@ struct SbtBatch {
 
 SBT_EXPORT int sbt_encode(const uint8_t* routine_blob, const uint64_t* routine_off, size_t num_routines,
                           const uint8_t* ast_blob, const uint64_t* ast_off, size_t num_asts, size_t num_columns,
-                          size_t num_constants, int banks_allowed, unsigned toggle_bits, int run_preflight,
+                          size_t num_constants, int banks_allowed, unsigned toggle_bits, int flags,
                           SbtBatch** out) {
-    const bool hoist = (run_preflight & 2) != 0; /* bit 1 of the flag word asks for the prelude split */
-    run_preflight &= 1;
+    /* flags: bit 0 run the preflight scan first; bit 1 hoist bank-only and row-only sub-expressions;
+     * bit 2 one-part records with direct constant addressing (the rollout kernel's form);
+     * bits 8.. cap on hoisted row values (0 = default) */
+    const bool run_preflight = (flags & 1) != 0, hoist = (flags & 2) != 0, flat = (flags & 4) != 0;
     std::vector<const SecantAstInstruction*> routines(num_routines), asts(num_asts);
     for (size_t i = 0; i < num_routines; ++i) routines[i] = routine_blob + routine_off[i];
     for (size_t i = 0; i < num_asts; ++i) asts[i] = ast_blob + ast_off[i];
@@ -42,7 +45,10 @@ SBT_EXPORT int sbt_encode(const uint8_t* routine_blob, const uint64_t* routine_o
     b->rules.num_constants = num_constants;
     b->rules.banks_allowed = banks_allowed != 0;
     b->rules.toggle_bits = toggle_bits;
-    b->rules.hoist_invariants = hoist;
+    b->rules.split_parts = !flat;
+    b->rules.hoist_bank = hoist && !flat;
+    b->rules.hoist_row = hoist && !flat;
+    if (flags >> 8) b->rules.max_hoisted = (unsigned)(flags >> 8);
     SecantResult r = SECANT_SUCCESS;
     if (run_preflight) {
         for (size_t i = 0; i < num_routines && r == SECANT_SUCCESS; ++i) r = preflight(routines[i], b->rules);
@@ -57,23 +63,24 @@ SBT_EXPORT int sbt_encode(const uint8_t* routine_blob, const uint64_t* routine_o
 
 SBT_EXPORT void sbt_free(SbtBatch* b) { delete b; }
 
-SBT_EXPORT void sbt_info(const SbtBatch* b, size_t program, uint32_t* n_insn, uint32_t* n_slots, uint32_t* n_ops,
-                         uint32_t* n_patch, uint32_t* n_affine, uint32_t* n_lits) {
-    /* with the prelude split requested, n_patch / n_affine report main_off / n_hoisted instead */
+/* info[0..9] = n_insn, n_slots, n_ops, n_patch, n_affine, n_lits, pre_off, main_off, n_hoisted, n_cst;
+ * info[10] = n_btmp, info[11] = flags */
+SBT_EXPORT void sbt_info(const SbtBatch* b, size_t program, uint32_t* info) {
     const SbProgram& p = b->enc.programs[program];
-    *n_insn = p.n_insn; *n_slots = p.n_slots; *n_ops = p.n_ops; *n_lits = p.n_lits;
-    *n_patch = b->rules.hoist_invariants ? p.main_off : p.n_patch;
-    *n_affine = b->rules.hoist_invariants ? p.n_hoisted : p.n_affine;
+    const uint32_t v[12] = {p.n_insn, p.n_slots, p.n_ops, p.n_patch, p.n_affine, p.n_lits,
+                            p.pre_off, p.main_off, p.n_hoisted, p.n_cst, p.n_btmp, p.flags};
+    for (int i = 0; i < 12; ++i) info[i] = v[i];
 }
 
-/* Instruction counts by case id over all programs: prelude[SB_NUM_CASES] for the
- * bank-independent part, main[SB_NUM_CASES] for the part repeated per bank group. */
-SBT_EXPORT unsigned sbt_case_histogram(const SbtBatch* b, uint64_t* prelude, uint64_t* main_part) {
-    for (unsigned c = 0; c < SB_NUM_CASES; ++c) prelude[c] = main_part[c] = 0;
+/* Instruction counts by case id over all programs, per part:
+ * hist[0][..] bank part, hist[1][..] row prelude, hist[2][..] main part. */
+SBT_EXPORT unsigned sbt_case_histogram(const SbtBatch* b, uint64_t* hist) {
+    for (unsigned c = 0; c < 3 * SB_NUM_CASES; ++c) hist[c] = 0;
     for (const SbProgram& p : b->enc.programs)
         for (unsigned i = 0; i < p.n_insn; ++i) {
             const unsigned c = b->enc.insns[p.insn_off + i].w0 & 0xffu;
-            if (c < SB_NUM_CASES) (i < p.main_off ? prelude : main_part)[c]++;
+            const unsigned part = i < p.pre_off ? 0u : i < p.main_off ? 1u : 2u;
+            if (c < SB_NUM_CASES) hist[part * SB_NUM_CASES + c]++;
         }
     return SB_NUM_CASES;
 }
@@ -107,7 +114,11 @@ static float apply_un(unsigned op, float a) {
     }
 }
 
-/* Value of program `program` on `row` for one bank vector and one permutation. */
+/* Value of program `program` on `row` for one bank vector and one permutation: the bank part
+ * once (filling the constant table), the row prelude once, then the main part twice with every
+ * spill slot poisoned in between, as the device runs the main part once per bank group after
+ * one prelude: a main part that relied on a slot written by the prelude or by its own previous
+ * run is caught. */
 SBT_EXPORT int sbt_eval(const SbtBatch* b, size_t program, const float* input, size_t input_ld, size_t row,
                         const float* bank, uint64_t permutation, float* value) {
     const EncodedBatch& e = b->enc;
@@ -118,63 +129,80 @@ SBT_EXPORT int sbt_eval(const SbtBatch* b, size_t program, const float* input, s
         const SbPatch& s = e.patches[p.patch_off + i];
         unsigned choice = (unsigned)(permutation >> s.bit0) & 1u;
         if (s.bit1 != 0xff) choice |= ((unsigned)(permutation >> s.bit1) & 1u) << 1;
+        if (s.insn >= code.size()) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
         code[s.insn] = s.alt[choice];
     }
-    std::vector<float> cst(K + p.n_affine + p.n_lits, 0.0f);
-    for (size_t k = 0; k < K; ++k) cst[k] = bank ? bank[k] : 0.0f;
+    std::vector<float> source(K + p.n_affine + p.n_lits, 0.0f);
+    for (size_t k = 0; k < K; ++k) source[k] = bank ? bank[k] : 0.0f;
     for (unsigned j = 0; j < p.n_affine; ++j) {
         const SbAffine& a = e.affines[p.affine_off + j];
         volatile float scaled = bank[a.slot] * a.scale;
-        cst[K + j] = scaled + a.offset;
+        source[K + j] = scaled + a.offset;
     }
-    for (unsigned j = 0; j < p.n_lits; ++j) cst[K + p.n_affine + j] = e.lits[p.lit_off + j];
-    std::vector<float> slots(p.n_slots ? p.n_slots : 1, 0.0f);
-    std::vector<float> hoisted(p.n_hoisted ? p.n_hoisted : 1, 0.0f);
-    float acc = 0.0f;
-    bool second_round = false;
-    auto operand = [&](unsigned kind, unsigned index, uint32_t imm) -> float {
+    for (unsigned j = 0; j < p.n_lits; ++j) source[K + p.n_affine + j] = e.lits[p.lit_off + j];
+    const bool split = b->rules.split_parts;
+    std::vector<float> table(p.n_cst ? p.n_cst : 1, std::nanf(""));
+    std::vector<float> slots(std::max<unsigned>(1, std::max(p.n_slots, p.n_btmp)), std::nanf(""));
+    std::vector<float> hoisted(p.n_hoisted ? p.n_hoisted : 1, std::nanf(""));
+    float acc = std::nanf("");
+    int part = 0; /* 0 bank, 1 prelude, 2 main */
+    bool failed = false;
+    auto operand = [&](unsigned kind, unsigned index, bool fma) -> float {
+        const unsigned hflag = fma ? (unsigned)SB_FMA_ROW_HOISTED : (unsigned)SB_ROW_HOISTED;
         switch (kind) {
-        case SB_KIND_ROW: return (index & SB_ROW_HOISTED) ? hoisted[index & 0x7f] : input[(size_t)index * input_ld + row];
-        case SB_KIND_CST: return cst[index];
-        default: (void)imm; return slots[index];
+        case SB_KIND_ROW:
+            if (part == 0) { if (index >= table.size()) { failed = true; return 0; } return table[index]; }
+            if (index & hflag) { const unsigned h = index & (hflag - 1); if (h >= hoisted.size()) { failed = true; return 0; } return hoisted[h]; }
+            return input[(size_t)index * input_ld + row];
+        case SB_KIND_CST:
+            if (!split || part == 0) { if (index >= source.size()) { failed = true; return 0; } return source[index]; }
+            if (index >= p.n_cst) { failed = true; return 0; }
+            return table[index];
+        default:
+            if (index >= slots.size()) { failed = true; return 0; }
+            return slots[index];
         }
     };
-    for (size_t pc = 0; pc < code.size(); ++pc) {
-        const SbInsn ins = code[pc];
-        const unsigned cs = ins.w0 & 0xffu, index = ins.w0 >> 16;
-        if (cs == SB_CASE_END) {
-            if (pc + 1 <= p.main_off) continue; /* end of the prelude: fall through into the main part */
-            if (p.main_off && !second_round) {
-                /* The device runs the main part once per bank group after ONE prelude: do it a
-                 * second time with every spill slot poisoned, so a main part that relied on a
-                 * slot written by the prelude or by its own previous run is caught. */
-                second_round = true;
-                for (auto& v : slots) v = std::nanf("");
-                acc = std::nanf("");
-                pc = (size_t)p.main_off - 1;
-                continue;
-            }
-            *value = acc;
-            return SECANT_SUCCESS;
+    auto run_part = [&](size_t begin, int which) -> bool {
+        part = which;
+        for (size_t pc = begin; pc < code.size(); ++pc) {
+            const SbInsn ins = code[pc];
+            const unsigned cs = ins.w0 & 0xffu, index = ins.w0 >> 16;
+            if (cs == SB_CASE_END) return !failed;
+            if (cs >= SB_CASE_LOAD && cs < SB_CASE_LOAD + SB_NUM_KINDS) acc = operand(cs - SB_CASE_LOAD, index, false);
+            else if (cs == SB_CASE_STORE) { if (index >= slots.size()) return false; slots[index] = acc; }
+            else if (cs == SB_CASE_STOREH) {
+                std::vector<float>& dst = which == 0 ? table : hoisted;
+                if (which == 2 || index >= dst.size()) return false;
+                dst[index] = acc;
+            } else if (cs >= SB_CASE_BIN && cs < SB_CASE_UN) {
+                const unsigned rel = cs - SB_CASE_BIN;
+                acc = apply_bin(rel / SB_NUM_KINDS, acc, operand(rel % SB_NUM_KINDS, index, false));
+            } else if (cs >= SB_CASE_UN && cs < SB_CASE_FMA) acc = apply_un(cs - SB_CASE_UN, acc);
+            else if (cs == SB_CASE_FMA) {
+                const unsigned kinds = (ins.w0 >> 8) & 0x3fu;
+                float v[3];
+                for (int i = 0; i < 3; ++i) {
+                    const unsigned kind = (kinds >> (2 * i)) & 3u, idx = (ins.w1 >> (10 * i)) & 1023u;
+                    v[i] = kind == SB_FMA_ACC ? acc : operand(kind, idx, true);
+                }
+                acc = fmaf(v[0], v[1], v[2]);
+            } else return false;
         }
-        if (cs >= SB_CASE_LOAD && cs < SB_CASE_LOAD + SB_NUM_KINDS) acc = operand(cs - SB_CASE_LOAD, index, ins.w1);
-        else if (cs == SB_CASE_STORE) slots[index] = acc;
-        else if (cs == SB_CASE_STOREH) hoisted[index] = acc;
-        else if (cs >= SB_CASE_BIN && cs < SB_CASE_UN) {
-            const unsigned rel = cs - SB_CASE_BIN;
-            acc = apply_bin(rel / SB_NUM_KINDS, acc, operand(rel % SB_NUM_KINDS, index, ins.w1));
-        } else if (cs >= SB_CASE_UN && cs < SB_CASE_FMA) acc = apply_un(cs - SB_CASE_UN, acc);
-        else if (cs == SB_CASE_FMA) {
-            const unsigned kinds = (ins.w0 >> 8) & 0x3fu;
-            float v[3];
-            for (int i = 0; i < 3; ++i) {
-                const unsigned kind = (kinds >> (2 * i)) & 3u, idx = (ins.w1 >> (10 * i)) & 1023u;
-                v[i] = kind == SB_FMA_ACC ? acc : operand(kind, idx, 0);
-            }
-            acc = fmaf(v[0], v[1], v[2]);
-        } else return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
+        return false;
+    };
+    if (p.pre_off && !run_part(0, 0)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
+    if (p.main_off > p.pre_off) {
+        for (auto& v : slots) v = std::nanf("");
+        if (!run_part(p.pre_off, 1)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
     }
-    return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
+    for (int round = 0; round < 2; ++round) {
+        for (auto& v : slots) v = std::nanf("");
+        acc = std::nanf("");
+        if (!run_part(p.main_off, 2)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
+    }
+    *value = acc;
+    return SECANT_SUCCESS;
 }
 
 /* Runs the request validation the runner performs before it clears or launches anything
@@ -194,4 +222,35 @@ SBT_EXPORT int sbt_validate_runs(const SecantCubinRecipeHeader* recipe, const Se
     }
     ProgramRules rules;
     return runs_validate(plan, runs.data(), count, &rules);
+}
+
+/* Launch geometry the runner would pick for a batch with the given maxima (planner.cpp), so its
+ * bounds can be checked without a device.  Returns 1 when a plan exists, 0 when the batch does not
+ * fit shared memory, -1 when a count does not fit the kernel's 32-bit indices.
+ * out[0..12] = variant, warps, tile_rows, tile_buffers, num_groups, groups_per_item, row_splits,
+ * rows_per_split, smem_bytes, partial_elements, grid_x, warp_bytes, items per CTA and tile. */
+#include "evaluator.cuh"
+SBT_EXPORT int sbt_plan(uint32_t num_programs, uint32_t max_insn, uint32_t max_slots, uint32_t max_hoisted, uint32_t max_cst,
+                        uint32_t max_btmp, int mode, uint32_t num_inputs, uint32_t num_targets, uint32_t num_banks,
+                        uint32_t toggle_bits, uint64_t rows, int sm_count, uint64_t smem_limit, uint64_t* out) {
+    DeviceBatch db;
+    std::memset(&db, 0, sizeof(db));
+    db.num_programs = num_programs; db.max_insn = max_insn; db.max_slots = max_slots; db.max_hoisted = max_hoisted;
+    db.max_cst = max_cst; db.max_btmp = max_btmp;
+    EvalProblem p;
+    std::memset(&p, 0, sizeof(p));
+    p.mode = mode; p.num_inputs = num_inputs; p.num_targets = num_targets; p.num_banks = num_banks; p.toggle_bits = toggle_bits;
+    p.num_rows = rows;
+    const LaunchPlan plan = plan_launch(db, p, sm_count, smem_limit, -1);
+    if (!plan.ok) return plan.overflow ? -1 : 0;
+    const Geom g = make_geom(db, p, plan);
+    const uint64_t rc = (uint64_t)kVariantBanks[plan.variant];
+    const uint64_t bank_groups = mode == EVAL_MATERIALIZE ? 1 : (num_banks + rc - 1) / rc;
+    const uint64_t items_per_program = mode == EVAL_MATERIALIZE ? 1 : (bank_groups / plan.groups_per_item) << toggle_bits;
+    const uint64_t per_cta = (num_programs + plan.num_groups - 1) / plan.num_groups;
+    const uint64_t v[13] = {(uint64_t)plan.variant, plan.warps, plan.tile_rows, plan.tile_buffers, plan.num_groups, plan.groups_per_item,
+                            plan.row_splits, plan.rows_per_split, plan.smem_bytes, plan.partial_elements, plan.grid_x, g.warp_bytes,
+                            per_cta * items_per_program};
+    for (int i = 0; i < 13; ++i) out[i] = v[i];
+    return 1;
 }

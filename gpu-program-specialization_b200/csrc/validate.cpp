@@ -165,11 +165,13 @@ SecantResult runs_validate(const SecantCubinPlan& plan, const UnpackedRun* runs,
     rules.num_constants = plan.num_constants;
     rules.banks_allowed = plan.shape == SECANT_KERNEL_SHAPE_TOGGLE_SSE_F32;
     rules.toggle_bits = rules.banks_allowed ? bits : 0;
-    /* bank-independent sub-expressions are worth a prelude as soon as a program is evaluated
-     * for more than one group of four banks */
-    rules.hoist_invariants = false;
+    /* records in three parts; row-only sub-expressions are worth a prelude as soon as a program
+     * is evaluated for more than one group of four banks */
+    rules.split_parts = true;
+    rules.hoist_bank = true;
+    rules.hoist_row = false;
     if (rules.banks_allowed)
-        for (size_t i = 0; i < count; ++i) rules.hoist_invariants = rules.hoist_invariants || runs[i].num_banks > 4;
+        for (size_t i = 0; i < count; ++i) rules.hoist_row = rules.hoist_row || runs[i].num_banks > 4;
     for (size_t i = 0; !skip_preflight && i < programs.routines.count; ++i) {
         const SecantResult s = preflight(programs.routines.items[i], rules);
         if (s != SECANT_SUCCESS) return s;

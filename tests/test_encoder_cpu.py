@@ -11,11 +11,22 @@ import support as S
 from secant_b200 import abi, programs as P
 
 
-def encode(packed, columns, constants, banks_allowed=True, toggle_bits=0, preflight=True, hoist=False):
+def encode(packed, columns, constants, banks_allowed=True, toggle_bits=0, preflight=True, hoist=False, flat=False,
+           max_hoisted=0):
+    """hoist: bank-only and row-only sub-expressions move to the bank part and the row prelude;
+    flat: one-part records with direct constant addressing (the rollout kernel's form)."""
     handle = C.c_void_p()
+    flags = int(preflight) | (2 if hoist else 0) | (4 if flat else 0) | (max_hoisted << 8)
     code = S.hooks().sbt_encode(*S.blob_args(packed), C.c_size_t(columns), C.c_size_t(constants), int(banks_allowed),
-                                toggle_bits, int(preflight) | (2 if hoist else 0), C.byref(handle))
+                                toggle_bits, flags, C.byref(handle))
     return code, handle
+
+
+def info(handle, index):
+    """n_insn, n_slots, n_ops, n_patch, n_affine, n_lits, pre_off, main_off, n_hoisted, n_cst, n_btmp, flags"""
+    out = (C.c_uint32 * 12)()
+    S.hooks().sbt_info(handle, C.c_size_t(index), out)
+    return list(out)
 
 
 def host_eval(handle, index, x, bank, perm, row):
@@ -31,14 +42,17 @@ def same(a, b):
     return (np.isnan(a) and np.isnan(b)) or a.view(np.uint32) == b.view(np.uint32)
 
 
-@pytest.mark.parametrize("hoist", [False, True])
+MODES = [dict(), dict(hoist=True), dict(hoist=True, max_hoisted=1), dict(flat=True)]
+
+
+@pytest.mark.parametrize("mode", MODES, ids=["split", "hoisted", "hoisted-one-row-value", "flat"])
 @pytest.mark.parametrize("seed,max_tokens,bits", [(3, 15, 0), (4, 32, 3), (5, 48, 8)])
-def test_records_evaluate_like_the_oracle(seed, max_tokens, bits, hoist):
+def test_records_evaluate_like_the_oracle(seed, max_tokens, bits, mode):
     pop = P.random_population(seed, 150, max_tokens, 6, 8, 2.0, toggle_bits=bits)
     n = 29
     x = np.stack([P.uniform(seed, c, n, -2, 2) for c in range(6)])
     banks = np.stack([P.normal(seed + 1, b, 8) for b in range(3)])
-    code, handle = encode(pop, 6, 8, True, bits, hoist=hoist)  # with and without the bank-independent prelude
+    code, handle = encode(pop, 6, 8, True, bits, **mode)
     assert code == 0
     configs = 3 << bits
     for cfg in sorted({0, 1, configs // 2, configs - 1}):
@@ -85,12 +99,12 @@ def test_fma_routines_and_shared_arguments():
     pop = P.PackedPrograms(progs, [sq, mix])
     x = np.stack([P.uniform(1, c, 7, 0.1, 2) for c in range(3)])
     banks = np.stack([P.normal(2, b, 2) for b in range(2)])
-    for hoist in (False, True):
-        check_hand_written(pop, progs, x, banks, hoist)
+    for mode in MODES:
+        check_hand_written(pop, progs, x, banks, mode)
 
 
-def check_hand_written(pop, progs, x, banks, hoist):
-    code, handle = encode(pop, 3, 2, True, 2, hoist=hoist)
+def check_hand_written(pop, progs, x, banks, mode):
+    code, handle = encode(pop, 3, 2, True, 2, **mode)
     assert code == 0
     for cfg in range(8):
         _, want = S.oracle_toggle_materialize(pop, x, banks, 2, 2, cfg)
@@ -137,6 +151,4 @@ def test_work_accounting_counts_inlined_routines():
     pop = P.PackedPrograms([P.col(0) + P.col(1) + P.routine(0) + P.routine(1) + P.RET], P.PROTECTED_ROUTINES)
     code, handle = encode(pop, 2, 0, True, 0)
     assert code == 0
-    info = [C.c_uint32() for _ in range(6)]
-    S.hooks().sbt_info(handle, C.c_size_t(0), *[C.byref(i) for i in info])
-    assert info[2].value == 7 == int(P.count_ops(pop)[0])  # pdiv = 4 operations, plog = 3
+    assert info(handle, 0)[2] == 7 == int(P.count_ops(pop)[0])  # pdiv = 4 operations, plog = 3
