@@ -450,10 +450,10 @@ __device__ __forceinline__ void stage_tile(float* tile, uint32_t tile_ld, const 
     cp_async_commit();
 }
 
-/* 16-value tiles run 20 warps per CTA within 96 registers; 32-value tiles need more
- * registers per thread and run 12 warps. */
+/* 16 values per thread: 20 warps per CTA within 96 registers (32-value tiles were measured
+ * slower at the 12 warps their 168 registers allow). */
 template <int RR, int RC, bool FAST>
-__global__ void __launch_bounds__(RR * RC > 16 ? 384 : 640, 1)
+__global__ void __launch_bounds__(640, 1)
 eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, float* __restrict__ partial) {
     using M = Machine<RR, RC, FAST>;
     extern __shared__ __align__(16) unsigned char smem[];
@@ -899,9 +899,8 @@ __global__ void rk4_validate_kernel(const Rk4Problem prob) {
 template <int RR, int RC>
 cudaError_t launch_variant(const DeviceBatch& batch, const EvalProblem& prob, const Geom& geom, const LaunchPlan& plan,
                            float* partial, cudaStream_t stream) {
-    /* approximate math exists for the 16-value tiles, which are the ones the planner picks */
-    if (RR * RC <= 16 && prob.fast_math)
-        eval_kernel<RR, RC, (RR * RC <= 16)><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom, partial);
+    if (prob.fast_math)
+        eval_kernel<RR, RC, true><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom, partial);
     else
         eval_kernel<RR, RC, false><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom, partial);
     return cudaGetLastError();
@@ -911,7 +910,7 @@ uint32_t round16(size_t v) { return (uint32_t)((v + 15) / 16 * 16); }
 
 }  // namespace
 
-#define SB_FOR_VARIANTS(X) X(4, 4) X(8, 2) X(16, 1) X(8, 4) X(16, 2) X(32, 1)
+#define SB_FOR_VARIANTS(X) X(4, 4) X(8, 2) X(16, 1)
 
 cudaError_t configure_kernels() {
     cudaError_t e;
@@ -920,7 +919,7 @@ cudaError_t configure_kernels() {
     if ((e = cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return e;
 #define SB_CONFIGURE(RR, RC) \
     if ((e = cudaFuncSetAttribute(eval_kernel<RR, RC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e; \
-    if (RR * RC <= 16 && (e = cudaFuncSetAttribute(eval_kernel<RR, RC, (RR * RC <= 16)>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(eval_kernel<RR, RC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
     SB_FOR_VARIANTS(SB_CONFIGURE)
 #undef SB_CONFIGURE
     return cudaSuccess;
@@ -961,10 +960,7 @@ cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem& prob, const
     switch (plan.variant) {
     case 0: e = launch_variant<4, 4>(batch, prob, geom, plan, partial, stream); break;
     case 1: e = launch_variant<8, 2>(batch, prob, geom, plan, partial, stream); break;
-    case 2: e = launch_variant<16, 1>(batch, prob, geom, plan, partial, stream); break;
-    case 3: e = launch_variant<8, 4>(batch, prob, geom, plan, partial, stream); break;
-    case 4: e = launch_variant<16, 2>(batch, prob, geom, plan, partial, stream); break;
-    default: e = launch_variant<32, 1>(batch, prob, geom, plan, partial, stream); break;
+    default: e = launch_variant<16, 1>(batch, prob, geom, plan, partial, stream); break;
     }
     if (e != cudaSuccess) return e;
     *launches = 1;

@@ -66,7 +66,7 @@ struct EvalProblem {
 
 /* Launch geometry chosen by plan_launch(). */
 struct LaunchPlan {
-    int variant;              /* rows x banks per thread: 0: 4x4, 1: 8x2, 2: 16x1, 3: 8x4, 4: 16x2, 5: 32x1 */
+    int variant;              /* rows x banks per thread: 0: 4x4, 1: 8x2, 2: 16x1 */
     uint32_t warps;           /* per CTA */
     uint32_t tile_rows;       /* rows staged per tile, multiple of the pass size */
     uint32_t tile_buffers;    /* 2 when a CTA walks more than one tile: the next tile is fetched while this one is used */
@@ -99,14 +99,15 @@ struct Geom {
     unsigned long long rows_per_split;
 };
 
-constexpr int kNumVariants = 6;
-constexpr int kVariantRows[kNumVariants] = {4, 8, 16, 8, 16, 32};
-constexpr int kVariantBanks[kNumVariants] = {4, 2, 1, 4, 2, 1};
+constexpr int kNumVariants = 3;
+constexpr int kVariantRows[kNumVariants] = {4, 8, 16};
+constexpr int kVariantBanks[kNumVariants] = {4, 2, 1};
 
 Geom make_geom(const DeviceBatch& batch, const EvalProblem& problem, const LaunchPlan& plan);
 
+/* scratch_limit: most floats of per-split partial sums a launch may use (row splits are reduced to fit). */
 LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& problem, int sm_count, size_t smem_limit,
-                       int forced_variant /* -1 = automatic */);
+                       size_t scratch_limit);
 
 /* Enqueues the evaluation of one batch on `stream`: the evaluator kernel writes per-split partial
  * sums into `partial` (plan.partial_elements floats, private to the stream until the launch has

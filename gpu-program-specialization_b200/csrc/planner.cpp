@@ -47,16 +47,14 @@ Geom make_geom(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPl
     return g;
 }
 
-LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm_count, size_t smem_limit, int forced_variant) {
+namespace {
+
+LaunchPlan plan_with_tile(const DeviceBatch& batch, const EvalProblem& prob, int sm_count, size_t smem_limit, size_t scratch_limit,
+                          int variant) {
     LaunchPlan plan{};
     plan.ok = false;
     plan.overflow = false;
     plan.groups_per_item = 1;
-    int variant = prob.num_banks >= 4 ? 0 : prob.num_banks >= 2 ? 1 : 2;
-    uint32_t forced_warps = 0;
-    if (forced_variant >= 0) { forced_warps = (uint32_t)forced_variant >> 8; forced_variant &= 0xff; }
-    if (forced_variant >= 0 && forced_variant < kNumVariants) variant = forced_variant;
-    if (prob.mode == EVAL_MATERIALIZE) variant = 2;
     plan.variant = variant;
     const uint32_t rr = (uint32_t)kVariantRows[variant], rc = (uint32_t)kVariantBanks[variant];
     const uint32_t pass = 32u * rr;
@@ -85,15 +83,10 @@ LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm
     const unsigned long long kMaxItems = 0xffffff00ull;
     if (items_per_program > kMaxItems) { plan.overflow = true; return plan; }
 
-    /* Warps per CTA and rows per tile.  20 warps run at a 96-register budget, the 32-value tiles
-     * stop at 12; a tile of at least 512 rows keeps the per-item set-up (program copy, toggle
-     * patches, bank part) small against the row passes, so fewer warps are preferred over a
-     * smaller tile down to 256 rows. */
-    static const uint32_t kSmallTile[] = {20, 16, 12, 8, 4, 2, 1, 0}, kLargeTile[] = {12, 8, 4, 2, 1, 0};
-    const uint32_t warp_cap = rr * rc > 16 ? 12u : 20u;
-    if (forced_warps > warp_cap) forced_warps = warp_cap;
-    const uint32_t forced_list[] = {forced_warps, 0};
-    const uint32_t* const warp_list = forced_warps ? forced_list : (rr * rc > 16 ? kLargeTile : kSmallTile);
+    /* Warps per CTA and rows per tile.  20 warps run at a 96-register budget; a tile of at least
+     * 512 rows keeps the per-item set-up (program copy, toggle patches, bank part) small against
+     * the row passes, so fewer warps are preferred over a smaller tile down to 256 rows. */
+    static const uint32_t warp_list[] = {20, 16, 12, 8, 4, 2, 1, 0};
     const size_t rows_padded = (prob.num_rows + pass - 1) / pass * pass;
     const uint32_t floors[3] = {512u, 256u, pass};
     for (int attempt = 0; attempt < 3 && !plan.ok; ++attempt) {
@@ -147,6 +140,13 @@ LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm
         groups = std::min<unsigned long long>(P, ((unsigned long long)sm_count + splits - 1) / splits);
         plan.num_groups = (uint32_t)groups;
     }
+    const unsigned long long configs = (unsigned long long)prob.num_banks << prob.toggle_bits;
+    if (!materialize && configs) { /* [split][program][quantity][configuration] floats of scratch */
+        const unsigned long long per_split = (unsigned long long)P * nq;
+        if (per_split > (~0ull >> 3) / configs) { plan.overflow = true; return plan; }
+        const unsigned long long fit = std::max<unsigned long long>(1, (unsigned long long)scratch_limit / (per_split * configs));
+        splits = (size_t)std::min<unsigned long long>(splits, fit);
+    }
     const size_t tiles_per_split = (tiles + splits - 1) / splits;
     plan.rows_per_split = tiles_per_split * plan.tile_rows;
     plan.row_splits = (uint32_t)((prob.num_rows + plan.rows_per_split - 1) / plan.rows_per_split);
@@ -157,13 +157,28 @@ LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm
 
     plan.partial_elements = 0;
     if (!materialize) {
-        /* [split][program][quantity][configuration] */
-        const unsigned long long configs = (unsigned long long)prob.num_banks << prob.toggle_bits;
-        unsigned long long n = (unsigned long long)plan.row_splits * P;
+        const unsigned long long n = (unsigned long long)plan.row_splits * P;
         if (configs && n > (~0ull >> 3) / configs / nq) { plan.overflow = true; return plan; }
         plan.partial_elements = (size_t)(n * nq * configs);
     }
     plan.ok = true;
+    return plan;
+}
+
+}  // namespace
+
+LaunchPlan plan_launch(const DeviceBatch& batch, const EvalProblem& prob, int sm_count, size_t smem_limit, size_t scratch_limit) {
+    /* register tile: 4 rows x 4 banks per thread, or 8 x 2 / 16 x 1 when there are fewer banks.  A
+     * tile with more rows per thread stages more rows per pass; when even one pass of a wide dataset
+     * does not fit shared memory, the tiles with fewer rows are tried (their spare bank columns
+     * compute padding that is never written). */
+    int variant = prob.num_banks >= 4 ? 0 : prob.num_banks >= 2 ? 1 : 2;
+    if (prob.mode == EVAL_MATERIALIZE) variant = 2;
+    LaunchPlan plan{};
+    for (; variant >= 0; --variant) {
+        plan = plan_with_tile(batch, prob, sm_count, smem_limit, scratch_limit, variant);
+        if (plan.ok || plan.overflow) break;
+    }
     return plan;
 }
 

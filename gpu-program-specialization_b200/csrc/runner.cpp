@@ -24,6 +24,15 @@
 #include <thread>
 #include <vector>
 
+/* Fault hooks: in the host-only test build (Makefile target `fakecuda`) the named sites ask the test
+ * harness whether to fail; in the product they compile to nothing. */
+#ifdef SECANT_B200_FAULT_HOOKS
+extern "C" int secant_b200_fault_hook(const char* site);
+#define SB_FAULT(site) (secant_b200_fault_hook(site) != 0)
+#else
+#define SB_FAULT(site) false
+#endif
+
 namespace sb {
 
 std::atomic<uint64_t> g_kernel_launches{0};
@@ -79,6 +88,8 @@ struct Slot {
 
 using namespace sb;
 
+constexpr size_t kDefaultScratchFloats = (size_t)1 << 28; /* 1 GiB of per-split partial sums per launch */
+
 struct SecantCubinRunnerImpl {
     SecantCubinPlan owned_plan;     /* used when created straight from a recipe */
     const SecantCubinPlan* plan = nullptr;
@@ -104,7 +115,8 @@ struct SecantCubinRunnerImpl {
     bool job_abort = false;
     /* handle state */
     bool active = false, failed = false, shutdown = false;
-    int forced_variant = -1;       /* test hook: pin the register-tile variant */
+    size_t populations = 0;        /* device-resident populations created from this runner and not yet destroyed */
+    size_t scratch_limit = kDefaultScratchFloats; /* secant_b200_runner_set_scratch_limit */
     uint32_t fast_math = 0;        /* secant_b200_runner_set_math */
     std::string last_error;
 };
@@ -150,12 +162,17 @@ void worker_main(SecantCubinRunnerImpl* r, size_t worker_index) {
 
         const double begin = now_seconds();
         SecantResult status = SECANT_SUCCESS;
-        slot->enc.clear();
-        slot->enc.programs.reserve(count);
-        for (size_t i = 0; i < count && status == SECANT_SUCCESS; ++i) {
-            status = encode_program(programs->asts.items[first + i], programs->routines, arity, rules, slot->enc);
-            if (status == SECANT_SUCCESS) slot->enc.programs.back().index = (uint32_t)(first + i);
+        try { /* an allocation failure inside the encoder must reach the caller as a result code */
+            slot->enc.clear();
+            slot->enc.programs.reserve(count);
+            for (size_t i = 0; i < count && status == SECANT_SUCCESS; ++i) {
+                status = encode_program(programs->asts.items[first + i], programs->routines, arity, rules, slot->enc);
+                if (status == SECANT_SUCCESS) slot->enc.programs.back().index = (uint32_t)(first + i);
+            }
+        } catch (...) {
+            status = SECANT_ERROR_ALLOCATION_FAILED;
         }
+        if (SB_FAULT("encode")) status = SECANT_ERROR_BAD_PROGRAM;
         const double spent = now_seconds() - begin;
 
         lock.lock();
@@ -205,7 +222,10 @@ SecantResult runner_init(SecantCubinRunnerImpl* r, const SecantCubinRunnerOption
     }
     r->worker_seconds.assign(options->num_workers, 0.0);
     try {
-        for (size_t i = 0; i < options->num_workers; ++i) r->workers.emplace_back(worker_main, r, i);
+        for (size_t i = 0; i < options->num_workers; ++i) {
+            if (SB_FAULT("thread")) throw std::bad_alloc();
+            r->workers.emplace_back(worker_main, r, i);
+        }
     } catch (...) {
         r->last_error = "worker thread creation failed";
         return SECANT_ERROR_THREAD_FAILED;
@@ -213,6 +233,9 @@ SecantResult runner_init(SecantCubinRunnerImpl* r, const SecantCubinRunnerOption
     return SECANT_SUCCESS;
 }
 
+/* Stops the workers, waits for the streams and releases everything the runner owns.  May be
+ * called again after a failure: a resource is forgotten only once its release has succeeded, so a
+ * second destroy retries what the first could not free. */
 SecantResult runner_teardown(SecantCubinRunnerImpl* r) {
     {
         std::lock_guard<std::mutex> lock(r->mutex);
@@ -223,23 +246,27 @@ SecantResult runner_teardown(SecantCubinRunnerImpl* r) {
         if (t.joinable()) t.join();
     r->workers.clear();
     SecantResult result = SECANT_SUCCESS;
-    auto check = [&](cudaError_t e) { if (e != cudaSuccess && e != cudaErrorCudartUnloading) result = SECANT_ERROR_DRIVER_FAILED; };
-    for (auto& s : r->streams) if (s) { check(cudaStreamSynchronize(s)); }
-    if (r->copy_stream) check(cudaStreamSynchronize(r->copy_stream));
-    if (result != SECANT_SUCCESS) return SECANT_ERROR_COMPLETION_UNKNOWN;
+    auto ok = [&](cudaError_t e) {
+        if (e == cudaSuccess || e == cudaErrorCudartUnloading) return true;
+        result = SECANT_ERROR_DRIVER_FAILED;
+        return false;
+    };
+    for (auto& s : r->streams) if (s) ok(cudaStreamSynchronize(s));
+    if (r->copy_stream) ok(cudaStreamSynchronize(r->copy_stream));
+    if (result != SECANT_SUCCESS) return SECANT_ERROR_COMPLETION_UNKNOWN; /* nothing is released under work that may still run */
     for (auto& s : r->slots) {
-        if (s.pinned) check(cudaFreeHost(s.pinned));
-        if (s.device) check(cudaFree(s.device));
-        if (s.uploaded) check(cudaEventDestroy(s.uploaded));
-        for (auto& e : s.done) if (e) check(cudaEventDestroy(e));
-        s.pinned = s.device = nullptr; s.uploaded = nullptr; s.done.clear();
+        if (s.pinned && ok(cudaFreeHost(s.pinned))) { s.pinned = nullptr; s.pinned_cap = 0; }
+        if (s.device && ok(cudaFree(s.device))) { s.device = nullptr; s.device_cap = 0; }
+        if (s.uploaded && ok(cudaEventDestroy(s.uploaded))) s.uploaded = nullptr;
+        for (auto& e : s.done) if (e && ok(cudaEventDestroy(e))) e = nullptr;
     }
-    for (auto& p : r->scratch) if (p) { check(cudaFree(p)); p = nullptr; }
-    for (auto& s : r->streams) if (s) { check(cudaStreamDestroy(s)); s = nullptr; }
-    if (r->copy_stream) { check(cudaStreamDestroy(r->copy_stream)); r->copy_stream = nullptr; }
-    if (r->ev_cleared) { check(cudaEventDestroy(r->ev_cleared)); r->ev_cleared = nullptr; }
-    if (r->ev_start) { check(cudaEventDestroy(r->ev_start)); r->ev_start = nullptr; }
-    if (r->ev_stop) { check(cudaEventDestroy(r->ev_stop)); r->ev_stop = nullptr; }
+    for (size_t k = 0; k < r->scratch.size(); ++k)
+        if (r->scratch[k] && ok(cudaFree(r->scratch[k]))) { r->scratch[k] = nullptr; r->scratch_cap[k] = 0; }
+    for (auto& s : r->streams) if (s && ok(cudaStreamDestroy(s))) s = nullptr;
+    if (r->copy_stream && ok(cudaStreamDestroy(r->copy_stream))) r->copy_stream = nullptr;
+    if (r->ev_cleared && ok(cudaEventDestroy(r->ev_cleared))) r->ev_cleared = nullptr;
+    if (r->ev_start && ok(cudaEventDestroy(r->ev_start))) r->ev_start = nullptr;
+    if (r->ev_stop && ok(cudaEventDestroy(r->ev_stop))) r->ev_stop = nullptr;
     return result;
 }
 
@@ -421,7 +448,7 @@ SecantResult launch_batch(SecantCubinRunnerImpl* r, const DeviceBatch& db, const
         prob.fast_math = r->fast_math;
         if (runs[e].program_bank_stride)
             prob.banks = reinterpret_cast<const float*>(runs[e].banks.address) + runs[e].first_program_index * runs[e].program_bank_stride;
-        const LaunchPlan lp = plan_launch(db, prob, r->sm_count, r->smem_limit, r->forced_variant);
+        const LaunchPlan lp = plan_launch(db, prob, r->sm_count, r->smem_limit, r->scratch_limit);
         if (!lp.ok) {
             r->last_error = lp.overflow ? "configuration count beyond the evaluator's 32-bit item index" : "program batch does not fit shared memory";
             return lp.overflow ? SECANT_ERROR_OVERFLOW : SECANT_ERROR_REGISTER_OVERFLOW;
@@ -440,6 +467,15 @@ SecantResult launch_batch(SecantCubinRunnerImpl* r, const DeviceBatch& db, const
         if (used) (*used)[k] = 1;
     }
     return SECANT_SUCCESS;
+}
+
+/* Waits for everything the runner has enqueued; false (and a destroy-only handle) when a wait fails. */
+bool drain_streams(SecantCubinRunnerImpl* r) {
+    bool ok = true;
+    for (auto& s : r->streams) ok = (cudaStreamSynchronize(s) == cudaSuccess) && ok;
+    ok = (cudaStreamSynchronize(r->copy_stream) == cudaSuccess) && ok;
+    if (!ok) r->failed = true;
+    return ok;
 }
 
 /* Waits until every compute stream that touched the slot has finished with it. */
@@ -495,6 +531,22 @@ SecantResult execute(SecantCubinRunnerImpl* r, const std::vector<UnpackedRun>& r
         r->job_active = true;
     }
     r->cv_work.notify_all();
+    /* Whatever way this function is left (a result code or an exception from a container), the
+     * workers must be off this job first: they read `arity`, `programs` and `rules`, which live in
+     * the caller's frames. */
+    struct JobGuard {
+        SecantCubinRunnerImpl* r;
+        ~JobGuard() {
+            std::unique_lock<std::mutex> lock(r->mutex);
+            r->job_abort = true;
+            r->cv_ready.wait(lock, [&] {
+                for (auto& s : r->slots)
+                    if (s.state == SLOT_ENCODING) return false;
+                return true;
+            });
+            r->job_active = false;
+        }
+    } job_guard{r};
 
     bool unknown = false;
     size_t launched_batches = 0, stream_cursor = 0;
@@ -613,7 +665,7 @@ SecantResult secant_cubin_runner_create(const SecantCubinPlan* plan, const void*
         return SECANT_ERROR_INVALID_VALUE;
     const SecantResult o = options_validate(options);
     if (o != SECANT_SUCCESS) return o;
-    SecantCubinRunnerImpl* r = new (std::nothrow) SecantCubinRunnerImpl();
+    SecantCubinRunnerImpl* r = SB_FAULT("alloc") ? nullptr : new (std::nothrow) SecantCubinRunnerImpl();
     if (!r) return SECANT_ERROR_ALLOCATION_FAILED;
     r->plan = plan;
     return create_common(r, options, runner_ret);
@@ -627,7 +679,7 @@ SecantResult secant_b200_runner_create(const SecantCubinRecipeHeader* recipe, co
     if (v != SECANT_SUCCESS) return v;
     const SecantResult o = options_validate(options);
     if (o != SECANT_SUCCESS) return o;
-    SecantCubinRunnerImpl* r = new (std::nothrow) SecantCubinRunnerImpl();
+    SecantCubinRunnerImpl* r = SB_FAULT("alloc") ? nullptr : new (std::nothrow) SecantCubinRunnerImpl();
     if (!r) return SECANT_ERROR_ALLOCATION_FAILED;
     plan_fill(&r->owned_plan, recipe, 0);
     r->plan = &r->owned_plan;
@@ -656,6 +708,7 @@ SecantResult secant_cubin_runner_run_batch(SecantCubinRunner r, const SecantCubi
     SecantResult result = SECANT_SUCCESS;
     std::vector<UnpackedRun> runs;
     try {
+        if (SB_FAULT("alloc")) throw std::bad_alloc();
         runs.resize(count);
     } catch (...) {
         result = SECANT_ERROR_ALLOCATION_FAILED;
@@ -667,7 +720,8 @@ SecantResult secant_cubin_runner_run_batch(SecantCubinRunner r, const SecantCubi
         try {
             result = execute(r, runs, rules, &measured);
         } catch (const std::bad_alloc&) {
-            result = SECANT_ERROR_ALLOCATION_FAILED;
+            /* work already enqueued still reads the caller's buffers: wait for it before handing them back */
+            result = drain_streams(r) ? SECANT_ERROR_ALLOCATION_FAILED : SECANT_ERROR_COMPLETION_UNKNOWN;
         }
     }
     {
@@ -690,7 +744,7 @@ SecantResult secant_cubin_runner_destroy(SecantCubinRunner r) {
     if (r->context && (!ok || ctx != r->context)) return SECANT_ERROR_INVALID_STATE;
     {
         std::lock_guard<std::mutex> lock(r->mutex);
-        if (r->active) return SECANT_ERROR_INVALID_STATE;
+        if (r->active || r->populations) return SECANT_ERROR_INVALID_STATE; /* populations hold a pointer to their runner */
     }
     const SecantResult result = runner_teardown(r);
     if (result != SECANT_SUCCESS) { r->failed = true; return result; }
@@ -865,6 +919,10 @@ SecantResult secant_b200_population_create(SecantCubinRunner r, const SecantAstP
         delete pop;
         return result;
     }
+    {
+        std::lock_guard<std::mutex> lock(r->mutex);
+        ++r->populations;
+    }
     *population_ret = pop;
     return SECANT_SUCCESS;
 }
@@ -890,7 +948,14 @@ SecantResult secant_b200_population_run_batch(SecantB200Population pop, const Se
         r->active = true;
     }
     SecantResult result = SECANT_SUCCESS;
-    std::vector<UnpackedRun> runs(count);
+    std::vector<UnpackedRun> runs;
+    try {
+        runs.resize(count);
+    } catch (...) {
+        std::lock_guard<std::mutex> lock(r->mutex);
+        r->active = false;
+        return SECANT_ERROR_ALLOCATION_FAILED;
+    }
     bool same_bits = true;
     for (size_t i = 0; result == SECANT_SUCCESS && i < count; ++i) {
         /* the request's program views are replaced by the population's own */
@@ -910,7 +975,13 @@ SecantResult secant_b200_population_run_batch(SecantB200Population pop, const Se
         /* records were encoded for pop->toggle_bits; fewer bits would leave stale patch sites unchecked */
         result = SECANT_ERROR_BAD_PROGRAM;
     }
-    if (result == SECANT_SUCCESS) result = execute_resident(r, pop, runs, &measured);
+    if (result == SECANT_SUCCESS) {
+        try {
+            result = execute_resident(r, pop, runs, &measured);
+        } catch (const std::bad_alloc&) {
+            result = drain_streams(r) ? SECANT_ERROR_ALLOCATION_FAILED : SECANT_ERROR_COMPLETION_UNKNOWN;
+        }
+    }
     {
         std::lock_guard<std::mutex> lock(r->mutex);
         r->active = false;
@@ -931,6 +1002,10 @@ SecantResult secant_b200_population_destroy(SecantB200Population pop) {
     SecantResult result = SECANT_SUCCESS;
     for (auto& b : pop->batches)
         if (b.device && cudaFree(b.device) != cudaSuccess) result = SECANT_ERROR_DRIVER_FAILED;
+    {
+        std::lock_guard<std::mutex> lock(pop->runner->mutex);
+        if (pop->runner->populations) --pop->runner->populations;
+    }
     delete pop;
     return result;
 }
@@ -943,9 +1018,12 @@ SecantResult secant_b200_runner_set_math(SecantCubinRunner r, uint32_t mode) {
     return SECANT_SUCCESS;
 }
 
-/* Test hook: pins the register-tile variant (0: 4x4, 1: 8x2, 2: 16x1, -1: automatic). */
-void secant_b200_runner_force_variant(SecantCubinRunner r, int variant) {
-    if (r) r->forced_variant = variant;
+SecantResult secant_b200_runner_set_scratch_limit(SecantCubinRunner r, size_t bytes) {
+    if (!r) return SECANT_ERROR_INVALID_VALUE;
+    std::lock_guard<std::mutex> lock(r->mutex);
+    if (r->active) return SECANT_ERROR_INVALID_STATE;
+    r->scratch_limit = bytes ? std::max<size_t>(1, bytes / sizeof(float)) : kDefaultScratchFloats;
+    return SECANT_SUCCESS;
 }
 
 }  // extern "C"

@@ -232,7 +232,7 @@ SBT_EXPORT int sbt_validate_runs(const SecantCubinRecipeHeader* recipe, const Se
 #include "evaluator.cuh"
 SBT_EXPORT int sbt_plan(uint32_t num_programs, uint32_t max_insn, uint32_t max_slots, uint32_t max_hoisted, uint32_t max_cst,
                         uint32_t max_btmp, int mode, uint32_t num_inputs, uint32_t num_targets, uint32_t num_banks,
-                        uint32_t toggle_bits, uint64_t rows, int sm_count, uint64_t smem_limit, uint64_t* out) {
+                        uint32_t toggle_bits, uint64_t rows, int sm_count, uint64_t smem_limit, uint64_t scratch_floats, uint64_t* out) {
     DeviceBatch db;
     std::memset(&db, 0, sizeof(db));
     db.num_programs = num_programs; db.max_insn = max_insn; db.max_slots = max_slots; db.max_hoisted = max_hoisted;
@@ -241,7 +241,7 @@ SBT_EXPORT int sbt_plan(uint32_t num_programs, uint32_t max_insn, uint32_t max_s
     std::memset(&p, 0, sizeof(p));
     p.mode = mode; p.num_inputs = num_inputs; p.num_targets = num_targets; p.num_banks = num_banks; p.toggle_bits = toggle_bits;
     p.num_rows = rows;
-    const LaunchPlan plan = plan_launch(db, p, sm_count, smem_limit, -1);
+    const LaunchPlan plan = plan_launch(db, p, sm_count, smem_limit, scratch_floats);
     if (!plan.ok) return plan.overflow ? -1 : 0;
     const Geom g = make_geom(db, p, plan);
     const uint64_t rc = (uint64_t)kVariantBanks[plan.variant];

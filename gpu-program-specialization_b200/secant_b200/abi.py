@@ -207,7 +207,7 @@ EXPORTED = {
     "secant_b200_population_run_batch": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), _sz, C.c_void_p]),
     "secant_b200_population_num_ops": (C.c_uint64, [C.c_void_p]),
     "secant_b200_population_destroy": (C.c_int32, [C.c_void_p]),
-    "secant_b200_runner_force_variant": (None, [C.c_void_p, C.c_int]),
+    "secant_b200_runner_set_scratch_limit": (C.c_int32, [C.c_void_p, C.c_size_t]),
     "secant_b200_runner_set_math": (C.c_int32, [C.c_void_p, C.c_uint32]),
     "secant_b200_grouped_topk": (C.c_int32, [C.c_size_t, _sz, _sz, C.c_uint32, C.c_uint32, C.c_uint32, C.c_size_t, C.c_size_t,
                                  C.c_void_p]),

@@ -164,8 +164,9 @@ class Runner:
         """fast=True selects the approximate division / transcendental functions of the reference's GPU kernels."""
         abi.check(self.lib.secant_b200_runner_set_math(self.handle, 1 if fast else 0), "secant_b200_runner_set_math")
 
-    def force_variant(self, variant):
-        self.lib.secant_b200_runner_force_variant(self.handle, variant)
+    def set_scratch_limit(self, nbytes):
+        """Caps the device scratch one launch may use for per-split partial sums (0 = default)."""
+        abi.check(self.lib.secant_b200_runner_set_scratch_limit(self.handle, C.c_size_t(nbytes)), "set_scratch_limit")
 
     def population(self, packed, toggle_bits=0):
         return Population(self, packed, toggle_bits)

@@ -87,9 +87,18 @@ SECANT_DEC SecantResult secant_b200_population_destroy(SecantB200Population popu
 enum { SECANT_B200_MATH_ACCURATE = 0, SECANT_B200_MATH_FAST = 1 };
 SECANT_DEC SecantResult secant_b200_runner_set_math(SecantCubinRunner runner, uint32_t mode);
 
-/* Pins the per-thread register tile used by the evaluator: 0 = 4 rows x 4 banks,
- * 1 = 8 x 2, 2 = 16 x 1, -1 = automatic.  Every variant computes the same values. */
-SECANT_DEC void secant_b200_runner_force_variant(SecantCubinRunner runner, int variant);
+/*
+ * Scratch memory of a run.  The evaluator splits the rows of a run across thread blocks, keeps one
+ * partial sum per (row split, program, target, configuration) in device memory of its own and adds
+ * the splits of a bin in a fixed order, so a score never depends on how the blocks were scheduled
+ * (the reference adds with atomics, projects/secant/s_cubin_generate_toggle_sse.c:378-381).  The
+ * buffer belongs to the runner (one per launch stream, grown on demand, kept between runs,
+ * released by destroy).  More row splits mean more, shorter blocks - better balance when there are
+ * few programs - and more scratch.  This call caps the scratch of one launch at `bytes`; 0 restores
+ * the default of 1 GiB.  A launch whose single-split scratch alone exceeds the cap still runs, with
+ * one split.  Returns INVALID_STATE while a run is in flight.
+ */
+SECANT_DEC SecantResult secant_b200_runner_set_scratch_limit(SecantCubinRunner runner, size_t bytes);
 
 /*
  * RK4 rollout scoring: the population-evaluation path with the program inside an integration

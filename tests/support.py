@@ -299,3 +299,63 @@ def sampled_constants(descriptors, uniform_pool, normal_pool, num_banks):
                 v = np.float32(np.float32(pool[offset + delta]) * np.float32(scale)) + np.float32(shift)
                 out[i, b, k] = min(np.float32(upper), max(np.float32(lower), np.float32(v)))
     return out
+
+
+def sse_reference_parallel(packed, x, y, banks, num_constants, toggle_bits, program_bank_stride=0, threads=None, ulps=2):
+    """(want64, slack) of a toggle-SSE run like oracle_toggle_sse() and sse_slack(), with the programs
+    spread over host threads (the checker is a single-threaded C loop that releases the GIL).
+    The shift of the math results is one global of the checker library, so the three passes
+    (plain, +ulps, -ulps) run one after the other, each on all threads."""
+    from concurrent.futures import ThreadPoolExecutor
+    lib = oracle()
+    A = len(packed.asts)
+    T, N = y.shape
+    threads = threads or min(A, os.cpu_count() or 1)
+    bounds = np.linspace(0, A, threads + 1).astype(int)
+    spans = [(int(a), int(b)) for a, b in zip(bounds[:-1], bounds[1:]) if b > a]
+    subs = [packed.subset(range(a, b)) for a, b in spans]
+    tables = [banks[a:b] if program_bank_stride else banks for a, b in spans]
+    if program_bank_stride:
+        nb = banks.shape[1]
+    else:
+        nb = banks.shape[0] if (banks is not None and num_constants) else 1
+    configs = nb << toggle_bits
+    xx = x if (x is not None and x.size) else np.zeros((1, N), dtype=np.float32)
+
+    def rows_of(i):
+        out = np.empty((spans[i][1] - spans[i][0], configs, N), dtype=np.float32)
+        for cfg in range(configs):
+            code, vals = oracle_toggle_materialize(subs[i], xx, tables[i], num_constants, toggle_bits, cfg, program_bank_stride)
+            assert code == 0, code
+            out[:, cfg, :] = vals
+        return out
+
+    def run_pass(shift):
+        lib.so_set_ulp_shift(shift)
+        try:
+            with ThreadPoolExecutor(max_workers=len(spans)) as pool:
+                return list(pool.map(rows_of, range(len(spans))))
+        finally:
+            lib.so_set_ulp_shift(0)
+
+    base = np.concatenate(run_pass(0))                      # [program][configuration][row]
+    sens = np.zeros(base.shape, dtype=np.float64)
+    for shift in (ulps, -ulps):
+        moved = np.concatenate(run_pass(shift))
+        with np.errstate(invalid="ignore", over="ignore"):
+            d = np.abs(moved.astype(np.float64) - base.astype(np.float64))
+        unstable = np.isfinite(moved) != np.isfinite(base)
+        d[unstable] = np.inf
+        d[~np.isfinite(base) & ~unstable] = 0.0
+        np.maximum(sens, d, out=sens)
+    want64 = np.zeros((A, T, configs), dtype=np.float64)
+    slack = np.zeros((A, T, configs), dtype=np.float64)
+    for t in range(T):
+        with np.errstate(invalid="ignore", over="ignore"):
+            err = (base - y[t][None, None, :]).astype(np.float64)   # the residual is a float32 subtraction, as in the evaluators
+            want64[:, t, :] = (err * err).sum(axis=2)
+            term = 2.0 * np.abs(err) * sens + sens * sens
+        term[np.isnan(term)] = np.inf
+        term[sens == 0] = 0.0
+        slack[:, t, :] = term.sum(axis=2)
+    return want64, slack

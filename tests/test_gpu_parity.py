@@ -75,24 +75,23 @@ def test_golden_random_population_against_reference_vectors(cuda):
 
 
 @pytest.mark.parametrize("rows", [1, 127, 128, 129, 255, 256, 257, 4097])
-@pytest.mark.parametrize("variant", [0, 1, 2])
-def test_tile_boundaries_all_register_tiles(cuda, rows, variant):
-    bits, nb = 2, 5
+@pytest.mark.parametrize("nb", [5, 2, 1], ids=["tile4x4", "tile8x2", "tile16x1"])
+def test_tile_boundaries_all_register_tiles(cuda, rows, nb):
+    """Row counts around the pass sizes of every register tile (the bank count selects the tile:
+    4 rows x 4 banks from four banks on, 8 x 2 for two or three, 16 x 1 for one), and 4,097 rows:
+    eight full tiles of 512 plus one row."""
+    bits = 2
     pop = P.random_population(31, 40, 32, 5, 6, 2.0, toggle_bits=bits)
     x = np.stack([P.uniform(32, c, rows, -2, 2) for c in range(5)])
     y = np.stack([P.normal(33, t, rows) for t in range(1)])
     banks = np.stack([P.normal(34, b, 6) for b in range(nb)])
     with Runner(abi.SHAPE_TOGGLE_SSE, 5, 1, 6) as rn:
-        rn.force_variant(variant)
         got = rn.toggle_sse(pop, dev(x), dev(y), dev(banks), nb, bits).cpu().numpy()
-    _, _, want64 = S.oracle_toggle_sse(pop, x, y, banks, 6, bits)
-    slack = S.sse_slack(pop, x, y, banks, 6, bits) if rows <= 300 else None
-    if slack is None:  # large case: programs with exact arithmetic only would be needed for a tight bound
-        ok = np.isclose(got, want64, rtol=5e-3, atol=1e-4) | ~np.isfinite(want64)
-        assert ok.mean() > 0.97
-    else:
-        assert parity.ill_conditioned_fraction(slack) < 0.1
-        assert not parity.sse_mismatches(got, want64, slack).any()
+    want64, slack = S.sse_reference_parallel(pop, x, y, banks, 6, bits)
+    print(f"skipped bins: {int((~np.isfinite(slack)).sum())} of {slack.size}")
+    assert parity.ill_conditioned_fraction(slack) < 0.1
+    bad = parity.sse_mismatches(got, want64, slack)
+    assert not bad.any(), (int(bad.sum()), np.argwhere(bad)[:4].tolist())
 
 
 def test_config1_static_sse_and_per_row_materialize(cuda):

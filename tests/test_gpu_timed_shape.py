@@ -1,0 +1,174 @@
+"""GPU parity on the shape the benchmark times: per-program coefficient tables with 64 sets of 16
+slots, 8 features, programs of up to 32 tokens over the full operation set with the protected
+routines, several row tiles and several row splits.  Checked against the CPU restatement (which is
+bit-identical to the reference's host evaluator, tests/test_oracle_golden.py) through its per-row
+values summed in float64, with the bound widened by the measured 2-ulp sensitivity of the math
+functions (tests/parity.py); the reference library itself is run on the same inputs where it was
+built.  Further cases hold the device path to bit-exact results where that is attainable.
+"""
+import numpy as np
+import pytest
+import torch
+
+import parity
+import support as S
+from secant_b200 import abi, programs as P
+from secant_b200.runner import Runner
+
+pytestmark = pytest.mark.gpu
+
+# Bins whose reference value changes between finite and non-finite when the math functions move by
+# 2 ulp cannot be compared at all.  On random 32-token programs with exp and the protected division
+# those are towers such as exp(exp(x) / ...) near the overflow threshold; their share has been
+# between 1 % and 4 % on every seed tried, so 8 % is the ceiling a test may skip.
+MAX_SKIPPED = 0.08
+
+
+def dev(a):
+    return torch.tensor(np.ascontiguousarray(a), device="cuda")
+
+
+def timed_shape(programs, rows, seed=2):
+    nb, K, F = 64, 16, 8
+    pop = P.random_population(seed, programs, 32, F, K, 3.0)
+    x = np.stack([P.uniform(seed + 100, c, rows, -3.0, 3.0) for c in range(F)])
+    y = (x[0] * x[1] - np.sin(x[2]) + P.normal(seed + 200, 0, rows, 0.05))[None, :].astype(np.float32)
+    banks = np.random.Generator(np.random.Philox(key=seed)).standard_normal((programs, nb, K), dtype=np.float32)
+    return pop, x, y, banks, nb, K, F
+
+
+def run_timed_shape(rn, pop, x, y, banks, nb, K):
+    out = torch.empty((len(pop.asts), 1, nb), device="cuda")
+    rn.run(rn.toggle_request(pop, dev(x), dev(y), dev(banks), nb, 0, out, bank_stride=K, program_bank_stride=nb * K))
+    return out.cpu().numpy()
+
+
+def test_population_of_the_timed_shape_over_tiles_and_splits(cuda):
+    """320 programs x 64 sets x 1,613 rows: four 512-row tiles, the last one ragged.  Scored three
+    ways: with the default plan (every CTA owns one tile, the splits are folded by the second
+    kernel), with the scratch capped so that one CTA walks all tiles (double-buffered staging,
+    accumulation across tiles), and a second time with the default plan (identical bits)."""
+    pop, x, y, banks, nb, K, F = timed_shape(320, 1613)
+    want64, slack = S.sse_reference_parallel(pop, x, y, banks, K, 0, program_bank_stride=nb * K)
+    skipped = parity.ill_conditioned_fraction(slack)
+    print(f"skipped bins: {int((~np.isfinite(slack)).sum())} of {slack.size} ({100 * skipped:.2f} %)")
+    assert skipped <= MAX_SKIPPED
+    with Runner(abi.SHAPE_TOGGLE_SSE, F, 1, K, workers=2, streams=2) as rn:
+        split = run_timed_shape(rn, pop, x, y, banks, nb, K)
+        again = run_timed_shape(rn, pop, x, y, banks, nb, K)
+        rn.set_scratch_limit(4 * len(pop.asts) * nb)          # room for a single split
+        walked = run_timed_shape(rn, pop, x, y, banks, nb, K)
+        rn.set_scratch_limit(0)
+    assert np.array_equal(split.view(np.uint32), again.view(np.uint32))      # sums do not depend on scheduling
+    for name, got in (("split", split), ("walked", walked)):
+        bad = parity.sse_mismatches(got, want64, slack)
+        assert not bad.any(), (name, int(bad.sum()), np.argwhere(bad)[:4].tolist())
+    # the same programs through the reference library itself (shared-table API: one program per call)
+    ref = S.reference_lib()
+    if ref is not None:
+        for a in range(0, len(pop.asts), 40):
+            code, want32 = S.reference_toggle_sse(ref, pop.subset([a]), x, y, banks[a], K, 0)
+            assert code == 0
+            calm = np.isfinite(slack[a]) & (slack[a] < 1e-6 * np.abs(want64[a]))
+            assert np.allclose(split[a][calm], want32[0][calm], rtol=3e-4, atol=1e-6)   # float32 sequential sums, ~1e-4 of noise
+
+
+def exact_population(seed, count, columns, constants, leaves=10):
+    """Random programs over operations every IEEE-754 implementation rounds identically:
+    + - * / min max neg abs sqrt rcp and the fused multiply-add (three-operand joins as in
+    projects/secant/tests/support/ast_stress.c:478-526)."""
+    rng = np.random.Generator(np.random.Philox(key=seed))
+    binary = ["ADD", "SUB", "MUL", "DIV", "MIN", "MAX"]
+    unary = ["NEG", "ABS", "SQRT", "RCP"]
+
+    def leaf():
+        k = rng.integers(4)
+        if k == 0:
+            return P.lit(float(rng.integers(-8, 9)) / 4.0)
+        if constants and k == 1:
+            return P.bank(int(rng.integers(constants)))
+        return P.col(int(rng.integers(columns)))
+
+    def expr(n):
+        if n <= 1:
+            body = leaf()
+        elif n >= 3 and rng.integers(5) == 0:
+            a = int(rng.integers(1, n - 1))
+            b = int(rng.integers(1, n - a))
+            body = expr(a) + expr(b) + expr(n - a - b) + P.op("FMA")
+        else:
+            a = int(rng.integers(1, n))
+            body = expr(a) + expr(n - a) + P.op(binary[int(rng.integers(len(binary)))])
+        while rng.integers(4) == 0:
+            body += P.op(unary[int(rng.integers(len(unary)))])
+        return body
+    return P.PackedPrograms([expr(int(rng.integers(1, leaves + 1))) + P.RET for _ in range(count)])
+
+
+def same_bits(a, b):
+    a, b = np.asarray(a, dtype=np.float32), np.asarray(b, dtype=np.float32)
+    return (a.view(np.uint32) == b.view(np.uint32)) | (np.isnan(a) & np.isnan(b))
+
+
+def test_exactly_rounded_operations_match_the_reference_bit_for_bit(cuda):
+    """Per-row outputs of programs over exactly rounded operations equal the host evaluator's bit
+    for bit, NaN and infinity included (projects/secant/s_cpu.c:329-352); their squared-error sums
+    then differ from the float64 sum of the same rows by float32 summation error only."""
+    rows, F, K, nb = 1500, 5, 4, 6
+    x = np.stack([P.uniform(91, c, rows, -2, 2) for c in range(F)])
+    x[:, :8] = np.array([0.0, -0.0, 1.0, -1.0, np.inf, -np.inf, 1e-40, 3e38], dtype=np.float32)   # special rows
+    static = exact_population(92, 300, F, 0)
+    with Runner(abi.SHAPE_MATERIALIZE, F) as rn:
+        got = rn.materialize(static, dev(x)).cpu().numpy()
+    ref = S.reference_lib()
+    code, want = S.reference_materialize(ref, static, x) if ref is not None else S.oracle_materialize(static, x)
+    assert code == 0
+    ok = same_bits(got, want)
+    # fminf/fmaxf of +0 and -0 may return either zero (C99 7.12.12); nothing else may differ
+    zero_sign = (got == 0) & (want == 0)
+    assert (ok | zero_sign).all(), np.argwhere(~(ok | zero_sign))[:4].tolist()
+    assert (~ok).sum() <= 1e-4 * ok.size
+    # the same operation set with banks and toggles, fused sums
+    bits = 2
+    pop = exact_population(93, 200, F, K)
+    y = np.stack([P.normal(94, 0, rows)])
+    banks = np.stack([P.normal(95, b, K) for b in range(nb)])
+    with Runner(abi.SHAPE_TOGGLE_SSE, F, 1, K, workers=2, streams=2) as rn:
+        sse = rn.toggle_sse(pop, dev(x), dev(y), dev(banks), nb, bits).cpu().numpy()
+    want64, slack = S.sse_reference_parallel(pop, x, y, banks, K, bits)
+    assert not slack.any()                                   # no transcendental anywhere: nothing to widen
+    finite = np.isfinite(want64) & (np.abs(want64) < 3e38)
+    assert np.array_equal(np.isnan(sse), np.isnan(want64))
+    assert np.array_equal(np.isfinite(sse), finite)
+    assert np.allclose(sse[finite], want64[finite], rtol=2e-6, atol=0)
+
+
+@pytest.mark.parametrize("inputs,targets", [(128, 1), (127, 2)])
+def test_datasets_as_wide_as_the_format_allows(cuda, inputs, targets):
+    """128 columns is the most a program can address (projects/secant/secant_instructions.h:41-48);
+    the last input columns and every target column must still be the ones read."""
+    rows = 300
+    x = np.stack([P.uniform(40, c, rows, -1, 1) for c in range(inputs)])
+    y = np.stack([P.normal(41, t, rows) for t in range(targets)])
+    progs = [P.col(inputs - 1) + P.RET, P.col(inputs - 1) + P.col(0) + P.op("MUL") + P.RET,
+             P.col(inputs - 2) + P.col(inputs - 1) + P.op("SUB") + P.col(64) + P.op("ADD") + P.RET]
+    pop = P.PackedPrograms(progs)
+    with Runner(abi.SHAPE_SSE, inputs, targets) as rn:
+        got = rn.sse(pop, dev(x), dev(y)).cpu().numpy()
+    _, _, want64 = S.oracle_sse(pop, x, y)
+    assert np.allclose(got, want64, rtol=1e-5)
+    with Runner(abi.SHAPE_MATERIALIZE, inputs) as rn:
+        mat = rn.materialize(pop, dev(x)).cpu().numpy()
+    assert same_bits(mat, S.oracle_materialize(pop, x)[1]).all()
+    with Runner(abi.SHAPE_AFFINE_STATS, inputs, targets) as rn:
+        stats = rn.affine_stats(pop, dev(x), dev(y)).cpu().numpy()
+    p = mat.astype(np.float64)
+    want = np.concatenate([p.sum(1)[:, None], (p * p).sum(1)[:, None], p @ y.astype(np.float64).T], axis=1)
+    assert np.allclose(stats, want, rtol=1e-5, atol=1e-5)
+    banks = np.stack([P.normal(42, b, 1) for b in range(5)])
+    toggled = P.PackedPrograms([P.col(inputs - 1) + P.bank(0) + P.op("MUL") + P.RET])
+    if inputs + 1 <= 128:
+        with Runner(abi.SHAPE_TOGGLE_SSE, inputs, targets, 1) as rn:
+            got = rn.toggle_sse(toggled, dev(x), dev(y), dev(banks), 5, 0).cpu().numpy()
+        _, _, want64 = S.oracle_toggle_sse(toggled, x, y, banks, 1, 0)
+        assert np.allclose(got, want64, rtol=1e-5)
