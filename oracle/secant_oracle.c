@@ -582,6 +582,14 @@ SO_EXPORT size_t so_topk(const float* scores, size_t count, size_t k, uint64_t* 
  * rounded operations (add, sub, mul, div, fma, sqrt, rcp, neg, abs, min, max).
  * Parity: unpinned beyond the reference's closed-form value and invalid-data matrix in the
  * test-suite (the reference has no general fp32 host scorer to run). */
+/* Checker-only switch.  The reference's one host-side rollout scorer takes every observation
+ * interval to be the constant 0.05f (projects/odezza/research/ast_tools/o_ast_engine_benchmark.c:376)
+ * instead of a difference of time stamps, and no float32 time axis has eight consecutive differences
+ * that all equal 0.05f.  With a positive value set here the integrator below uses it as the interval
+ * of every observation, which makes the two scorers comparable bit for bit; 0 restores the time axis. */
+static float so_fixed_interval = 0.0f;
+SO_EXPORT void so_rk4_set_fixed_interval(float value) { so_fixed_interval = value; }
+
 /* General form.  offsets == NULL: every trajectory has points_per_trajectory points and
  * times[points_per_trajectory] is shared.  offsets != NULL: the reference engine's launch layout
  * (projects/odezza/core/odezza.h:275-289, checks and loop of
@@ -642,7 +650,8 @@ static SecantResult so_rk4_general(const uint8_t* routine_blob, const uint64_t* 
                 valid = valid && isfinite(state[s]);
             }
             for (point = begin + 1; r == SECANT_SUCCESS && point < end; ++point) {
-                const float interval = offsets ? times[point] - times[point - 1] : times[point - begin] - times[point - begin - 1];
+                const float stamped = offsets ? times[point] - times[point - 1] : times[point - begin] - times[point - begin - 1];
+                const float interval = so_fixed_interval > 0.0f ? so_fixed_interval : stamped;
                 const float h = interval / (float)substeps;
                 const float half = 0.5f * h, sixth = h / 6.0f;
                 valid = valid && isfinite(interval) && interval > 0.0f && h > 0.0f;

@@ -108,3 +108,81 @@ def test_missing_observations_are_skipped_and_counted_out():
     holes[0, 3] = np.nan                                               # an initial value may never be missing
     _, scores = S.oracle_rk4(systems, 1, holes, 2, times, constants, substeps=2, offsets=offsets, allow_missing=True)
     assert np.all(scores == FLT_MAX)
+
+
+# ---- second pin: the reference's own host-side scorer on its fixed shape -----------------------
+
+_TO_ENGINE = {  # Secant opcode -> the reference engine's bytecode (projects/odezza/research/ast_tools/o_ast_tools.h:43-68)
+    "RET": 0x80, "COL": 0x81, "BANK": 0x82, "LIT": 0x83, "TOG2": 0x84, "TOG4": 0x85, "ADD": 0x90, "SUB": 0x91, "MUL": 0x92,
+    "DIV": 0x93, "NEG": 0x94, "SQRT": 0x95, "RCP": 0x96, "ABS": 0x97, "MIN": 0x98, "MAX": 0x99, "FMA": 0x9A, "SIN": 0x9B,
+    "COS": 0x9C, "EX2": 0x9D, "LG2": 0x9E, "RSQRT": 0x9F, "TANH": 0xA0, "EXP": 0xA1, "LOG": 0xA2}
+
+
+def to_engine_bytecode(code):
+    """The same postfix program in the reference engine's token values (operand bytes unchanged)."""
+    names = {v: k for k, v in P.OP.items()}
+    out, at = bytearray(), 0
+    while True:
+        name = names[code[at]]
+        width = P._WIDTH.get(code[at], 1)
+        out.append(_TO_ENGINE[name])
+        out += code[at + 1:at + width]
+        at += width
+        if name == "RET":
+            return bytes(out)
+
+
+def engine_reference_scorer():
+    import ctypes as C
+    import os
+    path = os.path.join(S.ROOT, "oracle", "_ref", "libodezza_cpu_ref.so")
+    if not os.path.exists(path):
+        return None
+    lib = C.CDLL(path)
+    lib.so_ref_o_cpu_score.restype = C.c_float
+    return lib
+
+
+def test_oracle_against_the_reference_host_scorer_on_its_fixed_shape():
+    """so_rk4_score against o_cpu_score (projects/odezza/research/ast_tools/o_ast_engine_benchmark.c:368-434,
+    over o_ast_cpu_evaluate, o_ast_cpu.c:111-209), compiled from the reference tree by `make -C oracle
+    odezza`: 4 states, 3 trajectories, 8 observations 0.05 apart, 5 toggle bits, 4 constants.  Seeded
+    right-hand sides over every operation (both sides call the same libm), toggles included, 1 and 4
+    steps per observation: the scores must agree bit for bit."""
+    import ctypes as C
+    import pytest
+    lib = engine_reference_scorer()
+    if lib is None:
+        pytest.skip("oracle/_ref/libodezza_cpu_ref.so is built only where the reference checkout is present")
+    S_, TR, OBS, K, BITS = 4, 3, 8, 4, 5
+    ops = [(P.op(n), 2) for n in ("ADD", "SUB", "MUL", "DIV", "MIN", "MAX")] + \
+          [(P.op(n), 1) for n in ("NEG", "ABS", "SQRT", "SIN", "COS", "TANH", "EXP", "LOG", "RCP")]
+    rng = np.random.Generator(np.random.Philox(key=808))
+    checked = finite = 0
+    S.oracle().so_rk4_set_fixed_interval(C.c_float(0.05))
+    try:
+        for trial in range(60):
+            pop = P.random_population(900 + trial, S_, 14, S_, K, 1.0, toggle_bits=BITS, ops=ops)
+            pop = P.PackedPrograms(pop.asts)                     # no routines in the engine's format
+            constants = rng.standard_normal((1, K)).astype(np.float32)
+            initial = rng.uniform(-1, 1, size=(S_, TR)).astype(np.float32)
+            targets = rng.uniform(-1, 1, size=(S_, TR, OBS)).astype(np.float32)
+            flat = np.concatenate([initial.reshape(-1), targets.reshape(-1)]).astype(np.float32)   # the scorer's own layout
+            mine = np.concatenate([initial[:, :, None], targets], axis=2).reshape(S_, TR * (OBS + 1))
+            times = (np.arange(OBS + 1) * 0.05).astype(np.float32)
+            engine = [to_engine_bytecode(a) for a in pop.asts]
+            bufs = [(C.c_uint8 * len(e)).from_buffer_copy(e) for e in engine]
+            ptrs = (C.POINTER(C.c_uint8) * S_)(*[C.cast(b, C.POINTER(C.c_uint8)) for b in bufs])
+            sizes = (C.c_size_t * S_)(*[len(e) for e in engine])
+            for perm in (0, 21, 31):
+                for steps in (1, 4):
+                    want = np.float32(lib.so_ref_o_cpu_score(ptrs, sizes, C.c_size_t(S_), S.fptr(constants), C.c_uint32(perm),
+                                                             S.fptr(flat), C.c_uint32(steps)))
+                    code, got = S.oracle_rk4(pop, S_, mine, TR, times, constants, substeps=steps, toggle_bits=BITS, permutation=perm)
+                    assert code == 0
+                    assert got[0].view(np.uint32) == want.view(np.uint32), (trial, perm, steps, float(got[0]), float(want))
+                    checked += 1
+                    finite += bool(want < FLT_MAX)
+    finally:
+        S.oracle().so_rk4_set_fixed_interval(C.c_float(0.0))
+    assert checked == 360 and finite > 100       # both valid scores and the FLT_MAX policy were exercised
