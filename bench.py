@@ -254,6 +254,118 @@ def rk4_arm(args, w):
                                    "frac": lane_ops / dt / peak.value, "traffic": None}}))
 
 
+# ------------------------------------------------------ the other benchmark shapes ----
+
+def _device_peak(lib):
+    probe = C.c_double()
+    abi.check(lib.secant_b200_fp32_peak_probe(0.5, C.byref(probe)), "fp32 peak probe")
+    return probe.value
+
+
+def toggles_arm(args, w):
+    """`--impl toggles`: the toggle-heavy shape (16,384 programs of at most 48 tokens whose sub-trees
+    are gated by 8 toggle bits, 256 variants x 4 coefficient sets = 1,024 configurations per program,
+    262,144 rows of 6 N(0,1) features), fused losses plus the best variant per program."""
+    import torch
+    from secant_b200 import runner as R
+    from secant_b200.runner import Runner
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device")
+    dev = torch.device("cuda", 0)
+    lib = abi.load()
+    Pn, bits, NB, F, K, N = (args.programs or 16384), 8, 4, 6, 8, (args.rows or 262144)
+    pop = P.gated_population(3, Pn, 48, F, K, bits)
+    ops = P.count_ops(pop)
+    x = torch.from_numpy(np.stack([P.normal(3, c, N) for c in range(F)])).to(dev)
+    y = torch.from_numpy(np.stack([P.normal(3, 100, N)])).to(dev)
+    banks = torch.from_numpy(np.stack([P.normal(3, 200 + b, K) for b in range(NB)])).to(dev)
+    configs = NB << bits
+    out = torch.empty((Pn, 1, configs), dtype=torch.float32, device=dev)
+    best = torch.empty(Pn * R.SCORE_BYTES, dtype=torch.uint8, device=dev)
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+    peak = _device_peak(lib)
+    seconds = []
+    with Runner(abi.SHAPE_TOGGLE_SSE, F, 1, K, workers=min(8, os.cpu_count() or 2), streams=2) as runner:
+        req = runner.toggle_request(pop, x, y, banks, NB, bits, out)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = lib.secant_b200_kernel_launch_count()
+        for it in range(args.warmup + args.steps):
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            if it == args.warmup:
+                launches0 = lib.secant_b200_kernel_launch_count()
+            runner.run(req)
+            ev0.record()
+            R.best_config(out.view(Pn, configs), out=best)
+            ev1.record()
+            torch.cuda.synchronize()
+            if it >= args.warmup:
+                seconds.append(runner.stats.runtime_seconds + ev0.elapsed_time(ev1) * 1e-3)
+        launches = lib.secant_b200_kernel_launch_count() - launches0
+    dt = sum(seconds) / len(seconds)
+    lane_ops = float((ops + 2).sum()) * configs * N
+    sse, cfg, valid = R.score_fields(best)
+    print(json.dumps({"impl": "toggles", "metric": METRIC, "value": float(Pn) * N / dt, "unit": "program-rows/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+                      "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "toggle-heavy specialization", "programs": Pn, "max_tokens": 48, "toggle_bits": bits,
+                                 "coefficient_sets": NB, "configurations_per_program": configs, "rows": N, "features": F,
+                                 "mean_ops_per_program": float(ops.mean()), "timed": "secant_cubin_runner_run with host "
+                                 "programs (CUDA events of the library's streams) plus the best-variant kernel"},
+                      "row_evals_per_s": float(Pn) * configs * N / dt, "gpu_launches": int(launches),
+                      "valid_fraction": float((valid > 0).float().mean().item()),
+                      "roofline": {"bound": "fp32", "achieved": lane_ops / dt / 1e12, "peak": peak / 1e12, "unit": "TFLOP/s",
+                                   "frac": lane_ops / dt / peak, "traffic": None}}))
+
+
+def box_arm(args, w):
+    """`--impl box`: the box-scale shape on one GPU (16 features, 2^22 rows, 16 coefficient sets per
+    program, programs of at most 32 tokens) with a program sample sized to seconds.  The 272 MiB
+    dataset does not fit the L2 cache, so every group of thread blocks streams its row range from
+    HBM: the line reports that stream in GB/s beside the arithmetic fraction."""
+    import torch
+    from secant_b200.runner import Runner
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device")
+    dev = torch.device("cuda", 0)
+    lib = abi.load()
+    Pn, NB, F, K, N = (args.programs or 49152), 16, 16, 16, (args.rows or 1 << 22)
+    pop = P.random_population(5, Pn, 32, F, K, 1.0)
+    ops = P.count_ops(pop)
+    x = torch.from_numpy(np.stack([P.uniform(5, c, N, -1.0, 1.0) for c in range(F)])).to(dev)
+    y = torch.from_numpy(hidden_target(x.cpu().numpy(), 5, depth=8)[None, :]).to(dev)
+    banks = torch.from_numpy(np.random.Generator(np.random.Philox(key=5)).standard_normal((Pn, NB, K), dtype=np.float32)).to(dev)
+    out = torch.empty((Pn, 1, NB), dtype=torch.float32, device=dev)
+    peak = _device_peak(lib)
+    seconds = []
+    with Runner(abi.SHAPE_TOGGLE_SSE, F, 1, K, workers=min(8, os.cpu_count() or 2), streams=2) as runner:
+        req = runner.toggle_request(pop, x, y, banks, NB, 0, out, bank_stride=K, program_bank_stride=NB * K)
+        launches0, stream0 = lib.secant_b200_kernel_launch_count(), lib.secant_b200_row_stream_bytes()
+        for it in range(args.warmup + args.steps):
+            if it == args.warmup:
+                launches0, stream0 = lib.secant_b200_kernel_launch_count(), lib.secant_b200_row_stream_bytes()
+            runner.run(req)                      # the dataset is larger than L2: nothing to flush
+            if it >= args.warmup:
+                seconds.append(runner.stats.runtime_seconds)
+        launches = lib.secant_b200_kernel_launch_count() - launches0
+        stream = (lib.secant_b200_row_stream_bytes() - stream0) / float(args.steps)
+    dt = sum(seconds) / len(seconds)
+    lane_ops = float((ops + 2).sum()) * NB * N
+    line = {"impl": "box", "metric": METRIC, "value": float(Pn) * N / dt, "unit": "program-rows/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "box-scale population, one GPU's share sampled", "programs": Pn, "rows": N, "features": F,
+                       "coefficient_sets": NB, "max_tokens": 32, "dataset_bytes": (F + 1) * 4 * N,
+                       "mean_ops_per_program": float(ops.mean())},
+            "row_evals_per_s": float(Pn) * NB * N / dt, "gpu_launches": int(launches),
+            "roofline": {"bound": "fp32", "achieved": lane_ops / dt / 1e12, "peak": peak / 1e12, "unit": "TFLOP/s",
+                         "frac": lane_ops / dt / peak, "traffic": None}}
+    line["row_stream"] = {"passes_over_the_dataset": stream / ((F + 1) * 4.0 * N), "bytes_per_step": stream,
+                          "GB_per_s": stream / dt / 1e9, "hbm_peak_GB_per_s": 6560.3,
+                          "note": "every program group of every launch reads each row once; measured copy peak of this pool's B200s"}
+    print(json.dumps(line))
+
+
 # ------------------------------------------------------------------ comparator arm ----
 
 def comparator_arm(args, w):
@@ -543,7 +655,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "comparator", "rk4"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "comparator", "rk4", "toggles", "box"])
     ap.add_argument("--programs", type=int, default=None, help="development only: shrink the population")
     ap.add_argument("--rows", type=int, default=None, help="development only: shrink the dataset")
     ap.add_argument("--no-cpu", action="store_true", help="development only: skip the CPU baseline and the parity spot check")
@@ -562,6 +674,10 @@ def main():
         comparator_arm(args, w)
     elif args.impl == "rk4":
         rk4_arm(args, w)
+    elif args.impl == "toggles":
+        toggles_arm(args, w)
+    elif args.impl == "box":
+        box_arm(args, w)
     else:
         gpu_arm(args, w)
 

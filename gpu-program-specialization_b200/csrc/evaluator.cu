@@ -201,10 +201,40 @@ struct Machine {
                 for (int g = 0; g < GROUPS; ++g)
                     *reinterpret_cast<float4*>(q + g * 128) = make_float4(acc[4 * g][0], acc[4 * g + 1][0], acc[4 * g + 2][0], acc[4 * g + 3][0]);
                 break; }
+#ifndef SB_MERGED_KINDS
             SB_BIN_CASES(SB_BIN_ADD)
             SB_BIN_CASES(SB_BIN_SUB)
             SB_BIN_CASES(SB_BIN_RSUB)
             SB_BIN_CASES(SB_BIN_MUL)
+#else
+            case SB_CASE_BIN + SB_BIN_ADD * SB_NUM_KINDS + 0: case SB_CASE_BIN + SB_BIN_ADD * SB_NUM_KINDS + 1: case SB_CASE_BIN + SB_BIN_ADD * SB_NUM_KINDS + 2:
+            case SB_CASE_BIN + SB_BIN_SUB * SB_NUM_KINDS + 0: case SB_CASE_BIN + SB_BIN_SUB * SB_NUM_KINDS + 1: case SB_CASE_BIN + SB_BIN_SUB * SB_NUM_KINDS + 2:
+            case SB_CASE_BIN + SB_BIN_RSUB * SB_NUM_KINDS + 0: case SB_CASE_BIN + SB_BIN_RSUB * SB_NUM_KINDS + 1: case SB_CASE_BIN + SB_BIN_RSUB * SB_NUM_KINDS + 2:
+            case SB_CASE_BIN + SB_BIN_MUL * SB_NUM_KINDS + 0: case SB_CASE_BIN + SB_BIN_MUL * SB_NUM_KINDS + 1: case SB_CASE_BIN + SB_BIN_MUL * SB_NUM_KINDS + 2:
+            case SB_CASE_BIN + SB_BIN_MIN * SB_NUM_KINDS + 0: case SB_CASE_BIN + SB_BIN_MIN * SB_NUM_KINDS + 1: case SB_CASE_BIN + SB_BIN_MIN * SB_NUM_KINDS + 2:
+            case SB_CASE_BIN + SB_BIN_MAX * SB_NUM_KINDS + 0: case SB_CASE_BIN + SB_BIN_MAX * SB_NUM_KINDS + 1: case SB_CASE_BIN + SB_BIN_MAX * SB_NUM_KINDS + 2: {
+                const unsigned rel = (ins.x & 0xffu) - SB_CASE_BIN;
+                const unsigned kind = rel % SB_NUM_KINDS;
+                float xv[RR][RC];
+                if (kind == SB_KIND_ROW) {
+                    float x[RR]; fetch_row(rowp, hrowp, tile_ld, idx, x);
+                    SB_FOR_TILE xv[r][c] = x[r];
+                } else if (kind == SB_KIND_CST) {
+                    float x[RC]; fetch_cst(cst, idx, x);
+                    SB_FOR_TILE xv[r][c] = x[c];
+                } else {
+                    fetch_slot(slots, idx, xv);
+                }
+                switch (rel / SB_NUM_KINDS) {
+                case SB_BIN_ADD: SB_FOR_TILE acc[r][c] = binop<SB_BIN_ADD>(acc[r][c], xv[r][c]); break;
+                case SB_BIN_SUB: SB_FOR_TILE acc[r][c] = binop<SB_BIN_SUB>(acc[r][c], xv[r][c]); break;
+                case SB_BIN_RSUB: SB_FOR_TILE acc[r][c] = binop<SB_BIN_RSUB>(acc[r][c], xv[r][c]); break;
+                case SB_BIN_MUL: SB_FOR_TILE acc[r][c] = binop<SB_BIN_MUL>(acc[r][c], xv[r][c]); break;
+                case SB_BIN_MIN: SB_FOR_TILE acc[r][c] = binop<SB_BIN_MIN>(acc[r][c], xv[r][c]); break;
+                default: SB_FOR_TILE acc[r][c] = binop<SB_BIN_MAX>(acc[r][c], xv[r][c]); break;
+                }
+                break; }
+#endif
             /* IEEE division is ~10 instructions per element: the six operand-kind cases
              * only expand the operand, then share one body per direction. */
             case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_ROW:
@@ -244,35 +274,28 @@ struct Machine {
                     }
                 }
                 break; }
+#ifndef SB_MERGED_KINDS
             SB_BIN_CASES(SB_BIN_MIN)
             SB_BIN_CASES(SB_BIN_MAX)
+#endif
             SB_UN_CASE(SB_UN_NEG)
             SB_UN_CASE(SB_UN_ABS)
-            case SB_CASE_UN + SB_UN_EX2:
-                if (FAST) { SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_EX2, acc[r][c]); } else SB_FOR_QUADS(sbm::exp2_4(in))
-                break;
-            case SB_CASE_UN + SB_UN_EXP:
-                if (FAST) { SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_EXP, acc[r][c]); } else SB_FOR_QUADS(sbm::exp4(in))
-                break;
-            case SB_CASE_UN + SB_UN_LOG:
-                if (FAST) { SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_LOG, acc[r][c]); } else SB_FOR_QUADS(sbm::log4(in))
-                break;
-            case SB_CASE_UN + SB_UN_SIN:
-            case SB_CASE_UN + SB_UN_COS: { /* cos x = sin(x + pi/2): one body, shifted quadrant */
-                const int shift = (int)(ins.x & 0xffu) - (SB_CASE_UN + SB_UN_SIN);
-                if (FAST) {
-                    if (shift) { SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_COS, acc[r][c]); }
-                    else { SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_SIN, acc[r][c]); }
-                } else SB_FOR_QUADS(sbm::sincos4(in, shift))
-                break; }
-            case SB_CASE_UN + SB_UN_SQRT:
-            case SB_CASE_UN + SB_UN_RCP:
-            case SB_CASE_UN + SB_UN_LG2:
-            case SB_CASE_UN + SB_UN_RSQRT:
+            case SB_CASE_UN + SB_UN_EX2: case SB_CASE_UN + SB_UN_EXP: case SB_CASE_UN + SB_UN_LOG:
+            case SB_CASE_UN + SB_UN_SIN: case SB_CASE_UN + SB_UN_COS: case SB_CASE_UN + SB_UN_SQRT:
+            case SB_CASE_UN + SB_UN_RCP: case SB_CASE_UN + SB_UN_LG2: case SB_CASE_UN + SB_UN_RSQRT:
             case SB_CASE_UN + SB_UN_TANH: {
+                /* one body for every function: the operation is selected inside the out-of-line call */
                 const unsigned op = (ins.x & 0xffu) - SB_CASE_UN;
-                if (FAST) { SB_FOR_TILE acc[r][c] = sbm::fast_unary(op, acc[r][c]); }
-                else SB_FOR_QUADS(sbm::rare4(in, op))
+                if (FAST) {
+                    switch (op) { /* a few instructions per element: unrolled in place */
+                    case SB_UN_SIN: SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_SIN, acc[r][c]); break;
+                    case SB_UN_COS: SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_COS, acc[r][c]); break;
+                    case SB_UN_EXP: SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_EXP, acc[r][c]); break;
+                    case SB_UN_LOG: SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_LOG, acc[r][c]); break;
+                    case SB_UN_EX2: SB_FOR_TILE acc[r][c] = sbm::fast_unary(SB_UN_EX2, acc[r][c]); break;
+                    default: SB_FOR_TILE acc[r][c] = sbm::fast_unary(op, acc[r][c]); break;
+                    }
+                } else SB_FOR_QUADS(sbm::unary4(in, op))
                 break; }
             case SB_CASE_FMA:
                 store_slot(slots, scratch_slot);
@@ -335,15 +358,7 @@ __device__ __forceinline__ float scalar_unary(unsigned op, float a) {
     if (op == SB_UN_NEG) return -a;
     if (op == SB_UN_ABS) return fabsf(a);
     if (FAST) return sbm::fast_unary(op, a);
-    const float4 v = make_float4(a, a, a, a);
-    switch (op) {
-    case SB_UN_SIN: return sbm::sincos4(v, 0).x;
-    case SB_UN_COS: return sbm::sincos4(v, 1).x;
-    case SB_UN_EX2: return sbm::exp2_4(v).x;
-    case SB_UN_EXP: return sbm::exp4(v).x;
-    case SB_UN_LOG: return sbm::log4(v).x;
-    default: return sbm::rare4(v, op).x;
-    }
+    return sbm::unary4(make_float4(a, a, a, a), op).x;
 }
 template <bool FAST>
 __device__ __forceinline__ float scalar_binary(unsigned op, float a, float x) {
@@ -389,25 +404,25 @@ __device__ __noinline__ void run_bank_part(const SbInsn* exec, uint32_t first_ba
         for (;;) {
             const uint2 ins = *ip++;
             const unsigned cs = ins.x & 0xffu;
+            if (cs == SB_CASE_END || cs > SB_CASE_FMA) break;
+            /* operands first, at one site (the fetch is the bulky part): one for loads and binary
+             * operations, three for the fused multiply-add, none otherwise */
+            float v[3] = {acc, acc, acc};
+            const bool fma = cs == SB_CASE_FMA, bin = cs >= SB_CASE_BIN && cs < SB_CASE_UN;
+            const unsigned count = fma ? 3u : (cs < SB_CASE_STORE || bin) ? 1u : 0u;
+#pragma unroll 1
+            for (unsigned i = 0; i < count; ++i) {
+                const unsigned kind = fma ? (ins.x >> (8 + 2 * i)) & 3u : bin ? (cs - SB_CASE_BIN) % SB_NUM_KINDS : cs - SB_CASE_LOAD;
+                const uint32_t idx = fma ? (ins.y >> (10 * i)) & 1023u : ins.x >> 16;
+                if (kind != SB_FMA_ACC) v[i] = operand(kind, idx);
+            }
             const uint32_t idx = ins.x >> 16;
-            if (cs == SB_CASE_END) break;
-            if (cs < SB_CASE_STORE) acc = operand(cs - SB_CASE_LOAD, idx);
+            if (cs < SB_CASE_STORE) acc = v[0];
             else if (cs == SB_CASE_STORE) tmp[idx * 32 + lane] = acc;
             else if (cs == SB_CASE_STOREH) { if (live) mine[(size_t)idx * RC] = acc; }
-            else if (cs < SB_CASE_UN) {
-                const unsigned rel = cs - SB_CASE_BIN;
-                acc = scalar_binary<FAST>(rel / SB_NUM_KINDS, acc, operand(rel % SB_NUM_KINDS, idx));
-            } else if (cs < SB_CASE_FMA) acc = scalar_unary<FAST>(cs - SB_CASE_UN, acc);
-            else if (cs == SB_CASE_FMA) {
-                const unsigned kinds = (ins.x >> 8) & 0x3fu;
-                float v[3];
-#pragma unroll
-                for (int i = 0; i < 3; ++i) {
-                    const unsigned kind = (kinds >> (2 * i)) & 3u;
-                    v[i] = kind == SB_FMA_ACC ? acc : operand(kind, (ins.y >> (10 * i)) & 1023u);
-                }
-                acc = __fmaf_rn(v[0], v[1], v[2]);
-            } else break;
+            else if (bin) acc = scalar_binary<FAST>((cs - SB_CASE_BIN) / SB_NUM_KINDS, acc, v[0]);
+            else if (fma) acc = __fmaf_rn(v[0], v[1], v[2]);
+            else acc = scalar_unary<FAST>(cs - SB_CASE_UN, acc);
         }
     }
 }
@@ -429,7 +444,7 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
  * [column][tile_ld]; rows up to `padded` are zero-filled.  A column whose first row is 16-byte
  * aligned moves as 16-byte copies, any other as 4-byte copies (callers only promise 4-byte
  * alignment of their matrices).  Completion: cp_async_wait_all() by every thread, then a barrier. */
-__device__ __forceinline__ void stage_tile(float* tile, uint32_t tile_ld, const EvalProblem& prob, uint32_t ncols, size_t c0,
+__device__ __noinline__ void stage_tile(float* tile, uint32_t tile_ld, const EvalProblem& prob, uint32_t ncols, size_t c0,
                                            uint32_t rows, uint32_t padded) {
     for (uint32_t col = 0; col < ncols; ++col) {
         const float* src = (col < prob.num_inputs ? prob.input + (size_t)col * prob.input_ld
@@ -481,27 +496,33 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
     const uint32_t gpi = geom.groups_per_item;
     /* configuration groups of one program: permutation-major, RC banks per group */
     const uint32_t bank_groups = materialize ? 1u : (prob.num_banks + RC - 1) / RC;
-    const unsigned long long items_per_program = materialize ? 1ull : ((unsigned long long)(bank_groups / gpi) << prob.toggle_bits);
-    const unsigned int num_items = (unsigned int)(items_per_program * prog_count); /* the planner keeps this below 2^32 - 256 */
+    /* items of one program: permutation-major, `chunks` items of gpi bank groups per permutation;
+     * the planner keeps items_per_program * prog_count below 2^32 - 256, so item arithmetic is 32-bit */
+    const uint32_t chunks = materialize ? 1u : bank_groups / gpi;
+    const uint32_t items_per_program = materialize ? 1u : (uint32_t)((unsigned long long)chunks << prob.toggle_bits);
+    const unsigned int num_items = items_per_program * prog_count;
     const unsigned long long configs = (unsigned long long)prob.num_banks << prob.toggle_bits;
     const size_t tile_floats = geom.tile_bytes / 4;
     const uint32_t num_tiles = (uint32_t)((row_end - row_begin + geom.tile_rows - 1) / geom.tile_rows);
 
+    /* Tiles: with two buffers tile t + 1 is fetched while tile t is used; with one (a tile so large
+     * that only one fits beside the warps' working sets) the fetch follows a barrier after the tile. */
+    const bool overlapped = geom.tile_buffers > 1;
     if (threadIdx.x == 0) queue[0] = 0u;
-    {
-        const uint32_t rows0 = (uint32_t)min((size_t)geom.tile_rows, row_end - row_begin);
-        stage_tile(tiles, tile_ld, prob, ncols, row_begin, rows0, (rows0 + M::PASS - 1) / M::PASS * M::PASS);
-    }
     for (uint32_t t = 0; t < num_tiles; ++t) {
         const size_t c0 = row_begin + (size_t)t * geom.tile_rows;
         const uint32_t chunk_rows = (uint32_t)min((size_t)geom.tile_rows, row_end - c0);
         const uint32_t npass = (chunk_rows + M::PASS - 1) / M::PASS;
-        const float* const tile = tiles + (size_t)(t & 1u) * tile_floats;
+        const float* const tile = tiles + (overlapped ? (size_t)(t & 1u) * tile_floats : 0);
         unsigned int* const q = queue + (t & 1u);
+        if (t == 0 || !overlapped) {
+            if (t) __syncthreads(); /* every warp has left the buffer */
+            stage_tile(tiles, tile_ld, prob, ncols, c0, chunk_rows, npass * M::PASS);
+        }
         cp_async_wait_all();
         __syncthreads(); /* tile t has landed; every warp has left tile t - 1 */
         if (threadIdx.x == 0) queue[(t + 1) & 1u] = 0u;
-        if (t + 1 < num_tiles) { /* fetch the next tile into the other buffer while this one is used */
+        if (overlapped && t + 1 < num_tiles) {
             const size_t n0 = c0 + geom.tile_rows;
             const uint32_t nrows = (uint32_t)min((size_t)geom.tile_rows, row_end - n0);
             stage_tile(tiles + (size_t)((t + 1) & 1u) * tile_floats, tile_ld, prob, ncols, n0, nrows, (nrows + M::PASS - 1) / M::PASS * M::PASS);
@@ -512,8 +533,7 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
             if (lane == 0) item = atomicAdd(q, 1u);
             item = __shfl_sync(0xffffffffu, item, 0);
             if (item >= num_items) break;
-            const uint32_t pi = (uint32_t)(item / items_per_program);
-            const unsigned long long first_group = (item % items_per_program) * gpi; /* among the program's configuration groups */
+            const uint32_t pi = item / items_per_program, within = item - pi * items_per_program;
             const uint32_t lp = group + pi * geom.num_groups;                        /* index inside the batch */
             const SbProgram* const hp = batch.programs + lp;
             const uint32_t n_insn = hp->n_insn, pre_off = hp->pre_off, main_off = hp->main_off, n_cst = hp->n_cst;
@@ -525,16 +545,16 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
                 if (lane == 0) exec[n_insn] = SbInsn{0u, 0u}; /* padding read by the instruction prefetch */
             }
             /* an item never straddles permutations: toggles are patched once per item */
-            const unsigned long long perm = materialize ? prob.fixed_permutation : first_group / bank_groups;
-            const uint32_t first_bg = materialize ? 0u : (uint32_t)(first_group % bank_groups);
+            const uint32_t perm = materialize ? prob.fixed_permutation : within / chunks;
+            const uint32_t first_bg = materialize ? 0u : (within - perm * chunks) * gpi;
             const uint32_t ngroups = materialize ? 1u : min(gpi, bank_groups - first_bg);
             if (n_patch) {
                 __syncwarp(); /* the copy above and the patches below touch the same words from different lanes */
                 const SbPatch* patches = batch.patches + hp->patch_off;
                 for (uint32_t i = lane; i < n_patch; i += 32) {
                     const SbPatch* p = patches + i;
-                    unsigned choice = (unsigned)(perm >> p->bit0) & 1u;
-                    if (p->bit1 != 0xffu) choice |= ((unsigned)(perm >> p->bit1) & 1u) << 1;
+                    unsigned choice = (perm >> p->bit0) & 1u;
+                    if (p->bit1 != 0xffu) choice |= ((perm >> p->bit1) & 1u) << 1;
                     exec[p->insn] = p->alt[choice];
                 }
             }
@@ -585,25 +605,15 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
                         m.fetch_column(rowp + (size_t)prob.num_inputs * tile_ld, tv);
 #pragma unroll
                         for (int c = 0; c < RC; ++c) part[c] = 0.0f;
-                        if (full) {
 #pragma unroll
-                            for (int r = 0; r < RR; ++r)
+                        for (int r = 0; r < RR; ++r)
+                            if (full || row0 + (r / 4) * 128 + (r % 4) < chunk_rows) { /* rows past the data score nothing */
 #pragma unroll
                                 for (int c = 0; c < RC; ++c) {
                                     const float e = __fsub_rn(m.acc[r][c], tv[r]);
                                     part[c] = __fmaf_rn(e, e, part[c]);
                                 }
-                        } else {
-#pragma unroll
-                            for (int r = 0; r < RR; ++r) {
-                                const bool ok = row0 + (r / 4) * 128 + (r % 4) < chunk_rows;
-#pragma unroll
-                                for (int c = 0; c < RC; ++c) {
-                                    const float e = ok ? __fsub_rn(m.acc[r][c], tv[r]) : 0.0f;
-                                    part[c] = __fmaf_rn(e, e, part[c]);
-                                }
                             }
-                        }
                         const float total = column_totals<RC>(part, lane);
                         if ((lane & (32 / RC - 1)) == 0) psum[g * RC + lane / (32 / RC)] += total;
                     } else {
@@ -642,16 +652,17 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
              * CTA touches them, and a barrier separates its tiles) */
             {
                 const bool independent = (flags & SB_PROG_BANK_INDEPENDENT) != 0;
-                float* const mine = partial + ((size_t)split * batch.num_programs + lp) * nq * configs + perm;
-                const uint32_t per_q = ngroups * RC;
-                for (uint32_t e = lane; e < nq * per_q; e += 32) {
-                    const uint32_t qn = e / per_q, rem = e % per_q, g = rem / RC, c = rem % RC;
-                    const uint32_t bank = (first_bg + g) * RC + c;
-                    if (bank >= prob.num_banks) continue;
-                    const float v = independent ? psum[qn * gpi * RC] : psum[(qn * gpi + g) * RC + c];
-                    float* dst = mine + (size_t)qn * configs + ((size_t)bank << prob.toggle_bits);
-                    *dst = t == 0 ? v : __fadd_rn(*dst, v);
-                }
+                float* mine = partial + ((size_t)split * batch.num_programs + lp) * nq * configs + perm;
+                const uint32_t width = ngroups * RC;          /* banks of the item, padding included */
+                const float* sums = psum;
+                for (uint32_t qn = 0; qn < nq; ++qn, mine += configs, sums += gpi * RC)
+                    for (uint32_t e = lane; e < width; e += 32) {
+                        const uint32_t bank = first_bg * RC + e;
+                        if (bank >= prob.num_banks) continue;
+                        const float v = independent ? sums[0] : sums[e]; /* psum is [quantity][group][bank of the group] */
+                        float* dst = mine + ((size_t)bank << prob.toggle_bits);
+                        *dst = t == 0 ? v : __fadd_rn(*dst, v);
+                    }
             }
         }
     }

@@ -103,6 +103,7 @@ LaunchPlan plan_with_tile(const DeviceBatch& batch, const EvalProblem& prob, int
                 trial.warps = *w;
                 trial.tile_rows = (uint32_t)tile_rows;
                 trial.tile_buffers = rows_padded > tile_rows ? 2u : 1u;
+                if (std::getenv("SB_DEV_SINGLE")) trial.tile_buffers = 1; /* DEV */
                 trial.num_groups = 1;
                 trial.row_splits = 1;
                 trial.rows_per_split = prob.num_rows;

@@ -36,6 +36,7 @@ extern "C" int secant_b200_fault_hook(const char* site);
 namespace sb {
 
 std::atomic<uint64_t> g_kernel_launches{0};
+std::atomic<uint64_t> g_row_stream_bytes{0};
 void note_kernel_launches(unsigned n) { g_kernel_launches.fetch_add(n); }
 
 namespace {
@@ -462,6 +463,9 @@ SecantResult launch_batch(SecantCubinRunnerImpl* r, const DeviceBatch& db, const
         cudaError_t ce = after ? cudaStreamWaitEvent(stream, after, 0) : cudaSuccess;
         if (ce == cudaSuccess) ce = launch_eval(db, prob, lp, partial, stream, &launches);
         g_kernel_launches.fetch_add(launches);
+        if (launches)
+            g_row_stream_bytes.fetch_add((uint64_t)lp.num_groups * (prob.num_inputs + (prob.mode == EVAL_MATERIALIZE ? 0u : prob.num_targets)) *
+                                         (uint64_t)prob.num_rows * sizeof(float));
         if (ce == cudaSuccess && done) ce = cudaEventRecord((*done)[k], stream);
         if (ce != cudaSuccess) return cuda_fail(r, ce, "kernel launch");
         if (used) (*used)[k] = 1;
@@ -755,6 +759,7 @@ SecantResult secant_cubin_runner_destroy(SecantCubinRunner r) {
 const char* secant_b200_runner_last_error(SecantCubinRunner r) { return r ? r->last_error.c_str() : ""; }
 
 uint64_t secant_b200_kernel_launch_count(void) { return g_kernel_launches.load(); }
+uint64_t secant_b200_row_stream_bytes(void) { return g_row_stream_bytes.load(); }
 
 }  // extern "C"
 

@@ -219,6 +219,7 @@ EXPORTED = {
     "secant_b200_fp32_peak_probe": (C.c_int32, [C.c_double, C.POINTER(C.c_double)]),
     "secant_b200_runner_last_error": (C.c_char_p, [C.c_void_p]),
     "secant_b200_kernel_launch_count": (C.c_uint64, []),
+    "secant_b200_row_stream_bytes": (C.c_uint64, []),
 }
 
 _lib = None

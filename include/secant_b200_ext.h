@@ -249,4 +249,10 @@ SECANT_DEC const char* secant_b200_runner_last_error(SecantCubinRunner runner);
 /* Number of kernels this library has launched in the calling process so far. */
 SECANT_DEC uint64_t secant_b200_kernel_launch_count(void);
 
+/* Bytes of dataset rows the evaluator launches of the calling process have been asked to read so
+ * far: every launch splits its programs into groups of thread blocks and each group reads every
+ * row of every column once ((inputs + targets) x rows x 4 bytes per group).  With a dataset larger
+ * than the L2 cache this is the row stream from HBM; benchmarks divide it by the run time. */
+SECANT_DEC uint64_t secant_b200_row_stream_bytes(void);
+
 #endif /* SECANT_B200_EXT_H_INCLUDED */

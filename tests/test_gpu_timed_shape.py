@@ -165,10 +165,12 @@ def test_datasets_as_wide_as_the_format_allows(cuda, inputs, targets):
     p = mat.astype(np.float64)
     want = np.concatenate([p.sum(1)[:, None], (p * p).sum(1)[:, None], p @ y.astype(np.float64).T], axis=1)
     assert np.allclose(stats, want, rtol=1e-5, atol=1e-5)
+    # the toggle recipe bounds (inputs + targets) x tile rows by 12,000 floats
+    # (projects/secant/s_cubin_generate_toggle_sse.c:333-334): 91 columns are its widest at 128 rows
+    wide = 91
     banks = np.stack([P.normal(42, b, 1) for b in range(5)])
-    toggled = P.PackedPrograms([P.col(inputs - 1) + P.bank(0) + P.op("MUL") + P.RET])
-    if inputs + 1 <= 128:
-        with Runner(abi.SHAPE_TOGGLE_SSE, inputs, targets, 1) as rn:
-            got = rn.toggle_sse(toggled, dev(x), dev(y), dev(banks), 5, 0).cpu().numpy()
-        _, _, want64 = S.oracle_toggle_sse(toggled, x, y, banks, 1, 0)
-        assert np.allclose(got, want64, rtol=1e-5)
+    toggled = P.PackedPrograms([P.col(wide - 1) + P.bank(0) + P.op("MUL") + P.col(wide - 2) + P.op("ADD") + P.RET])
+    with Runner(abi.SHAPE_TOGGLE_SSE, wide, targets, 1) as rn:
+        got = rn.toggle_sse(toggled, dev(x[:wide]), dev(y), dev(banks), 5, 0).cpu().numpy()
+    _, _, want64 = S.oracle_toggle_sse(toggled, x[:wide], y, banks, 1, 0)
+    assert np.allclose(got, want64, rtol=1e-5)
