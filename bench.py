@@ -370,12 +370,12 @@ def box_arm(args, w):
 
 def comparator_arm(args, w):
     """`--impl comparator`: the reference's kernel design with compiler-written program bodies
-    (secant_b200/comparator.py) against this library's evaluator, on the same sample of the
+    (tests/comparator.py) against this library's evaluator, on the same sample of the
     workload with one shared coefficient table (the reference's bank semantics).  Compile time
     is reported beside the kernel time; it is what the reference's machine-code patching and
     this library's record interpreter both exist to avoid."""
     import torch
-    from secant_b200 import comparator as K
+    import comparator as K
     from secant_b200.runner import Runner
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device")

@@ -254,3 +254,13 @@ SBT_EXPORT int sbt_plan(uint32_t num_programs, uint32_t max_insn, uint32_t max_s
     for (int i = 0; i < 13; ++i) out[i] = v[i];
     return 1;
 }
+
+/* Copies the instruction words of one record (w0, w1 pairs); returns the instruction count. */
+SBT_EXPORT size_t sbt_instructions(const SbtBatch* b, size_t program, uint32_t* words, size_t capacity_insns) {
+    const SbProgram& p = b->enc.programs[program];
+    for (size_t i = 0; i < p.n_insn && i < capacity_insns; ++i) {
+        words[2 * i] = b->enc.insns[p.insn_off + i].w0;
+        words[2 * i + 1] = b->enc.insns[p.insn_off + i].w1;
+    }
+    return p.n_insn;
+}

@@ -28,7 +28,7 @@ import time
 
 import numpy as np
 
-from .programs import OP, _WIDTH
+from secant_b200.programs import OP, _WIDTH
 
 _BINARY = {OP["ADD"]: "__fadd_rn({a}, {b})", OP["SUB"]: "__fsub_rn({a}, {b})", OP["MUL"]: "__fmul_rn({a}, {b})",
            OP["DIV"]: "({a} / {b})", OP["MIN"]: "fminf({a}, {b})", OP["MAX"]: "fmaxf({a}, {b})"}

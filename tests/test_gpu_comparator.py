@@ -1,4 +1,4 @@
-"""The compiled-topology comparator (secant_b200/comparator.py) must compute what the oracle
+"""The compiled-topology comparator (tests/comparator.py) must compute what the oracle
 computes, otherwise its timing means nothing: NVRTC-compiled expression code in the reference's
 kernel layout against the float64-accumulated oracle sums, toggles and affine leaves included."""
 import numpy as np
@@ -7,7 +7,8 @@ import torch
 
 import parity
 import support as S
-from secant_b200 import comparator as K, programs as P
+import comparator as K
+from secant_b200 import programs as P
 
 
 def test_generated_source_matches_reference_layout_rules():

@@ -23,3 +23,41 @@ def test_reference_consumer_passes_against_the_drop_in(cuda):
     done = subprocess.run([BINARY], capture_output=True, text=True, timeout=300)
     assert done.returncode == 0, done.stderr[-2000:]
     assert "CUDA SR adapter: CPU agreement" in done.stdout
+
+
+SEARCH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "oracle", "_ref", "secant_sr_search")
+
+
+def _search(backend, extra=()):
+    import json
+    args = [SEARCH, "--backend", backend, "--problem", "nguyen1", "--population", "256", "--generations", "6", "--banks", "16",
+            "--constants", "4", "--toggle-bits", "4", "--seed", "7", "--rows", "512", "--validation-rows", "256", *extra]
+    env = dict(os.environ, CUDA_MODULE_LOADING="EAGER")
+    done = subprocess.run(args, capture_output=True, text=True, timeout=600, env=env)
+    events = [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
+    return done, events
+
+
+@pytest.mark.gpu
+def test_reference_search_driver_runs_on_the_drop_in(cuda):
+    """The reference's search driver (projects/secant-sr/toggle/src/main.c, README.md:68-79) with its
+    CUDA backend, compiled unmodified against this library (oracle/Makefile, target `search`):
+    populations are scored through secant_cubin_runner_run_toggle_sse, coefficient refinement through
+    secant_sr_cuda_score_banks (projects/secant-sr/toggle/src/cuda.c:368-489).  The driver replays its
+    winner on the host evaluator and fails when the two scores disagree; the first generation, scored
+    from the same seeded population on both backends, must report the same best error."""
+    if not os.path.exists(SEARCH):
+        pytest.skip("oracle/_ref/secant_sr_search is built only where the reference checkout exists")
+    gpu, gpu_events = _search("cuda")
+    assert gpu.returncode == 0, gpu.stderr[-2000:]
+    cpu, cpu_events = _search("cpu")
+    assert cpu.returncode == 0, cpu.stderr[-2000:]
+    first = lambda events: next(e for e in events if e.get("event") == "generation")
+    g, c = first(gpu_events), first(cpu_events)
+    assert g["configurations"] == c["configurations"] and g["finite_configurations"] == c["finite_configurations"]
+    assert abs(g["best_mse"] - c["best_mse"]) <= 2e-4 * abs(c["best_mse"]) + 1e-9, (g, c)
+    assert any(e.get("event") == "result" for e in gpu_events)
+    # the refinement path: new coefficient banks proposed and scored for a fixed set of programs
+    refined, events = _search("cuda", ("--refine-rounds", "2", "--refine-budget", "32"))
+    assert refined.returncode == 0, refined.stderr[-2000:]
+    assert any(e.get("event") == "result" for e in events)
