@@ -477,7 +477,7 @@ def parity_spot(w, pop, x_h, y_h, banks_h, runner, dev, programs=32, rows=65536)
 def gpu_arm(args, w):
     import torch
     import torch.distributed as dist
-    from secant_b200 import runner as R
+    from secant_b200 import sharding
     from secant_b200.runner import Runner
 
     rank = int(os.environ.get("RANK", "0"))
@@ -524,17 +524,13 @@ def gpu_arm(args, w):
     out = torch.empty((Pn, 1, NB), dtype=torch.float32, device=dev)
     flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)   # larger than the 126 MB L2
 
-    records = torch.empty(Pn * R.SCORE_BYTES, dtype=torch.uint8, device=dev)          # all-gather send buffer
-    gathered = torch.empty(world * Pn * R.SCORE_BYTES, dtype=torch.uint8, device=dev) if world > 1 else records
-    k_top = min(1024, world * Pn)
+    # best set per program (device kernel writing straight into the all-gather send buffer), one
+    # all-gather of the 24-byte records, the same top-1024 kernel on every rank
+    combine_step = sharding.Combine(world * Pn, world, rank, 1024, dev)
+    k_top = combine_step.k
 
     def combine(scores):
-        """Best set per program (device kernel writing straight into the all-gather send
-        buffer), one all-gather of the 24-byte records, the same top-1024 on every rank."""
-        R.best_config(scores.view(Pn, NB), out=records)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, records)
-        return R.topk(R.score_fields(gathered)[0], k_top)[0]
+        return combine_step(scores.view(Pn, NB))[0]
 
     runner = Runner(abi.SHAPE_TOGGLE_SSE, F, 1, K, workers=min(8, max(2, (os.cpu_count() or 2) // max(1, world))), streams=2)
     req = runner.toggle_request(pop, x_d, y_d, banks_d, NB, 0, out, bank_stride=K, program_bank_stride=NB * K)

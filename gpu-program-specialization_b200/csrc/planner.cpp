@@ -11,7 +11,6 @@
 #include "evaluator.cuh"
 
 #include <algorithm>
-#include <cstdlib> /* DEV */
 
 namespace sb {
 
@@ -87,23 +86,20 @@ LaunchPlan plan_with_tile(const DeviceBatch& batch, const EvalProblem& prob, int
     /* Warps per CTA and rows per tile.  20 warps run at a 96-register budget; a tile of at least
      * 512 rows keeps the per-item set-up (program copy, toggle patches, bank part) small against
      * the row passes, so fewer warps are preferred over a smaller tile down to 256 rows. */
-    static uint32_t warp_list[] = {20, 16, 12, 8, 4, 2, 1, 0};
-    uint32_t dev_tr = 1024; /* DEV */
-    if (const char* e = std::getenv("SB_DEV_WARPS")) warp_list[0] = (uint32_t)std::atoi(e); /* DEV */
-    if (const char* e = std::getenv("SB_DEV_TR")) dev_tr = (uint32_t)std::atoi(e); /* DEV */
+    static const uint32_t warp_list[] = {20, 16, 12, 8, 4, 2, 1, 0};
+    const uint32_t widest_tile = 1024;
     const size_t rows_padded = (prob.num_rows + pass - 1) / pass * pass;
     const uint32_t floors[3] = {512u, 256u, pass};
     for (int attempt = 0; attempt < 3 && !plan.ok; ++attempt) {
         const size_t floor_rows = std::min<size_t>(std::max<uint32_t>(floors[attempt], pass), rows_padded);
         for (const uint32_t* w = warp_list; *w && !plan.ok; ++w) {
-            for (uint32_t want = dev_tr; want >= pass; want /= 2) {
+            for (uint32_t want = widest_tile; want >= pass; want /= 2) {
                 size_t tile_rows = std::min<size_t>(std::max<uint32_t>(want, pass) / pass * pass, rows_padded);
                 if (tile_rows < floor_rows) break;
                 LaunchPlan trial = plan;
                 trial.warps = *w;
                 trial.tile_rows = (uint32_t)tile_rows;
                 trial.tile_buffers = rows_padded > tile_rows ? 2u : 1u;
-                if (std::getenv("SB_DEV_SINGLE")) trial.tile_buffers = 1; /* DEV */
                 trial.num_groups = 1;
                 trial.row_splits = 1;
                 trial.rows_per_split = prob.num_rows;
@@ -124,7 +120,6 @@ LaunchPlan plan_with_tile(const DeviceBatch& batch, const EvalProblem& prob, int
      * cost and group g takes programs g, g + num_groups, ..., so every CTA's queue runs from its
      * costliest item to its cheapest and the warps reach the end of a tile close together. */
     unsigned long long want_items = 8ull * plan.warps;
-    if (const char* e = std::getenv("SB_DEV_ITEMS")) want_items = (unsigned long long)std::atoi(e) * plan.warps; /* DEV */
     unsigned long long per_cta = (want_items + items_per_program - 1) / items_per_program;
     per_cta = std::max<unsigned long long>(1, std::min<unsigned long long>(per_cta, P));
     unsigned long long groups = std::max<unsigned long long>(1, P / per_cta);
@@ -139,7 +134,6 @@ LaunchPlan plan_with_tile(const DeviceBatch& batch, const EvalProblem& prob, int
      * idle.  Each split keeps at least four tiles unless the program groups alone cannot fill the GPU. */
     const size_t tiles = (prob.num_rows + plan.tile_rows - 1) / plan.tile_rows;
     size_t want_ctas = (size_t)sm_count * 16;
-    if (const char* e = std::getenv("SB_DEV_CTAS")) want_ctas = (size_t)sm_count * (size_t)std::atoi(e); /* DEV */
     size_t most = groups >= (unsigned long long)sm_count * 2ull ? std::max<size_t>(1, tiles / 4) : tiles;
     size_t splits = std::min<size_t>(most, (want_ctas + (size_t)groups - 1) / (size_t)groups);
     splits = std::max<size_t>(1, splits);

@@ -210,7 +210,9 @@ class Population:
 
 # ---- device-side reductions over score grids (extension API) -----------------------------
 
-SCORE_BYTES = C.sizeof(abi.Score)
+from .sharding import SCORE_BYTES, record_fields as score_fields  # noqa: E402,F401  (the record layout lives with the combine step)
+
+assert SCORE_BYTES == C.sizeof(abi.Score)
 
 
 def best_config(scores, out=None):
@@ -225,14 +227,6 @@ def best_config(scores, out=None):
     abi.check(lib.secant_b200_best_config(flat.data_ptr(), flat.shape[0], flat.shape[1], flat.stride(0), out.data_ptr(),
                                           C.c_void_p(stream)), "secant_b200_best_config")
     return out
-
-
-def score_fields(records):
-    """(sse float32 view, configuration int64 view, valid int64 view) of a record buffer."""
-    n = records.numel() // SCORE_BYTES
-    sse = records.view(torch.float32).view(n, 6)[:, 0]
-    words = records.view(torch.int64).view(n, 3)
-    return sse, words[:, 1], words[:, 2]
 
 
 def topk(scores, k):

@@ -37,9 +37,9 @@ def test_two_gpu_shards_agree_with_single_process_oracle(tmp_path):
         mine = pop.subset(range(lo, hi))
         with R.Runner(abi.SHAPE_TOGGLE_SSE, 3, 1, K) as rn:
             grid = rn.toggle_sse(mine, torch.tensor(x, device=dev), torch.tensor(y, device=dev), torch.tensor(banks, device=dev), nb, 0)
-        best = R.score_fields(R.best_config(grid.view(hi - lo, nb)))[0].contiguous()
-        everyone = sharding.all_gather_scores(best, total, world)
-        top, _ = R.topk(everyone, 32)
+        combine = sharding.Combine(total, world, rank, 32, dev)       # the step the benchmark runs
+        top, records = combine(grid.view(hi - lo, nb))
+        everyone = sharding.record_fields(records)[0][combine.global_index >= 0]
         _, _, want64 = S.oracle_toggle_sse(pop, x, y, banks, K, 0)
         ref_best = np.where(np.isfinite(want64[:, 0, :]), want64[:, 0, :], np.inf).min(axis=1)
         order = sorted(range(total), key=lambda i: (ref_best[i], i))[:32]
