@@ -14,6 +14,25 @@
 namespace sb {
 /* adds to the process-wide count reported by secant_b200_kernel_launch_count() */
 void note_kernel_launches(unsigned n);
+
+/* Grouped top-k of a [system][configuration] score grid (reduce.cu); scratch may be zero. */
+SecantResult grouped_topk(uintptr_t scores, size_t num_systems, size_t num_banks, uint32_t toggle_bits, uint32_t grouping, uint32_t k,
+                          uintptr_t winners, uintptr_t counts, uintptr_t scratch, size_t scratch_bytes, cudaStream_t stream);
+
+/* Random pools and winner gathering of the ODE engine interface (pools.cu). */
+cudaError_t fill_pool(float* out, unsigned long long size, unsigned long long seed, unsigned long long stream_id,
+                      unsigned long long sample_base, bool normal, cudaStream_t stream);
+struct GatherProblem {
+    const SecantB200Winner* winners;
+    const float* banks;                          /* [system][bank][constant], or null when sampled */
+    const SecantB200SampledParameter* sampled;   /* [system][constant], or null */
+    const float* uniform_pool;
+    const float* normal_pool;
+    unsigned long long pool_size, entries, configurations, bank_count, score_count;
+    unsigned toggle_bits, constants;
+    float* rows;                                 /* [entry][constant] */
+};
+cudaError_t gather_constants(const GatherProblem& problem, cudaStream_t stream);
 }
 
 namespace sb {

@@ -19,6 +19,8 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 
+#include <algorithm>
+
 namespace {
 
 constexpr int kBestThreads = 128;
@@ -154,29 +156,25 @@ __device__ __forceinline__ unsigned long long group_flat_index(unsigned long lon
     return mode == 2 ? e : mode == 0 ? group * configs + e : (group / perms) * configs + e * perms + group % perms;
 }
 
-__global__ void __launch_bounds__(kGroupThreads)
-grouped_topk_kernel(const float* __restrict__ scores, unsigned long long elements, unsigned long long configs, unsigned long long perms,
-                    unsigned mode, unsigned k, SecantB200Winner* winners, SecantB200ScoreCounts* counts) {
-    __shared__ unsigned long long keys[kGroupKeys];
-    __shared__ unsigned long long tally[3];
-    const unsigned long long group = blockIdx.x;
-    const unsigned fresh = kGroupKeys - k; /* scores merged per round */
+/* Keeps the k smallest of n keys in keys[0..k), ascending.  Candidates arrive kGroupKeys - k at a
+ * time behind the current best k and the whole array is sorted; a batch in which nothing beats
+ * the current k-th key is dropped without sorting.  Keys are unique, so the result does not depend
+ * on how the candidates were batched or split over CTAs. */
+template <class Fetch>
+__device__ void select_smallest(unsigned long long* keys, unsigned k, unsigned long long n, Fetch& fetch) {
+    const unsigned fresh = kGroupKeys - k;
     for (int i = threadIdx.x; i < kGroupKeys; i += kGroupThreads) keys[i] = ~0ull;
-    if (threadIdx.x < 3) tally[threadIdx.x] = 0;
-    unsigned long long valid = 0, invalid = 0, negative = 0;
-    for (unsigned long long base = 0; base < elements; base += fresh) {
+    for (unsigned long long base = 0; base < n; base += fresh) {
         __syncthreads();
+        const unsigned long long bar = keys[k - 1];
+        int beats = 0;
         for (unsigned i = threadIdx.x; i < fresh; i += kGroupThreads) {
             const unsigned long long e = base + i;
-            unsigned long long key = ~0ull;
-            if (e < elements) {
-                const float f = scores[group_flat_index(group, e, configs, perms, mode)];
-                const bool ok = f >= 0.0f && f < 3.402823466e+38f;
-                if (ok) { ++valid; key = ((unsigned long long)__float_as_uint(f == 0.0f ? 0.0f : f) << 32) | (unsigned)e; }
-                else { ++invalid; negative += (f < 0.0f && f > -CUDART_INF_F) ? 1 : 0; }
-            }
+            const unsigned long long key = e < n ? fetch(e) : ~0ull;
             keys[k + i] = key;
+            beats |= key < bar;
         }
+        if (!__syncthreads_or(beats)) continue;
         for (unsigned size = 2; size <= kGroupKeys; size <<= 1)
             for (unsigned stride = size >> 1; stride > 0; stride >>= 1) {
                 __syncthreads();
@@ -188,8 +186,34 @@ grouped_topk_kernel(const float* __restrict__ scores, unsigned long long element
                 }
             }
     }
-    atomicAdd(&tally[0], valid); atomicAdd(&tally[1], invalid); atomicAdd(&tally[2], negative);
     __syncthreads();
+}
+
+struct RawScores { /* element of a group -> key, tallying validity on the way */
+    const float* scores;
+    unsigned long long group, first, configs, perms;
+    unsigned mode;
+    unsigned long long valid, invalid, negative;
+    __device__ unsigned long long operator()(unsigned long long e) {
+        const unsigned long long element = first + e;
+        const float f = scores[group_flat_index(group, element, configs, perms, mode)];
+        if (f >= 0.0f && f < 3.402823466e+38f) {
+            ++valid;
+            return ((unsigned long long)__float_as_uint(f == 0.0f ? 0.0f : f) << 32) | (unsigned)element;
+        }
+        ++invalid;
+        negative += (f < 0.0f && f > -CUDART_INF_F) ? 1 : 0;
+        return ~0ull;
+    }
+};
+
+struct StoredKeys {
+    const unsigned long long* keys;
+    __device__ unsigned long long operator()(unsigned long long e) const { return keys[e]; }
+};
+
+__device__ void emit_winners(const unsigned long long* keys, const float* scores, unsigned long long group, unsigned long long configs,
+                             unsigned long long perms, unsigned mode, unsigned k, SecantB200Winner* winners) {
     for (unsigned rank = threadIdx.x; rank < k; rank += kGroupThreads) {
         const unsigned long long key = keys[rank];
         SecantB200Winner w{3.402823466e+38f, 0u, ~0ull};
@@ -199,6 +223,53 @@ grouped_topk_kernel(const float* __restrict__ scores, unsigned long long element
         }
         winners[group * k + rank] = w;
     }
+}
+
+/* grid = groups x segments.  With one segment per group the CTA writes the group's winners and
+ * counts; otherwise its best k keys and its tallies go to part_keys / part_counts for the merge. */
+__global__ void __launch_bounds__(kGroupThreads)
+grouped_topk_kernel(const float* __restrict__ scores, unsigned long long elements, unsigned long long configs, unsigned long long perms,
+                    unsigned mode, unsigned k, unsigned segments, unsigned long long span, SecantB200Winner* winners,
+                    SecantB200ScoreCounts* counts, unsigned long long* part_keys, SecantB200ScoreCounts* part_counts) {
+    __shared__ unsigned long long keys[kGroupKeys];
+    __shared__ unsigned long long tally[3];
+    const unsigned long long group = blockIdx.x / segments;
+    const unsigned segment = blockIdx.x % segments;
+    const unsigned long long first = (unsigned long long)segment * span;
+    const unsigned long long n = first >= elements ? 0ull : (elements - first < span ? elements - first : span);
+    if (threadIdx.x < 3) tally[threadIdx.x] = 0;
+    RawScores fetch{scores, group, first, configs, perms, mode, 0ull, 0ull, 0ull};
+    select_smallest(keys, k, n, fetch);
+    atomicAdd(&tally[0], fetch.valid); atomicAdd(&tally[1], fetch.invalid); atomicAdd(&tally[2], fetch.negative);
+    __syncthreads();
+    if (segments == 1) {
+        emit_winners(keys, scores, group, configs, perms, mode, k, winners);
+        if (threadIdx.x == 0) counts[group] = SecantB200ScoreCounts{tally[0], tally[1], tally[2]};
+    } else {
+        for (unsigned rank = threadIdx.x; rank < k; rank += kGroupThreads) part_keys[(size_t)blockIdx.x * k + rank] = keys[rank];
+        if (threadIdx.x == 0) part_counts[blockIdx.x] = SecantB200ScoreCounts{tally[0], tally[1], tally[2]};
+    }
+}
+
+/* one CTA per group: the best k of its segments' keys, and the sum of their tallies */
+__global__ void __launch_bounds__(kGroupThreads)
+grouped_merge_kernel(const float* __restrict__ scores, unsigned long long configs, unsigned long long perms, unsigned mode, unsigned k,
+                     unsigned segments, const unsigned long long* __restrict__ part_keys, const SecantB200ScoreCounts* __restrict__ part_counts,
+                     SecantB200Winner* winners, SecantB200ScoreCounts* counts) {
+    __shared__ unsigned long long keys[kGroupKeys];
+    __shared__ unsigned long long tally[3];
+    const unsigned long long group = blockIdx.x;
+    if (threadIdx.x < 3) tally[threadIdx.x] = 0;
+    StoredKeys fetch{part_keys + (size_t)group * segments * k};
+    select_smallest(keys, k, (unsigned long long)segments * k, fetch);
+    unsigned long long valid = 0, invalid = 0, negative = 0;
+    for (unsigned s = threadIdx.x; s < segments; s += kGroupThreads) {
+        const SecantB200ScoreCounts c = part_counts[(size_t)group * segments + s];
+        valid += c.valid; invalid += c.invalid; negative += c.negative;
+    }
+    atomicAdd(&tally[0], valid); atomicAdd(&tally[1], invalid); atomicAdd(&tally[2], negative);
+    __syncthreads();
+    emit_winners(keys, scores, group, configs, perms, mode, k, winners);
     if (threadIdx.x == 0) counts[group] = SecantB200ScoreCounts{tally[0], tally[1], tally[2]};
 }
 
@@ -226,12 +297,13 @@ static cudaError_t topk_rounds(const float* scores, unsigned long long count, un
     return cudaGetLastError();
 }
 
-extern "C" {
-
-SecantResult secant_b200_grouped_topk(uintptr_t scores, size_t num_systems, size_t num_banks, uint32_t toggle_bits, uint32_t grouping,
-                                      uint32_t k, uintptr_t winners, uintptr_t counts, void* stream) {
-    if (!scores || !winners || !counts || scores % 4 || winners % 8 || counts % 8 || !num_systems || !num_banks || toggle_bits > 32 ||
-        grouping > SECANT_B200_GROUP_GLOBAL || !k || k > 256)
+/* Grouped top-k with an optional scratch area.  Large groups are cut into segments scored by
+ * separate CTAs when `scratch` (8-byte aligned device memory of scratch_bytes) has room for their
+ * partial results: segments x (k keys + one tally) per group; without it one CTA walks each group. */
+SecantResult sb::grouped_topk(uintptr_t scores, size_t num_systems, size_t num_banks, uint32_t toggle_bits, uint32_t grouping, uint32_t k,
+                              uintptr_t winners, uintptr_t counts, uintptr_t scratch, size_t scratch_bytes, cudaStream_t stream) {
+    if (!scores || !winners || !counts || scores % 4 || winners % 8 || counts % 8 || scratch % 8 || !num_systems || !num_banks ||
+        toggle_bits > 32 || grouping > SECANT_B200_GROUP_GLOBAL || !k || k > 256)
         return SECANT_ERROR_INVALID_VALUE;
     const unsigned long long perms = 1ull << toggle_bits;
     if (num_banks > (~0ull >> toggle_bits) || (num_banks << toggle_bits) > ~0ull / num_systems) return SECANT_ERROR_OVERFLOW;
@@ -241,11 +313,37 @@ SecantResult secant_b200_grouped_topk(uintptr_t scores, size_t num_systems, size
     else if (grouping == SECANT_B200_GROUP_BY_SYSTEM_PERMUTATION) { groups = num_systems * perms; elements = num_banks; }
     else { groups = 1; elements = configs * num_systems; }
     if (groups > 0x7fffffffull || elements > 0xffffffffull) return SECANT_ERROR_OVERFLOW; /* grid size, 32-bit key index */
-    grouped_topk_kernel<<<(unsigned)groups, kGroupThreads, 0, (cudaStream_t)stream>>>(
-        reinterpret_cast<const float*>(scores), elements, configs, perms, grouping, k, reinterpret_cast<SecantB200Winner*>(winners),
-        reinterpret_cast<SecantB200ScoreCounts*>(counts));
-    sb::note_kernel_launches(1);
+    /* segments: enough CTAs for four per SM, at least 4096 elements each, and no more than the scratch holds */
+    unsigned long long segments = 1;
+    if (scratch && groups < 592) {
+        segments = std::min<unsigned long long>((592 + groups - 1) / groups, (elements + 4095) / 4096);
+        const unsigned long long per_segment = (unsigned long long)k * 8 + sizeof(SecantB200ScoreCounts);
+        segments = std::min<unsigned long long>(segments, scratch_bytes / per_segment / groups);
+        if (segments < 2) segments = 1;
+    }
+    const unsigned long long span = (elements + segments - 1) / segments;
+    unsigned long long* part_keys = reinterpret_cast<unsigned long long*>(scratch);
+    SecantB200ScoreCounts* part_counts = reinterpret_cast<SecantB200ScoreCounts*>(part_keys + groups * segments * k);
+    const float* grid = reinterpret_cast<const float*>(scores);
+    grouped_topk_kernel<<<(unsigned)(groups * segments), kGroupThreads, 0, stream>>>(
+        grid, elements, configs, perms, grouping, k, (unsigned)segments, span, reinterpret_cast<SecantB200Winner*>(winners),
+        reinterpret_cast<SecantB200ScoreCounts*>(counts), part_keys, part_counts);
+    unsigned launched = 1;
+    if (segments > 1) {
+        grouped_merge_kernel<<<(unsigned)groups, kGroupThreads, 0, stream>>>(grid, configs, perms, grouping, k, (unsigned)segments, part_keys,
+                                                                             part_counts, reinterpret_cast<SecantB200Winner*>(winners),
+                                                                             reinterpret_cast<SecantB200ScoreCounts*>(counts));
+        ++launched;
+    }
+    sb::note_kernel_launches(launched);
     return cudaGetLastError() == cudaSuccess ? SECANT_SUCCESS : SECANT_ERROR_DRIVER_FAILED;
+}
+
+extern "C" {
+
+SecantResult secant_b200_grouped_topk(uintptr_t scores, size_t num_systems, size_t num_banks, uint32_t toggle_bits, uint32_t grouping,
+                                      uint32_t k, uintptr_t winners, uintptr_t counts, void* stream) {
+    return sb::grouped_topk(scores, num_systems, num_banks, toggle_bits, grouping, k, winners, counts, 0, 0, (cudaStream_t)stream);
 }
 
 size_t secant_b200_topk_scratch_elements(size_t count, size_t k) {
