@@ -201,40 +201,10 @@ struct Machine {
                 for (int g = 0; g < GROUPS; ++g)
                     *reinterpret_cast<float4*>(q + g * 128) = make_float4(acc[4 * g][0], acc[4 * g + 1][0], acc[4 * g + 2][0], acc[4 * g + 3][0]);
                 break; }
-#ifndef SB_MERGED_KINDS
             SB_BIN_CASES(SB_BIN_ADD)
             SB_BIN_CASES(SB_BIN_SUB)
             SB_BIN_CASES(SB_BIN_RSUB)
             SB_BIN_CASES(SB_BIN_MUL)
-#else
-            case SB_CASE_BIN + SB_BIN_ADD * SB_NUM_KINDS + 0: case SB_CASE_BIN + SB_BIN_ADD * SB_NUM_KINDS + 1: case SB_CASE_BIN + SB_BIN_ADD * SB_NUM_KINDS + 2:
-            case SB_CASE_BIN + SB_BIN_SUB * SB_NUM_KINDS + 0: case SB_CASE_BIN + SB_BIN_SUB * SB_NUM_KINDS + 1: case SB_CASE_BIN + SB_BIN_SUB * SB_NUM_KINDS + 2:
-            case SB_CASE_BIN + SB_BIN_RSUB * SB_NUM_KINDS + 0: case SB_CASE_BIN + SB_BIN_RSUB * SB_NUM_KINDS + 1: case SB_CASE_BIN + SB_BIN_RSUB * SB_NUM_KINDS + 2:
-            case SB_CASE_BIN + SB_BIN_MUL * SB_NUM_KINDS + 0: case SB_CASE_BIN + SB_BIN_MUL * SB_NUM_KINDS + 1: case SB_CASE_BIN + SB_BIN_MUL * SB_NUM_KINDS + 2:
-            case SB_CASE_BIN + SB_BIN_MIN * SB_NUM_KINDS + 0: case SB_CASE_BIN + SB_BIN_MIN * SB_NUM_KINDS + 1: case SB_CASE_BIN + SB_BIN_MIN * SB_NUM_KINDS + 2:
-            case SB_CASE_BIN + SB_BIN_MAX * SB_NUM_KINDS + 0: case SB_CASE_BIN + SB_BIN_MAX * SB_NUM_KINDS + 1: case SB_CASE_BIN + SB_BIN_MAX * SB_NUM_KINDS + 2: {
-                const unsigned rel = (ins.x & 0xffu) - SB_CASE_BIN;
-                const unsigned kind = rel % SB_NUM_KINDS;
-                float xv[RR][RC];
-                if (kind == SB_KIND_ROW) {
-                    float x[RR]; fetch_row(rowp, hrowp, tile_ld, idx, x);
-                    SB_FOR_TILE xv[r][c] = x[r];
-                } else if (kind == SB_KIND_CST) {
-                    float x[RC]; fetch_cst(cst, idx, x);
-                    SB_FOR_TILE xv[r][c] = x[c];
-                } else {
-                    fetch_slot(slots, idx, xv);
-                }
-                switch (rel / SB_NUM_KINDS) {
-                case SB_BIN_ADD: SB_FOR_TILE acc[r][c] = binop<SB_BIN_ADD>(acc[r][c], xv[r][c]); break;
-                case SB_BIN_SUB: SB_FOR_TILE acc[r][c] = binop<SB_BIN_SUB>(acc[r][c], xv[r][c]); break;
-                case SB_BIN_RSUB: SB_FOR_TILE acc[r][c] = binop<SB_BIN_RSUB>(acc[r][c], xv[r][c]); break;
-                case SB_BIN_MUL: SB_FOR_TILE acc[r][c] = binop<SB_BIN_MUL>(acc[r][c], xv[r][c]); break;
-                case SB_BIN_MIN: SB_FOR_TILE acc[r][c] = binop<SB_BIN_MIN>(acc[r][c], xv[r][c]); break;
-                default: SB_FOR_TILE acc[r][c] = binop<SB_BIN_MAX>(acc[r][c], xv[r][c]); break;
-                }
-                break; }
-#endif
             /* IEEE division is ~10 instructions per element: the six operand-kind cases
              * only expand the operand, then share one body per direction. */
             case SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS + SB_KIND_ROW:
@@ -274,10 +244,8 @@ struct Machine {
                     }
                 }
                 break; }
-#ifndef SB_MERGED_KINDS
             SB_BIN_CASES(SB_BIN_MIN)
             SB_BIN_CASES(SB_BIN_MAX)
-#endif
             SB_UN_CASE(SB_UN_NEG)
             SB_UN_CASE(SB_UN_ABS)
             case SB_CASE_UN + SB_UN_EX2: case SB_CASE_UN + SB_UN_EXP: case SB_CASE_UN + SB_UN_LOG:
