@@ -654,227 +654,6 @@ __global__ void combine_kernel(const DeviceBatch batch, const EvalProblem prob, 
     }
 }
 
-/* ---- RK4 rollout scoring ---------------------------------------------------------------
- * Restates the integration loop of the reference's generated scoring kernel
- * (projects/odezza/core/o_generate_scoring_cuda.c:494-588): per observation interval
- * h = interval / substeps; per substep base = stage = state, sum = 0, four stages with
- * sum = fma(w, rhs, sum) (w = 1,2,2,1), stage = fma(h/2 or h, rhs, base), then
- * state = fma(h/6, sum, base); after every interval all states must be finite and
- * sq = fma(err, err, sq).  Score = sq / residuals, or FLT_MAX when anything was not finite.
- *
- * Mapping (different from the reference, which gives a thread one configuration and loops all
- * trajectories inside it): one warp per (system, configuration), lanes = trajectories, four
- * per lane.  The integrator's vectors live in the warp's spill slots: slot s = stage state s
- * (what COLUMN s of a right-hand side reads), then next-stage, sum and state vectors (the state
- * is not touched during a step, so it doubles as the step's base).  Warps per CTA are chosen at
- * launch so that as many warps as possible fit the SM's shared memory. */
-constexpr int kRk4MaxWarps = 16;
-
-/* projects/odezza/core/o_sampled_constants_source.h:32-44 */
-__device__ __forceinline__ float sampled_constant(const Rk4Problem& prob, unsigned long long index, uint32_t bank) {
-    const SecantB200SampledParameter p = prob.sampled[index];
-    if (!p.distribution) return p.shift;
-    const unsigned long long delta = (unsigned long long)bank * p.stride;
-    if (p.offset >= prob.pool_size || delta >= prob.pool_size - p.offset) return __int_as_float(0x7fc00000);
-    const float* pool = p.distribution == 1 ? prob.uniform_pool : p.distribution == 2 ? prob.normal_pool : nullptr;
-    if (!pool) return __int_as_float(0x7fc00000);
-    const float value = __fadd_rn(__fmul_rn(pool[p.offset + delta], p.scale), p.shift);
-    return fminf(p.upper, fmaxf(p.lower, value));
-}
-
-__global__ void __launch_bounds__(kRk4MaxWarps * 32, 1)
-rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, uint32_t cst_bytes, uint32_t warp_bytes,
-           uint32_t scratch_slot) {
-    using M = Machine<4, 1>;
-    extern __shared__ __align__(16) unsigned char smem[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t S = prob.num_states, K = prob.num_constants;
-    unsigned char* const warea = smem + (size_t)warp * warp_bytes;
-    float4* const slots = reinterpret_cast<float4*>(warea + (size_t)S * (exec_bytes + cst_bytes)) + lane;
-    const unsigned long long configs = (unsigned long long)prob.num_banks << prob.toggle_bits;
-    const unsigned long long item = (unsigned long long)blockIdx.x * (blockDim.x >> 5) + warp;
-    if (item >= configs * prob.num_systems) return;
-    const uint32_t sys = (uint32_t)(item / configs);
-    const unsigned long long cfg = item % configs;
-    const unsigned long long perm = cfg & ((1ull << prob.toggle_bits) - 1ull);
-    const uint32_t bank = (uint32_t)(cfg >> prob.toggle_bits);
-    const float* bank_ptr = prob.banks ? prob.banks + (size_t)sys * prob.system_bank_stride + (size_t)bank * prob.bank_stride : nullptr;
-
-    for (uint32_t s = 0; s < S; ++s) { /* private copy of every right-hand side, toggles resolved, constants staged */
-        const SbProgram pr = batch.programs[sys * S + s];
-        SbInsn* exec = reinterpret_cast<SbInsn*>(warea + (size_t)s * exec_bytes);
-        float* cst = reinterpret_cast<float*>(warea + (size_t)S * exec_bytes + (size_t)s * cst_bytes);
-        for (uint32_t i = lane; i < pr.n_insn; i += 32) exec[i] = batch.insns[pr.insn_off + i];
-        if (lane == 0) exec[pr.n_insn] = SbInsn{0u, 0u};
-        __syncwarp();
-        for (uint32_t i = lane; i < pr.n_patch; i += 32) {
-            const SbPatch* p = batch.patches + pr.patch_off + i;
-            unsigned choice = (unsigned)(perm >> p->bit0) & 1u;
-            if (p->bit1 != 0xffu) choice |= ((unsigned)(perm >> p->bit1) & 1u) << 1;
-            exec[p->insn] = p->alt[choice];
-        }
-        for (uint32_t e = lane; e < K + pr.n_affine + pr.n_lits; e += 32) {
-            float v;
-            if (e < K) v = prob.sampled ? sampled_constant(prob, (unsigned long long)sys * K + e, bank) : bank_ptr[e];
-            else if (e < K + pr.n_affine) {
-                const SbAffine a = batch.affines[pr.affine_off + e - K];
-                const float slot = prob.sampled ? sampled_constant(prob, (unsigned long long)sys * K + a.slot, bank) : bank_ptr[a.slot];
-                v = __fadd_rn(__fmul_rn(slot, a.scale), a.offset);
-            } else v = batch.lits[pr.lit_off + e - K - pr.n_affine];
-            cst[e] = v;
-        }
-    }
-    __syncwarp();
-
-    const uint32_t STAGE = 0, NEXT = S, SUM = 2 * S, STATE = 3 * S, BASE = STATE;
-    const bool ragged = prob.offsets != nullptr;
-    M m;
-    float sq = 0.0f;
-    unsigned long long residuals = 0;
-    /* any non-finite time or reference value (NaN excepted where it means "unobserved"), found
-     * by the validation kernel, invalidates every score; so do offsets that do not span the data */
-    bool ok = *prob.invalid_flag == 0;
-    if (ragged) ok = ok && prob.offsets[0] == 0u && prob.offsets[prob.num_trajectories] == prob.total_points;
-    for (uint32_t t0 = 0; t0 < prob.num_trajectories; t0 += 128) {
-        uint32_t begin[4], npts[4], longest = 0;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const uint32_t traj = t0 + lane * 4 + q;
-            const bool live = traj < prob.num_trajectories;
-            begin[q] = 0; npts[q] = 0;
-            if (live && ragged) {
-                const uint32_t b = prob.offsets[traj], e = prob.offsets[traj + 1];
-                const bool sane = e > b && e <= prob.total_points;
-                ok = ok && sane;
-                if (sane) { begin[q] = b; npts[q] = e - b; }
-            } else if (live) {
-                begin[q] = traj * prob.points_per_trajectory; npts[q] = prob.points_per_trajectory;
-            }
-            longest = max(longest, npts[q]);
-        }
-#pragma unroll
-        for (int d = 16; d; d >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, d));
-        for (uint32_t s = 0; s < S; ++s) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float v = npts[q] ? prob.reference[(size_t)s * prob.reference_ld + begin[q]] : 0.0f;
-                ok = ok && (fabsf(v) <= 3.402823466e+38f); /* initial states must be complete and finite */
-                m.acc[q][0] = v;
-            }
-            m.store_slot(slots, STATE + s);
-        }
-        for (uint32_t k = 1; k < longest; ++k) {
-            /* per trajectory step size; a trajectory that has ended keeps integrating with h = 0
-             * and is left out of every check and sum */
-            float h[4], sixth[4];
-            bool act[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                act[q] = k < npts[q];
-                const uint32_t at = ragged ? begin[q] + k : k;
-                const float interval = act[q] ? prob.times[at] - prob.times[at - 1] : 0.0f;
-                const float step = interval / (float)prob.substeps;
-                ok = ok && (!act[q] || ((fabsf(interval) <= 3.402823466e+38f) && interval > 0.0f && step > 0.0f));
-                h[q] = act[q] ? step : 0.0f;
-                sixth[q] = h[q] / 6.0f;
-            }
-            for (uint32_t sub = 0; sub < prob.substeps; ++sub) {
-                for (uint32_t s = 0; s < S; ++s) {
-                    m.fetch_slot(slots, STATE + s, m.acc);
-                    m.store_slot(slots, STAGE + s);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) m.acc[q][0] = 0.0f;
-                    m.store_slot(slots, SUM + s);
-                }
-#pragma unroll 1
-                for (int stage = 0; stage < 4; ++stage) {
-                    const float weight = (stage == 0 || stage == 3) ? 1.0f : 2.0f;
-                    for (uint32_t s = 0; s < S; ++s) {
-                        const SbInsn* exec = reinterpret_cast<const SbInsn*>(warea + (size_t)s * exec_bytes);
-                        const float* cst = reinterpret_cast<const float*>(warea + (size_t)S * exec_bytes + (size_t)s * cst_bytes);
-                        m.run(exec, nullptr, 0, cst, slots, scratch_slot); /* acc = rhs of state s at the stage values */
-                        float rhs[4], v[4][1];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) rhs[q] = m.acc[q][0];
-                        m.fetch_slot(slots, SUM + s, v);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) m.acc[q][0] = __fmaf_rn(weight, rhs[q], v[q][0]);
-                        m.store_slot(slots, SUM + s);
-                        if (stage != 3) {
-                            m.fetch_slot(slots, BASE + s, v);
-#pragma unroll
-                            for (int q = 0; q < 4; ++q)
-                                m.acc[q][0] = __fmaf_rn(stage == 2 ? h[q] : __fmul_rn(0.5f, h[q]), rhs[q], v[q][0]);
-                            m.store_slot(slots, NEXT + s);
-                        }
-                    }
-                    if (stage != 3)
-                        for (uint32_t s = 0; s < S; ++s) {
-                            m.fetch_slot(slots, NEXT + s, m.acc);
-                            m.store_slot(slots, STAGE + s);
-                        }
-                }
-                for (uint32_t s = 0; s < S; ++s) {
-                    float sum[4][1], base[4][1];
-                    m.fetch_slot(slots, SUM + s, sum);
-                    m.fetch_slot(slots, BASE + s, base);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) m.acc[q][0] = __fmaf_rn(sixth[q], sum[q][0], base[q][0]);
-                    m.store_slot(slots, STATE + s);
-                }
-            }
-            for (uint32_t s = 0; s < S; ++s) { /* all states must be finite before any residual counts */
-                m.fetch_slot(slots, STATE + s, m.acc);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) ok = ok && (!act[q] || fabsf(m.acc[q][0]) <= 3.402823466e+38f);
-            }
-            for (uint32_t s = 0; s < S; ++s) {
-                m.fetch_slot(slots, STATE + s, m.acc);
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    if (act[q]) {
-                        const float ref = prob.reference[(size_t)s * prob.reference_ld + begin[q] + k];
-                        if (prob.allow_missing && ref != ref) continue; /* unobserved */
-                        const float err = __fsub_rn(m.acc[q][0], ref);
-                        sq = __fmaf_rn(err, err, sq);
-                        ++residuals;
-                    }
-            }
-        }
-    }
-    const float total = warp_sum(sq);
-    uint32_t lo = (uint32_t)residuals, hi = (uint32_t)(residuals >> 32);
-#pragma unroll
-    for (int d = 16; d; d >>= 1) {
-        const unsigned long long other = ((unsigned long long)__shfl_xor_sync(0xffffffffu, hi, d) << 32) | __shfl_xor_sync(0xffffffffu, lo, d);
-        residuals += other;
-        lo = (uint32_t)residuals; hi = (uint32_t)(residuals >> 32);
-    }
-    const bool all_ok = __all_sync(0xffffffffu, ok);
-    if (lane == 0) {
-        const bool finite = fabsf(total) <= 3.402823466e+38f;
-        prob.output[(size_t)sys * prob.output_ld + cfg] = (all_ok && residuals && finite) ? total / (float)residuals : 3.402823466e+38f;
-    }
-}
-
-/* Raises *flag when a time or a reference value of an active state is not finite; NaN reference
- * values are tolerated when they mean "unobserved" (initial points are checked by the scorer). */
-__global__ void rk4_validate_kernel(const Rk4Problem prob) {
-    const size_t n = (size_t)prob.total_points * (prob.num_states + 1);
-    bool bad = false;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t row = i / prob.total_points, col = i % prob.total_points;
-        if (row == prob.num_states) {
-            if (!prob.offsets && col >= prob.points_per_trajectory) continue; /* uniform form: one shared time axis */
-            bad = bad || !(fabsf(prob.times[col]) <= 3.402823466e+38f);
-        } else {
-            const float v = prob.reference[row * prob.reference_ld + col];
-            bad = bad || !((fabsf(v) <= 3.402823466e+38f) || (prob.allow_missing && v != v));
-        }
-    }
-    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(prob.invalid_flag, 1);
-}
-
 template <int RR, int RC>
 cudaError_t launch_variant(const DeviceBatch& batch, const EvalProblem& prob, const Geom& geom, const LaunchPlan& plan,
                            float* partial, cudaStream_t stream) {
@@ -902,34 +681,6 @@ cudaError_t configure_kernels() {
     SB_FOR_VARIANTS(SB_CONFIGURE)
 #undef SB_CONFIGURE
     return cudaSuccess;
-}
-
-cudaError_t launch_rk4(const DeviceBatch& batch, const Rk4Problem& prob, size_t smem_limit, cudaStream_t stream) {
-    const uint32_t exec_bytes = round16(((size_t)batch.max_insn + 1) * sizeof(SbInsn));
-    const uint32_t cst_bytes = round16(((size_t)prob.num_constants + batch.max_extra) * 4 + 16);
-    const uint32_t scratch_slot = batch.max_slots; /* max_slots already includes the integrator's reserved slots */
-    const uint32_t warp_bytes = prob.num_states * (exec_bytes + cst_bytes) + (batch.max_slots + 1u) * 4u * 128u;
-    /* warps per CTA: the count that puts most warps on an SM (shared memory per SM is the CTA
-     * limit plus 1 KB reserved per resident CTA; the register file holds about 24 warps) */
-    int warps = 0, best = 0;
-    for (int w = 2; w <= kRk4MaxWarps; ++w) {
-        const size_t cta = (size_t)warp_bytes * w;
-        if (cta > smem_limit) break;
-        int ctas = (int)((smem_limit + 1024) / (cta + 1024));
-        if (ctas * w > 24) ctas = 24 / w; /* registers: about 80 per thread */
-        if (ctas * w >= best) { best = ctas * w; warps = w; }
-    }
-    if (!warps) return cudaErrorInvalidConfiguration;
-    const size_t smem = (size_t)warp_bytes * warps;
-    cudaError_t e = cudaFuncSetAttribute(rk4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
-    if (e != cudaSuccess) return e;
-    const unsigned long long items = ((unsigned long long)prob.num_banks << prob.toggle_bits) * prob.num_systems;
-    const unsigned long long blocks = (items + warps - 1) / warps;
-    if (blocks > 0x7fffffffull) return cudaErrorInvalidConfiguration;
-    const size_t values = (size_t)prob.total_points * (prob.num_states + 1);
-    rk4_validate_kernel<<<(unsigned)std::min<size_t>(1024, (values + 255) / 256), 256, 0, stream>>>(prob);
-    rk4_kernel<<<(unsigned)blocks, warps * 32, smem, stream>>>(batch, prob, exec_bytes, cst_bytes, warp_bytes, scratch_slot);
-    return cudaGetLastError();
 }
 
 cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPlan& plan, float* partial,

@@ -154,6 +154,8 @@ struct Rk4Problem {
     unsigned long long pool_size;
     float* output;                 /* [system][configuration] */
     size_t output_ld;
+    unsigned long long* queue;      /* device counter, zero at launch: the next item to be taken */
+    unsigned long long* integrated; /* optional device counter: (trajectory, observation interval) pairs integrated */
 };
 /* batch.programs holds num_systems * num_states records, system-major, encoded with
  * columns_are_slots and 5 * num_states reserved slots. */

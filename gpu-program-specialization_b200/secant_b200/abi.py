@@ -144,7 +144,7 @@ class Rk4Run(C.Structure):  # SecantB200Rk4Run
                 ("times", C.c_size_t), ("steps_per_observation", _sz), ("output", DeviceMatrix),
                 ("trajectory_offsets", C.c_size_t), ("total_points", _sz), ("allow_missing_observations", _u32),
                 ("reserved3", _u32), ("sampled_parameters", C.c_size_t), ("uniform_pool", C.c_size_t),
-                ("normal_pool", C.c_size_t), ("rng_pool_size", C.c_uint64)]
+                ("normal_pool", C.c_size_t), ("rng_pool_size", C.c_uint64), ("integrated_intervals", C.c_size_t)]
 
 
 class SampledParameter(C.Structure):  # SecantB200SampledParameter, layout of the reference's OdezzaSampledParameter

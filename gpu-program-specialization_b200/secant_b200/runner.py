@@ -243,7 +243,8 @@ def topk(scores, k):
 
 
 def rk4_score(packed, num_states, reference, times, constants=None, num_constants=0, num_banks=1, toggle_bits=0,
-              steps_per_observation=1, points_per_trajectory=None, offsets=None, allow_missing=False, sampled=None):
+              steps_per_observation=1, points_per_trajectory=None, offsets=None, allow_missing=False, sampled=None,
+              integrated=None):
     """Fixed-step RK4 rollout scores [system][configuration] (extension API).
 
     packed: num_systems * num_states right-hand-side programs, system-major.
@@ -253,7 +254,9 @@ def rk4_score(packed, num_states, reference, times, constants=None, num_constant
     reference values after a trajectory's first point are unobserved.
     constants: CUDA tensor [system][bank][slot] or None.
     sampled: (descriptors, uniform_pool, normal_pool) instead of constants - a CUDA uint8 tensor
-    holding abi.SampledParameter[system][constant] and two CUDA float pools of equal size."""
+    holding abi.SampledParameter[system][constant] and two CUDA float pools of equal size.
+    integrated: optional CUDA int64 tensor of one element, incremented by the (trajectory, observation
+    interval) pairs that were integrated (candidates that are already invalid are not integrated on)."""
     lib = abi.load()
     run = abi.Rk4Run()
     run.struct_size, run.version = C.sizeof(run), abi.RUN_VERSION
@@ -281,6 +284,8 @@ def rk4_score(packed, num_states, reference, times, constants=None, num_constant
         run.rng_pool_size = uniform_pool.numel()
     run.times = times.data_ptr()
     run.steps_per_observation = steps_per_observation
+    if integrated is not None:
+        run.integrated_intervals = integrated.data_ptr()
     out = torch.empty((systems, num_banks << toggle_bits), dtype=torch.float32, device=reference.device)
     run.output = _matrix(out)
     abi.check(lib.secant_b200_rk4_score(C.byref(run)), "secant_b200_rk4_score")

@@ -123,7 +123,10 @@ SECANT_DEC SecantResult secant_b200_runner_set_scratch_limit(SecantCubinRunner r
  * unobserved value: it is skipped, and the mean divides by the values that were observed.
  *   constants   [system][bank][slot]; system_bank_stride 0 = num_banks * bank_stride
  *   output      [system][configuration], configuration = bank * 2^toggle_bits + permutation
- * Blocking; uses the current CUDA device and context.  Transcendental opcodes are allowed in
+ * Blocking; uses the current CUDA device and context; runs on the call's own streams, ordered after
+ * the work the caller has queued on the default stream.  Programs are validated before anything is
+ * launched; a structural error found later, while a chunk of systems is being encoded, ends the call
+ * with its code after earlier chunks may have written their scores.  Transcendental opcodes are allowed in
  * right-hand sides, but only exactly rounded operations (add, sub, mul, div, fma, sqrt, neg,
  * abs, min, max) reproduce a host rollout bit for bit, which chaotic systems need.
  */
@@ -159,6 +162,11 @@ typedef struct SecantB200Rk4Run {
      * `constants` is then unused and may be zero; the pools hold rng_pool_size floats each */
     uintptr_t sampled_parameters, uniform_pool, normal_pool;
     uint64_t rng_pool_size;
+    /* optional device uint64 (8-byte aligned), incremented by the number of (trajectory, observation
+     * interval) pairs that were integrated.  A candidate whose score is already FLT_MAX (a state or a
+     * step became non-finite) is not integrated further, so this is what the call actually computed;
+     * the full count is num_systems * configurations * scored points. */
+    uintptr_t integrated_intervals;
 } SecantB200Rk4Run;
 SECANT_DEC SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run);
 
