@@ -247,8 +247,9 @@ struct Operand {
     unsigned index;
 };
 
-/* The three instruction runs of a record. */
-enum Run { RUN_BANK = 0, RUN_ROW = 1, RUN_MAIN = 2 };
+/* The instruction runs of a record.  The row prelude comes in two runs: values no toggle can change,
+ * which an item that covers several permutations computes once, and values a toggle reaches. */
+enum Run { RUN_BANK = 0, RUN_SHARED = 1, RUN_ROW = 2, RUN_MAIN = 3, NUM_RUNS = 4 };
 
 /* rough executed-instruction weights used for scheduling (SbProgram::cost) and for choosing
  * which row-only sub-expressions are worth a hoist slot */
@@ -280,8 +281,8 @@ struct Emitter {
     EncodedBatch& out;
     size_t lit_base;
     unsigned n_affine;
-    std::vector<SbInsn> code[3];
-    std::vector<SbPatch> sites[3]; /* SbPatch::insn is relative to the run until the record is assembled */
+    std::vector<SbInsn> code[NUM_RUNS];
+    std::vector<SbPatch> sites[NUM_RUNS]; /* SbPatch::insn is relative to the run until the record is assembled */
     Run run = RUN_MAIN;
     std::vector<uint8_t> slot_busy;
     unsigned slots_high = 0, btmp_high = 0;
@@ -344,6 +345,26 @@ struct Emitter {
             inside_row = true;
         }
         for (unsigned i = 0; i < arity_of(n); ++i) collect(nodes[id].child[i], inside_row, bank_roots, row_roots, seen);
+    }
+
+    /* whether a toggle lies anywhere below the node: such a value changes with the permutation */
+    bool reaches_toggle(int id, std::vector<int8_t>& memo) {
+        if (memo[(size_t)id] >= 0) return memo[(size_t)id] != 0;
+        const Node& n = nodes[id];
+        bool any = n.type == N_TOGGLE;
+        for (unsigned i = 0; i < arity_of(n) && !any; ++i) any = reaches_toggle(nodes[id].child[i], memo);
+        memo[(size_t)id] = any ? 1 : 0;
+        return any;
+    }
+    /* maximal computed row-only nodes below `id` that no toggle reaches */
+    void collect_shared(int id, std::vector<int>& shared, std::vector<int8_t>& memo) {
+        const Node& n = nodes[id];
+        if (leaf_type(n)) return;
+        if (classify(id) == VC_ROW && !reaches_toggle(id, memo)) {
+            if (std::find(shared.begin(), shared.end(), id) == shared.end()) shared.push_back(id);
+            return;
+        }
+        for (unsigned i = 0; i < arity_of(n); ++i) collect_shared(nodes[id].child[i], shared, memo);
     }
 
     int alloc_slot() {
@@ -655,14 +676,28 @@ SecantResult encode_program(const SecantAstInstruction* program, const SecantAst
         std::vector<int> bank_roots, row_roots;
         std::vector<uint8_t> seen(nodes.size(), 0);
         em.collect(root, false, bank_roots, row_roots, seen);
-        /* keep the costliest row-only expressions when there are more than the kernel has room for */
-        std::stable_sort(row_roots.begin(), row_roots.end(), [&](int a, int b) { return nodes[a].weight > nodes[b].weight; });
-        if (row_roots.size() > rules.max_hoisted) row_roots.resize(rules.max_hoisted);
+        /* row-only expressions a toggle reaches change with the permutation; what lies below them and
+         * does not is worth a value of its own, computed once for all permutations of an item */
+        std::vector<int8_t> memo(nodes.size(), -1);
+        std::vector<int> shared_roots, toggled_roots;
+        for (int id : row_roots) {
+            if (!em.reaches_toggle(id, memo)) { shared_roots.push_back(id); continue; }
+            if (rules.hoist_toggled) toggled_roots.push_back(id);
+            em.collect_shared(id, shared_roots, memo);
+        }
+        /* keep the costliest values when there are more than the kernel has room for */
+        std::vector<int> chosen(shared_roots);
+        chosen.insert(chosen.end(), toggled_roots.begin(), toggled_roots.end());
+        std::stable_sort(chosen.begin(), chosen.end(), [&](int a, int b) { return nodes[a].weight > nodes[b].weight; });
+        if (chosen.size() > rules.max_hoisted) chosen.resize(rules.max_hoisted);
         /* operands before the expressions that use them: children were created first */
         std::sort(bank_roots.begin(), bank_roots.end());
-        std::sort(row_roots.begin(), row_roots.end());
+        std::sort(chosen.begin(), chosen.end());
         for (int id : bank_roots) em.hoist(RUN_BANK, id);
-        for (int id : row_roots) em.hoist(RUN_ROW, id);
+        for (int id : chosen)
+            if (!em.reaches_toggle(id, memo)) em.hoist(RUN_SHARED, id);
+        for (int id : chosen)
+            if (em.reaches_toggle(id, memo)) em.hoist(RUN_ROW, id);
         if (em.error != SECANT_SUCCESS) return em.error;
     }
     em.begin_phase(RUN_MAIN, root); /* counts the RETURN as the root's first use */
@@ -670,17 +705,18 @@ SecantResult encode_program(const SecantAstInstruction* program, const SecantAst
     if (em.error != SECANT_SUCCESS) return em.error;
     em.consume(root);
 
-    /* assemble: bank part | row prelude | main part, each closed by END; patch sites become
-     * positions inside the whole record */
-    size_t offset[3] = {0, 0, 0}, total = 0;
-    for (int k = 0; k < 3; ++k) {
+    /* assemble: bank part | shared row prelude | row prelude | main part, each closed by END; patch
+     * sites become positions inside the whole record */
+    size_t offset[NUM_RUNS] = {0, 0, 0, 0}, total = 0;
+    for (int k = 0; k < NUM_RUNS; ++k) {
         offset[k] = total;
         if (k == RUN_MAIN || !em.code[k].empty()) total += em.code[k].size() + 1;
     }
     uint64_t cost = 0, pre_cost = 0;
     for (const SbInsn& i : em.code[RUN_MAIN]) cost += (uint64_t)insn_weight(i);
+    for (const SbInsn& i : em.code[RUN_SHARED]) pre_cost += (uint64_t)insn_weight(i);
     for (const SbInsn& i : em.code[RUN_ROW]) pre_cost += (uint64_t)insn_weight(i);
-    for (int k = 0; k < 3; ++k) {
+    for (int k = 0; k < NUM_RUNS; ++k) {
         if (k != RUN_MAIN && em.code[k].empty()) continue;
         out.insns.insert(out.insns.end(), em.code[k].begin(), em.code[k].end());
         out.insns.push_back(SbInsn{sb_w0(SB_CASE_END, 0, 0), 0});
@@ -704,7 +740,8 @@ SecantResult encode_program(const SecantAstInstruction* program, const SecantAst
     rec.n_lits = (uint16_t)n_lits;
     rec.n_slots = (uint16_t)em.slots_high;
     rec.n_ops = (uint16_t)(parser.n_ops > 0xffffu ? 0xffffu : parser.n_ops);
-    rec.pre_off = (uint16_t)offset[RUN_ROW];
+    rec.pre_off = (uint16_t)offset[RUN_SHARED];
+    rec.mid_off = (uint16_t)offset[RUN_ROW];
     rec.main_off = (uint16_t)offset[RUN_MAIN];
     rec.n_hoisted = (uint16_t)em.n_hoisted;
     rec.n_cst = (uint16_t)em.n_entries;

@@ -41,6 +41,10 @@ struct ProgramRules {
      * operands, only less often. */
     bool hoist_bank = false;
     bool hoist_row = false;
+    /* hoist_toggled: row-only sub-expressions that a toggle reaches get a prelude value as well (one
+     * per permutation: worth it when a permutation is evaluated for several bank groups); without
+     * it only what no toggle reaches is hoisted, which an item shares among its permutations. */
+    bool hoist_toggled = true;
     unsigned max_hoisted = 4;
 };
 

@@ -462,12 +462,15 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
     const uint32_t T = prob.num_targets;
     const uint32_t nq = prob.mode == EVAL_AFFINE_STATS ? T + 2 : T;
     const uint32_t gpi = geom.groups_per_item;
+    const uint32_t ppi = materialize ? 1u : geom.perms_per_item;
+    const uint32_t wide = ppi * gpi; /* (permutation, bank group) pairs of an item: the partial sums' middle dimension */
     /* configuration groups of one program: permutation-major, RC banks per group */
     const uint32_t bank_groups = materialize ? 1u : (prob.num_banks + RC - 1) / RC;
-    /* items of one program: permutation-major, `chunks` items of gpi bank groups per permutation;
-     * the planner keeps items_per_program * prog_count below 2^32 - 256, so item arithmetic is 32-bit */
+    /* items of one program: permutation-major, `chunks` items of gpi bank groups per permutation, or
+     * (when one item holds every bank group) one item per block of ppi permutations; the planner keeps
+     * items_per_program * prog_count below 2^32 - 256, so item arithmetic is 32-bit */
     const uint32_t chunks = materialize ? 1u : bank_groups / gpi;
-    const uint32_t items_per_program = materialize ? 1u : (uint32_t)((unsigned long long)chunks << prob.toggle_bits);
+    const uint32_t items_per_program = materialize ? 1u : (uint32_t)(((unsigned long long)chunks << prob.toggle_bits) / ppi);
     const unsigned int num_items = items_per_program * prog_count;
     const unsigned long long configs = (unsigned long long)prob.num_banks << prob.toggle_bits;
     const size_t tile_floats = geom.tile_bytes / 4;
@@ -504,7 +507,7 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
             const uint32_t pi = item / items_per_program, within = item - pi * items_per_program;
             const uint32_t lp = group + pi * geom.num_groups;                        /* index inside the batch */
             const SbProgram* const hp = batch.programs + lp;
-            const uint32_t n_insn = hp->n_insn, pre_off = hp->pre_off, main_off = hp->main_off, n_cst = hp->n_cst;
+            const uint32_t n_insn = hp->n_insn, pre_off = hp->pre_off, mid_off = hp->mid_off, main_off = hp->main_off, n_cst = hp->n_cst;
             const uint32_t n_patch = hp->n_patch, flags = hp->flags;
             __syncwarp(); /* the previous item's reads of exec, table and psum are done */
             {
@@ -512,38 +515,46 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
                 for (uint32_t i = lane; i < n_insn; i += 32) exec[i] = code[i];
                 if (lane == 0) exec[n_insn] = SbInsn{0u, 0u}; /* padding read by the instruction prefetch */
             }
-            /* an item never straddles permutations: toggles are patched once per item */
-            const uint32_t perm = materialize ? prob.fixed_permutation : within / chunks;
-            const uint32_t first_bg = materialize ? 0u : (within - perm * chunks) * gpi;
+            /* the item's permutations perm0 .. perm0 + ppi - 1 (one, unless the item holds every bank group) */
+            const uint32_t block = materialize ? 0u : within / chunks;
+            const uint32_t perm0 = materialize ? prob.fixed_permutation : block * ppi;
+            const uint32_t first_bg = materialize ? 0u : (within - block * chunks) * gpi;
             const uint32_t ngroups = materialize ? 1u : min(gpi, bank_groups - first_bg);
-            if (n_patch) {
-                __syncwarp(); /* the copy above and the patches below touch the same words from different lanes */
-                const SbPatch* patches = batch.patches + hp->patch_off;
+            const SbPatch* const patches = batch.patches + hp->patch_off;
+            /* rewrites the toggle sites of the warp's copy for one permutation */
+            auto patch_for = [&](uint32_t perm) {
+                __syncwarp(); /* earlier reads and writes of the copy by other lanes are done */
                 for (uint32_t i = lane; i < n_patch; i += 32) {
                     const SbPatch* p = patches + i;
                     unsigned choice = (perm >> p->bit0) & 1u;
                     if (p->bit1 != 0xffu) choice |= ((perm >> p->bit1) & 1u) << 1;
                     exec[p->insn] = p->alt[choice];
                 }
-            }
-            for (uint32_t e = lane; e < nq * gpi * RC; e += 32) psum[e] = 0.0f;
-            __syncwarp();
-            const size_t gp = prob.first_program + hp->index; /* position in the run: output row, bank table */
-            if (pre_off) {
-                BankSource src;
-                src.banks = prob.banks ? prob.banks + gp * prob.program_bank_stride : nullptr;
-                src.bank_stride = prob.bank_stride;
-                src.num_banks = prob.banks ? prob.num_banks : 0u; /* without a table every bank constant reads zero */
-                src.K = prob.num_constants;
-                src.n_affine = hp->n_affine;
-                src.affines = batch.affines + hp->affine_off;
-                src.lits = batch.lits + hp->lit_off;
-                run_bank_part<RC, FAST>(exec, first_bg * RC, ngroups * RC, n_cst, table, slot_base, src, lane);
                 __syncwarp();
-            }
-            const bool has_prelude = main_off > pre_off;
-            const uint32_t eval_groups = (flags & SB_PROG_BANK_INDEPENDENT) ? 1u : ngroups;
+            };
+            for (uint32_t e = lane; e < nq * wide * RC; e += 32) psum[e] = 0.0f;
+            const size_t gp = prob.first_program + hp->index; /* position in the run: output row, bank table */
             const uint32_t table_stride = n_cst * RC;
+            /* the constant tables of every permutation of the item; an item of one permutation stays
+             * patched for it, the others are patched again inside the row passes */
+            for (uint32_t j = 0; j < ((pre_off || ppi == 1u) ? ppi : 0u); ++j) {
+                if (n_patch) patch_for(perm0 + j);
+                if (pre_off) {
+                    BankSource src;
+                    src.banks = prob.banks ? prob.banks + gp * prob.program_bank_stride : nullptr;
+                    src.bank_stride = prob.bank_stride;
+                    src.num_banks = prob.banks ? prob.num_banks : 0u; /* without a table every bank constant reads zero */
+                    src.K = prob.num_constants;
+                    src.n_affine = hp->n_affine;
+                    src.affines = batch.affines + hp->affine_off;
+                    src.lits = batch.lits + hp->lit_off;
+                    __syncwarp();
+                    run_bank_part<RC, FAST>(exec, first_bg * RC, ngroups * RC, n_cst, table + j * ngroups * table_stride, slot_base, src, lane);
+                }
+            }
+            __syncwarp();
+            const bool has_shared = mid_off > pre_off, has_prelude = main_off > mid_off;
+            const uint32_t eval_groups = (flags & SB_PROG_BANK_INDEPENDENT) ? 1u : ngroups;
 
             M m;
 #pragma unroll 1
@@ -552,13 +563,20 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
                 float* const hrowp = hoist + lane * 4;
                 const uint32_t row0 = pass * M::PASS + lane * 4; /* first row of this thread in the tile */
                 const bool full = (pass + 1) * M::PASS <= chunk_rows;
-                /* iteration -1 (only when the program has a row prelude) evaluates the bank-independent
-                 * sub-expressions once for the pass; iterations 0.. evaluate the main part per bank group.
-                 * One call site: a second inlined copy of the interpreter would not fit the instruction caches. */
+                /* Permutation -1 (only when the program has a shared row prelude) evaluates, once for the
+                 * pass, the row-only sub-expressions no toggle reaches.  For every permutation of the item,
+                 * iteration -1 (only when the program has one) evaluates the row-only sub-expressions that
+                 * depend on it, and iterations 0.. the main part per bank group.  One call site: a second
+                 * inlined copy of the interpreter would not fit the instruction caches. */
 #pragma unroll 1
-                for (int g = has_prelude ? -1 : 0; g < (int)eval_groups; ++g) {
+                for (int j = has_shared ? -1 : 0; j < (int)ppi; ++j) {
+                if (j >= 0 && ppi > 1u && n_patch) patch_for(perm0 + (uint32_t)j);
+                const int g_end = j < 0 ? 0 : (int)eval_groups;
+#pragma unroll 1
+                for (int g = (j < 0 || has_prelude) ? -1 : 0; g < g_end; ++g) {
                     const bool prelude = g < 0;
-                    m.run(exec + (prelude ? pre_off : main_off), rowp, tile_ld, table + (prelude ? 0u : (uint32_t)g * table_stride), slots,
+                    const uint32_t gi = (uint32_t)(j < 0 ? 0 : j) * ngroups + (uint32_t)(prelude ? 0 : g); /* this permutation's table, this group's */
+                    m.run(exec + (prelude ? (j < 0 ? pre_off : mid_off) : main_off), rowp, tile_ld, table + gi * table_stride, slots,
                           geom.scratch_slot, hrowp);
                     if (prelude) continue;
                     if (materialize) {
@@ -583,9 +601,9 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
                                 }
                             }
                         const float total = column_totals<RC>(part, lane);
-                        if ((lane & (32 / RC - 1)) == 0) psum[g * RC + lane / (32 / RC)] += total;
+                        if ((lane & (32 / RC - 1)) == 0) psum[gi * RC + lane / (32 / RC)] += total;
                     } else {
-                        /* several targets, or affine statistics: quantity q of bank group g lives in psum[(q * gpi + g) * RC + c] */
+                        /* several targets, or affine statistics: quantity q of pair gi lives in psum[(q * wide + gi) * RC + c] */
                         for (uint32_t qn = 0; qn < nq; ++qn) {
                             float tv[RR];
                             const bool is_target = prob.mode == EVAL_SSE || qn >= 2;
@@ -609,9 +627,10 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
                                 }
                             }
                             const float total = column_totals<RC>(s, lane);
-                            if ((lane & (32 / RC - 1)) == 0) psum[(qn * gpi + g) * RC + lane / (32 / RC)] += total;
+                            if ((lane & (32 / RC - 1)) == 0) psum[(qn * wide + gi) * RC + lane / (32 / RC)] += total;
                         }
                     }
+                }
                 }
             }
             if (materialize) continue;
@@ -620,17 +639,19 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
              * CTA touches them, and a barrier separates its tiles) */
             {
                 const bool independent = (flags & SB_PROG_BANK_INDEPENDENT) != 0;
-                float* mine = partial + ((size_t)split * batch.num_programs + lp) * nq * configs + perm;
                 const uint32_t width = ngroups * RC;          /* banks of the item, padding included */
-                const float* sums = psum;
-                for (uint32_t qn = 0; qn < nq; ++qn, mine += configs, sums += gpi * RC)
-                    for (uint32_t e = lane; e < width; e += 32) {
-                        const uint32_t bank = first_bg * RC + e;
-                        if (bank >= prob.num_banks) continue;
-                        const float v = independent ? sums[0] : sums[e]; /* psum is [quantity][group][bank of the group] */
-                        float* dst = mine + ((size_t)bank << prob.toggle_bits);
-                        *dst = t == 0 ? v : __fadd_rn(*dst, v);
-                    }
+                for (uint32_t j = 0; j < ppi; ++j) {
+                    float* mine = partial + ((size_t)split * batch.num_programs + lp) * nq * configs + perm0 + j;
+                    const float* sums = psum + j * width;     /* psum is [quantity][permutation][group][bank of the group] */
+                    for (uint32_t qn = 0; qn < nq; ++qn, mine += configs, sums += wide * RC)
+                        for (uint32_t e = lane; e < width; e += 32) {
+                            const uint32_t bank = first_bg * RC + e;
+                            if (bank >= prob.num_banks) continue;
+                            const float v = independent ? sums[0] : sums[e];
+                            float* dst = mine + ((size_t)bank << prob.toggle_bits);
+                            *dst = t == 0 ? v : __fadd_rn(*dst, v);
+                        }
+                }
             }
         }
     }

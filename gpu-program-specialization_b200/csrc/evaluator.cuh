@@ -91,6 +91,7 @@ struct LaunchPlan {
     uint32_t tile_buffers;    /* 2 when a CTA walks more than one tile: the next tile is fetched while this one is used */
     uint32_t num_groups;      /* CTAs along the programs; group g owns programs g, g + num_groups, ... */
     uint32_t groups_per_item; /* bank groups of one permutation a warp handles per queue item */
+    uint32_t perms_per_item;  /* consecutive permutations one item covers (a power of two; above 1 only when an item holds every bank group) */
     uint32_t row_splits;      /* CTAs sharing one program group, each with a row range */
     size_t rows_per_split;
     size_t smem_bytes;
@@ -108,6 +109,7 @@ struct Geom {
     uint32_t num_groups;
     uint32_t row_splits;
     uint32_t groups_per_item;
+    uint32_t perms_per_item;
     uint32_t exec_bytes;      /* per-warp regions, each a multiple of 16 bytes */
     uint32_t table_bytes;
     uint32_t hoist_bytes;

@@ -28,6 +28,7 @@ Geom make_geom(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPl
     const uint32_t rr = (uint32_t)kVariantRows[plan.variant], rc = (uint32_t)kVariantBanks[plan.variant];
     const uint32_t ncols = prob.num_inputs + (prob.mode == EVAL_MATERIALIZE ? 0u : prob.num_targets);
     const uint32_t gpi = plan.groups_per_item ? plan.groups_per_item : 1u;
+    const uint32_t ppi = plan.perms_per_item ? plan.perms_per_item : 1u;
     const uint32_t slots = batch.max_slots + (batch.uses_scratch ? 1u : 0u);
     Geom g;
     g.tile_rows = plan.tile_rows;
@@ -36,11 +37,12 @@ Geom make_geom(const DeviceBatch& batch, const EvalProblem& prob, const LaunchPl
     g.num_groups = plan.num_groups;
     g.row_splits = plan.row_splits;
     g.groups_per_item = gpi;
+    g.perms_per_item = ppi;
     g.exec_bytes = round16(((size_t)batch.max_insn + 1) * sizeof(SbInsn));
-    g.table_bytes = round16((size_t)std::max<uint32_t>(1u, gpi * batch.max_cst * rc) * 4);
+    g.table_bytes = round16((size_t)std::max<uint32_t>(1u, ppi * gpi * batch.max_cst * rc) * 4);
     g.hoist_bytes = round16((size_t)batch.max_hoisted * 32u * rr * 4);
     g.slot_bytes = round16(std::max<size_t>((size_t)slots * rr * rc * 128u, (size_t)batch.max_btmp * 128u));
-    g.psum_bytes = round16((size_t)std::max<uint32_t>(1u, quantities(prob) * gpi * rc) * 4);
+    g.psum_bytes = round16((size_t)std::max<uint32_t>(1u, quantities(prob) * ppi * gpi * rc) * 4);
     g.warp_bytes = g.exec_bytes + g.table_bytes + g.hoist_bytes + g.slot_bytes + g.psum_bytes;
     g.scratch_slot = batch.max_slots; /* one slot beyond what the programs use */
     g.rows_per_split = plan.rows_per_split;
@@ -55,6 +57,7 @@ LaunchPlan plan_with_tile(const DeviceBatch& batch, const EvalProblem& prob, int
     plan.ok = false;
     plan.overflow = false;
     plan.groups_per_item = 1;
+    plan.perms_per_item = 1;
     plan.variant = variant;
     const uint32_t rr = (uint32_t)kVariantRows[variant], rc = (uint32_t)kVariantBanks[variant];
     const uint32_t pass = 32u * rr;
@@ -77,7 +80,16 @@ LaunchPlan plan_with_tile(const DeviceBatch& batch, const EvalProblem& prob, int
         }
         plan.groups_per_item = (uint32_t)gpi;
         if (prob.toggle_bits > 40 || (bank_groups / gpi) > (~0ull >> prob.toggle_bits)) { plan.overflow = true; return plan; }
-        items_per_program = (bank_groups / gpi) << prob.toggle_bits;
+        /* An item that holds every bank group of its permutation may go on to the next permutations, up
+         * to sixteen (permutation, bank group) pairs within the same table and partial-sum budgets: the
+         * program is fetched once for them and its toggle-free row prelude runs once per row pass. */
+        unsigned long long ppi = 1;
+        if (gpi == bank_groups)
+            while (ppi * 2 * gpi <= 16 && ppi * 2 <= (1ull << prob.toggle_bits) && ppi * 2 * gpi * batch.max_cst * rc * 4 <= 2048 &&
+                   ppi * 2 * gpi * nq * rc * 4 <= 2048)
+                ppi *= 2;
+        plan.perms_per_item = (uint32_t)ppi;
+        items_per_program = ((bank_groups / gpi) << prob.toggle_bits) / ppi;
     }
     /* item ids are 32-bit and every warp draws one id past the end */
     const unsigned long long kMaxItems = 0xffffff00ull;

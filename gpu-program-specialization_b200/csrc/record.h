@@ -88,15 +88,18 @@ enum {
 
 /* Per-program header; offsets index the pools of the batch the program belongs to.
  *
- * A program is up to three instruction runs, each closed by END:
+ * A program is up to four instruction runs, each closed by END:
  *   [0, pre_off)         bank part: everything that depends on the coefficient bank but not on
  *                        the row (and every constant the other parts read) is computed once per
  *                        bank by a scalar machine and left in the program's constant table of
  *                        n_cst entries per bank (STOREH);
- *   [pre_off, main_off)  row prelude: sub-expressions that depend on the row but not on the bank,
- *                        evaluated once per row and kept as per-row values (STOREH), which the
- *                        main part reads as ROW operands with SB_ROW_HOISTED set;
- *   [main_off, n_insn)   main part, run once per (row tile, bank group).
+ *   [pre_off, mid_off)   shared row prelude: sub-expressions that depend on the row but neither on
+ *                        the bank nor on any toggle, evaluated once per row for all permutations
+ *                        an item covers and kept as per-row values (STOREH), which later runs read
+ *                        as ROW operands with SB_ROW_HOISTED set;
+ *   [mid_off, main_off)  row prelude: the same for row-only sub-expressions a toggle reaches,
+ *                        evaluated once per (row, permutation);
+ *   [main_off, n_insn)   main part, run once per (row tile, permutation, bank group).
  * Values and rounding are those of the plain postfix evaluation: the same operations run on the
  * same operands, only less often.  Records made for the rollout kernel have a main part only
  * (pre_off = main_off = 0) and address source constants directly. */
@@ -119,6 +122,8 @@ typedef struct SbProgram {
     uint16_t flags;     /* SB_PROG_* */
     uint32_t index;     /* position of the program in the run (output row, bank table) */
     uint32_t cost;      /* scheduling weight: bits 0..15 main part per bank group, bits 16..31 row prelude */
+    uint16_t mid_off;
+    uint16_t reserved;
 } SbProgram;
 
 #endif

@@ -29,7 +29,8 @@ SBT_EXPORT int sbt_encode(const uint8_t* routine_blob, const uint64_t* routine_o
                           const uint8_t* ast_blob, const uint64_t* ast_off, size_t num_asts, size_t num_columns,
                           size_t num_constants, int banks_allowed, unsigned toggle_bits, int flags,
                           SbtBatch** out) {
-    /* flags: bit 0 run the preflight scan first; bit 1 hoist bank-only and row-only sub-expressions;
+    /* flags: bit 0 run the preflight scan first; bit 1 hoist bank-only and row-only sub-expressions; bit 3 only
+     * row-only sub-expressions that no toggle reaches;
      * bit 2 one-part records with direct constant addressing (the rollout kernel's form);
      * bits 8.. cap on hoisted row values (0 = default) */
     const bool run_preflight = (flags & 1) != 0, hoist = (flags & 2) != 0, flat = (flags & 4) != 0;
@@ -48,6 +49,7 @@ SBT_EXPORT int sbt_encode(const uint8_t* routine_blob, const uint64_t* routine_o
     b->rules.split_parts = !flat;
     b->rules.hoist_bank = hoist && !flat;
     b->rules.hoist_row = hoist && !flat;
+    b->rules.hoist_toggled = !(flags & 8u);
     if (flags >> 8) b->rules.max_hoisted = (unsigned)(flags >> 8);
     SecantResult r = SECANT_SUCCESS;
     if (run_preflight) {
@@ -64,12 +66,12 @@ SBT_EXPORT int sbt_encode(const uint8_t* routine_blob, const uint64_t* routine_o
 SBT_EXPORT void sbt_free(SbtBatch* b) { delete b; }
 
 /* info[0..9] = n_insn, n_slots, n_ops, n_patch, n_affine, n_lits, pre_off, main_off, n_hoisted, n_cst;
- * info[10] = n_btmp, info[11] = flags */
+ * info[10] = n_btmp, info[11] = flags, info[12] = mid_off */
 SBT_EXPORT void sbt_info(const SbtBatch* b, size_t program, uint32_t* info) {
     const SbProgram& p = b->enc.programs[program];
-    const uint32_t v[12] = {p.n_insn, p.n_slots, p.n_ops, p.n_patch, p.n_affine, p.n_lits,
-                            p.pre_off, p.main_off, p.n_hoisted, p.n_cst, p.n_btmp, p.flags};
-    for (int i = 0; i < 12; ++i) info[i] = v[i];
+    const uint32_t v[13] = {p.n_insn, p.n_slots, p.n_ops, p.n_patch, p.n_affine, p.n_lits,
+                            p.pre_off, p.main_off, p.n_hoisted, p.n_cst, p.n_btmp, p.flags, p.mid_off};
+    for (int i = 0; i < 13; ++i) info[i] = v[i];
 }
 
 /* Instruction counts by case id over all programs, per part:
@@ -115,7 +117,7 @@ static float apply_un(unsigned op, float a) {
 }
 
 /* Value of program `program` on `row` for one bank vector and one permutation: the bank part
- * once (filling the constant table), the row prelude once, then the main part twice with every
+ * once (filling the constant table), the two row preludes once, then the main part twice with every
  * spill slot poisoned in between, as the device runs the main part once per bank group after
  * one prelude: a main part that relied on a slot written by the prelude or by its own previous
  * run is caught. */
@@ -125,13 +127,16 @@ SBT_EXPORT int sbt_eval(const SbtBatch* b, size_t program, const float* input, s
     const SbProgram& p = e.programs[program];
     const size_t K = b->rules.num_constants;
     std::vector<SbInsn> code(e.insns.begin() + p.insn_off, e.insns.begin() + p.insn_off + p.n_insn);
-    for (unsigned i = 0; i < p.n_patch; ++i) {
-        const SbPatch& s = e.patches[p.patch_off + i];
-        unsigned choice = (unsigned)(permutation >> s.bit0) & 1u;
-        if (s.bit1 != 0xff) choice |= ((unsigned)(permutation >> s.bit1) & 1u) << 1;
-        if (s.insn >= code.size()) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
-        code[s.insn] = s.alt[choice];
-    }
+    auto patch_for = [&](uint64_t perm) -> bool {
+        for (unsigned i = 0; i < p.n_patch; ++i) {
+            const SbPatch& s = e.patches[p.patch_off + i];
+            unsigned choice = (unsigned)(perm >> s.bit0) & 1u;
+            if (s.bit1 != 0xff) choice |= ((unsigned)(perm >> s.bit1) & 1u) << 1;
+            if (s.insn >= code.size()) return false;
+            code[s.insn] = s.alt[choice];
+        }
+        return true;
+    };
     std::vector<float> source(K + p.n_affine + p.n_lits, 0.0f);
     for (size_t k = 0; k < K; ++k) source[k] = bank ? bank[k] : 0.0f;
     for (unsigned j = 0; j < p.n_affine; ++j) {
@@ -191,10 +196,21 @@ SBT_EXPORT int sbt_eval(const SbtBatch* b, size_t program, const float* input, s
         }
         return false;
     };
-    if (p.pre_off && !run_part(0, 0)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
-    if (p.main_off > p.pre_off) {
+    /* the shared prelude runs once for all permutations of an item, with the program patched for
+     * whichever of them came last and the table of the item's first one: here under the
+     * complementary permutation, which differs in every toggle */
+    if (p.mid_off > p.pre_off) {
+        if (!patch_for(~permutation)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
+        if (p.pre_off && !run_part(0, 0)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
         for (auto& v : slots) v = std::nanf("");
         if (!run_part(p.pre_off, 1)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
+        for (auto& v : table) v = std::nanf("");
+    }
+    if (!patch_for(permutation)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
+    if (p.pre_off && !run_part(0, 0)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
+    if (p.main_off > p.mid_off) {
+        for (auto& v : slots) v = std::nanf("");
+        if (!run_part(p.mid_off, 1)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
     }
     for (int round = 0; round < 2; ++round) {
         for (auto& v : slots) v = std::nanf("");
@@ -227,8 +243,8 @@ SBT_EXPORT int sbt_validate_runs(const SecantCubinRecipeHeader* recipe, const Se
 /* Launch geometry the runner would pick for a batch with the given maxima (planner.cpp), so its
  * bounds can be checked without a device.  Returns 1 when a plan exists, 0 when the batch does not
  * fit shared memory, -1 when a count does not fit the kernel's 32-bit indices.
- * out[0..12] = variant, warps, tile_rows, tile_buffers, num_groups, groups_per_item, row_splits,
- * rows_per_split, smem_bytes, partial_elements, grid_x, warp_bytes, items per CTA and tile. */
+ * out[0..13] = variant, warps, tile_rows, tile_buffers, num_groups, groups_per_item, row_splits,
+ * rows_per_split, smem_bytes, partial_elements, grid_x, warp_bytes, items per CTA and tile, perms_per_item. */
 #include "evaluator.cuh"
 SBT_EXPORT int sbt_plan(uint32_t num_programs, uint32_t max_insn, uint32_t max_slots, uint32_t max_hoisted, uint32_t max_cst,
                         uint32_t max_btmp, int mode, uint32_t num_inputs, uint32_t num_targets, uint32_t num_banks,
@@ -246,12 +262,12 @@ SBT_EXPORT int sbt_plan(uint32_t num_programs, uint32_t max_insn, uint32_t max_s
     const Geom g = make_geom(db, p, plan);
     const uint64_t rc = (uint64_t)kVariantBanks[plan.variant];
     const uint64_t bank_groups = mode == EVAL_MATERIALIZE ? 1 : (num_banks + rc - 1) / rc;
-    const uint64_t items_per_program = mode == EVAL_MATERIALIZE ? 1 : (bank_groups / plan.groups_per_item) << toggle_bits;
+    const uint64_t items_per_program = mode == EVAL_MATERIALIZE ? 1 : ((bank_groups / plan.groups_per_item) << toggle_bits) / plan.perms_per_item;
     const uint64_t per_cta = (num_programs + plan.num_groups - 1) / plan.num_groups;
-    const uint64_t v[13] = {(uint64_t)plan.variant, plan.warps, plan.tile_rows, plan.tile_buffers, plan.num_groups, plan.groups_per_item,
+    const uint64_t v[14] = {(uint64_t)plan.variant, plan.warps, plan.tile_rows, plan.tile_buffers, plan.num_groups, plan.groups_per_item,
                             plan.row_splits, plan.rows_per_split, plan.smem_bytes, plan.partial_elements, plan.grid_x, g.warp_bytes,
-                            per_cta * items_per_program};
-    for (int i = 0; i < 13; ++i) out[i] = v[i];
+                            per_cta * items_per_program, plan.perms_per_item};
+    for (int i = 0; i < 14; ++i) out[i] = v[i];
     return 1;
 }
 

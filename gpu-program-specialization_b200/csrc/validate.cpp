@@ -194,13 +194,15 @@ SecantResult runs_validate(const SecantCubinPlan& plan, const UnpackedRun* runs,
     rules.num_constants = plan.num_constants;
     rules.banks_allowed = plan.shape == SECANT_KERNEL_SHAPE_TOGGLE_SSE_F32;
     rules.toggle_bits = rules.banks_allowed ? smallest_bits : 0;
-    /* records in three parts; row-only sub-expressions are worth a prelude as soon as a program
-     * is evaluated for more than one group of four banks */
+    /* records in parts; row-only sub-expressions are worth a prelude as soon as a program is
+     * evaluated for more than one group of four banks, and those no toggle reaches as soon as there
+     * are toggles (an item then covers several permutations and computes them once) */
     rules.split_parts = true;
     rules.hoist_bank = true;
-    rules.hoist_row = false;
+    rules.hoist_toggled = false;
     if (rules.banks_allowed)
-        for (size_t i = 0; i < count; ++i) rules.hoist_row = rules.hoist_row || runs[i].num_banks > 4;
+        for (size_t i = 0; i < count; ++i) rules.hoist_toggled = rules.hoist_toggled || runs[i].num_banks > 4;
+    rules.hoist_row = rules.hoist_toggled || rules.toggle_bits > 0;
     if (!skip_preflight) {
         const SecantAstProgramList* lists[2] = {&programs.routines, &programs.asts};
         for (const SecantAstProgramList* list : lists)

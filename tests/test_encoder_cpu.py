@@ -23,8 +23,8 @@ def encode(packed, columns, constants, banks_allowed=True, toggle_bits=0, prefli
 
 
 def info(handle, index):
-    """n_insn, n_slots, n_ops, n_patch, n_affine, n_lits, pre_off, main_off, n_hoisted, n_cst, n_btmp, flags"""
-    out = (C.c_uint32 * 12)()
+    """n_insn, n_slots, n_ops, n_patch, n_affine, n_lits, pre_off, main_off, n_hoisted, n_cst, n_btmp, flags, mid_off"""
+    out = (C.c_uint32 * 13)()
     S.hooks().sbt_info(handle, C.c_size_t(index), out)
     return list(out)
 

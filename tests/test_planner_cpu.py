@@ -8,13 +8,13 @@ import pytest
 import support as S
 
 SMEM = 232448          # opt-in shared memory per block of a B200, bytes
-FIELDS = "variant warps tile_rows buffers groups gpi splits rows_per_split smem partial grid warp_bytes items".split()
+FIELDS = "variant warps tile_rows buffers groups gpi splits rows_per_split smem partial grid warp_bytes items ppi".split()
 SSE, MATERIALIZE, AFFINE = 0, 1, 2
 
 
 def plan(programs, rows, banks=64, bits=0, inputs=8, targets=1, mode=SSE, insn=80, slots=2, hoisted=4, table=8, btmp=3,
          sms=148, smem=SMEM, scratch=1 << 28):
-    out = (C.c_uint64 * 13)()
+    out = (C.c_uint64 * 14)()
     code = S.hooks().sbt_plan(programs, insn, slots, hoisted, table, btmp, mode, inputs, targets, banks, bits, C.c_uint64(rows), sms,
                               C.c_uint64(smem), C.c_uint64(scratch), out)
     return code, dict(zip(FIELDS, list(out)))
@@ -30,6 +30,20 @@ def test_headline_shape_fills_the_machine():
     assert p["rows_per_split"] % p["tile_rows"] == 0 and p["rows_per_split"] * p["splits"] >= 1 << 20
 
 
+def test_items_span_permutations_when_one_item_holds_every_bank():
+    """Four coefficient sets are one bank group of the 4 x 4 tile, so an item goes on over sixteen
+    permutations (the program is fetched once for them); with sixteen bank groups per item there
+    is no room, and the tables of long programs shrink the span."""
+    code, p = plan(16384, 1 << 18, banks=4, bits=8, inputs=6, table=8)
+    assert code == 1 and p["gpi"] == 1 and p["ppi"] == 16
+    assert p["items"] == -(-16384 // p["groups"]) * (256 // 16)
+    assert plan(16384, 1 << 18, banks=64, bits=8)[1]["ppi"] == 1
+    assert plan(16384, 1 << 18, banks=8, bits=8)[1]["ppi"] == 8                # two bank groups per permutation
+    assert plan(16384, 1 << 18, banks=4, bits=2)[1]["ppi"] == 4                # no more permutations than there are
+    assert plan(16384, 1 << 18, banks=4, bits=8, table=24)[1]["ppi"] == 4      # 24 entries x 16 bytes x 4 = 1,536 bytes of tables
+    assert plan(16384, 1 << 18, banks=4, bits=0)[1]["ppi"] == 1
+
+
 def test_scratch_cap_trades_row_splits_for_memory():
     _, free = plan(2048, 1 << 18)
     _, capped = plan(2048, 1 << 18, scratch=3 * 2048 * 64)
@@ -41,14 +55,17 @@ def test_scratch_cap_trades_row_splits_for_memory():
 def test_item_index_stays_inside_32_bits():
     """toggle_bits up to 32 is a valid request (projects/secant/s_toggle_internal.h:52-71); the
     queue's item ids are 32-bit, so such runs are refused with OVERFLOW instead of being launched
-    (a wrapped counter would never reach the end of the queue)."""
-    assert plan(1, 1000, banks=1, bits=32)[0] == -1
-    assert plan(1, 1000, banks=4, bits=32)[0] == -1
-    code, p = plan(1, 1000, banks=4, bits=31)
-    assert code == 1 and p["items"] == 1 << 31 and p["items"] + 20 < 1 << 32
-    code, p = plan(64, 1000, banks=4, bits=28)                 # many programs: fewer per CTA, never a wrapped count
+    (a wrapped counter would never reach the end of the queue).  An item covers up to sixteen
+    (permutation, bank group) pairs, so the bound is reached with many banks."""
+    assert plan(1, 1000, banks=64, bits=32)[0] == -1           # 2^32 items of sixteen bank groups
+    assert plan(1, 1000, banks=128, bits=31)[0] == -1
+    code, p = plan(1, 1000, banks=4, bits=32)                  # one bank group: sixteen permutations per item
+    assert code == 1 and p["ppi"] == 16 and p["items"] == 1 << 28
+    code, p = plan(1, 1000, banks=64, bits=31)
+    assert code == 1 and p["ppi"] == 1 and p["items"] == 1 << 31 and p["items"] + 20 < 1 << 32
+    code, p = plan(64, 1000, banks=64, bits=28)                # many programs: fewer per CTA, never a wrapped count
     assert code == 1 and p["items"] + 20 < 1 << 32 and p["groups"] >= 4
-    code, p = plan(100000, 1000, banks=4, bits=31)
+    code, p = plan(100000, 1000, banks=64, bits=31)
     assert code == 1 and p["groups"] == 100000 and p["items"] == 1 << 31
 
 
