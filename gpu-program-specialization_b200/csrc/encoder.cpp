@@ -489,6 +489,11 @@ struct Emitter {
             }
             p.insn = (uint16_t)code[run].size();
             if (code[run].size() > 0xffffu) error = SECANT_ERROR_REGISTER_OVERFLOW;
+            /* a site of the bank part names itself in the second word (1 + its position among the
+             * program's sites, which begin with the bank part's): the scalar machine serves several
+             * permutations at once and lets every lane take its own alternative */
+            if (run == RUN_BANK)
+                for (unsigned i = 0; i < 4; ++i) p.alt[i].w1 = (uint32_t)sites[RUN_BANK].size() + 1u;
             sites[run].push_back(p);
             push(p.alt[0].w0, p.alt[0].w1);
         } else {

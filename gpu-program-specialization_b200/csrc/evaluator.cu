@@ -343,18 +343,23 @@ __device__ __forceinline__ float scalar_binary(unsigned op, float a, float x) {
 }
 
 /* Runs the bank part of the warp's program for the `count` banks starting at `first_bank` (count is
- * a multiple of RC; banks past the table's end are padding and read zeros).  Lane l handles banks
- * l, l + 32, ...  Results go to the warp's constant table laid out [bank group][entry][bank of the
- * group], `entries` entries per group; temporaries live in `tmp`, 32 floats apart.  The same
- * functions as the tile machine are called, so a value computed here has the bits it would have
- * had in the main part. */
+ * a multiple of RC; banks past the table's end are padding and read zeros) and for `perms`
+ * permutations starting at `perm0`.  Lane l handles (permutation, bank) pairs l, l + 32, ...,
+ * permutation-major.  Results go to the warp's constant tables laid out [permutation][bank group]
+ * [entry][bank of the group], `entries` entries per group; temporaries live in `tmp`, 32 floats
+ * apart.  A toggle site of the bank part carries 1 + its index in the second instruction word; every
+ * lane takes the alternative of its own permutation from the program's site list, so the state of
+ * the warp's patched copy does not matter here.  The same functions as the tile machine are called,
+ * so a value computed here has the bits it would have had in the main part. */
 template <int RC, bool FAST>
-__device__ __noinline__ void run_bank_part(const SbInsn* exec, uint32_t first_bank, uint32_t count, uint32_t entries, float* table,
-                                           float* tmp, const BankSource src, int lane) {
-    for (uint32_t b0 = 0; b0 < count; b0 += 32) {
-        const uint32_t b = b0 + lane, bank = first_bank + b;
-        const bool live = b < count, real = live && bank < src.num_banks;
-        float* const mine = table + ((size_t)(b / RC) * entries) * RC + (b % RC);
+__device__ __noinline__ void run_bank_part(const SbInsn* exec, uint32_t first_bank, uint32_t count, uint32_t perms, uint32_t perm0,
+                                           const SbPatch* sites, uint32_t entries, float* table, float* tmp, const BankSource src, int lane) {
+    const uint32_t pairs = count * perms;
+    for (uint32_t v0 = 0; v0 < pairs; v0 += 32) {
+        const uint32_t v = v0 + lane, j = v / count, b = v - j * count, bank = first_bank + b;
+        const uint32_t perm = perm0 + j;
+        const bool live = v < pairs, real = live && bank < src.num_banks;
+        float* const mine = table + ((size_t)(j * (count / RC) + b / RC) * entries) * RC + (b % RC);
         const float* const row = src.banks + (size_t)bank * src.bank_stride;
         auto operand = [&](unsigned kind, uint32_t idx) -> float {
             if (kind == SB_KIND_ROW) return live ? mine[(size_t)idx * RC] : 0.0f;
@@ -370,17 +375,24 @@ __device__ __noinline__ void run_bank_part(const SbInsn* exec, uint32_t first_ba
         float acc = 0.0f;
 #pragma unroll 1
         for (;;) {
-            const uint2 ins = *ip++;
-            const unsigned cs = ins.x & 0xffu;
+            uint2 ins = *ip++;
+            const unsigned cs = ins.x & 0xffu; /* the operation is the same in every alternative of a site */
             if (cs == SB_CASE_END || cs > SB_CASE_FMA) break;
+            const bool fma = cs == SB_CASE_FMA, bin = cs >= SB_CASE_BIN && cs < SB_CASE_UN;
+            if (!fma && ins.y) { /* a toggle site: this lane's permutation selects the operand */
+                const SbPatch* p = sites + (ins.y - 1u);
+                unsigned choice = (perm >> p->bit0) & 1u;
+                if (p->bit1 != 0xffu) choice |= ((perm >> p->bit1) & 1u) << 1;
+                ins.x = p->alt[choice].w0;
+            }
+            const unsigned mine_cs = ins.x & 0xffu;
             /* operands first, at one site (the fetch is the bulky part): one for loads and binary
              * operations, three for the fused multiply-add, none otherwise */
             float v[3] = {acc, acc, acc};
-            const bool fma = cs == SB_CASE_FMA, bin = cs >= SB_CASE_BIN && cs < SB_CASE_UN;
             const unsigned count = fma ? 3u : (cs < SB_CASE_STORE || bin) ? 1u : 0u;
 #pragma unroll 1
             for (unsigned i = 0; i < count; ++i) {
-                const unsigned kind = fma ? (ins.x >> (8 + 2 * i)) & 3u : bin ? (cs - SB_CASE_BIN) % SB_NUM_KINDS : cs - SB_CASE_LOAD;
+                const unsigned kind = fma ? (ins.x >> (8 + 2 * i)) & 3u : bin ? (mine_cs - SB_CASE_BIN) % SB_NUM_KINDS : mine_cs - SB_CASE_LOAD;
                 const uint32_t idx = fma ? (ins.y >> (10 * i)) & 1023u : ins.x >> 16;
                 if (kind != SB_FMA_ACC) v[i] = operand(kind, idx);
             }
@@ -535,23 +547,21 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
             for (uint32_t e = lane; e < nq * wide * RC; e += 32) psum[e] = 0.0f;
             const size_t gp = prob.first_program + hp->index; /* position in the run: output row, bank table */
             const uint32_t table_stride = n_cst * RC;
-            /* the constant tables of every permutation of the item; an item of one permutation stays
-             * patched for it, the others are patched again inside the row passes */
-            for (uint32_t j = 0; j < ((pre_off || ppi == 1u) ? ppi : 0u); ++j) {
-                if (n_patch) patch_for(perm0 + j);
-                if (pre_off) {
-                    BankSource src;
-                    src.banks = prob.banks ? prob.banks + gp * prob.program_bank_stride : nullptr;
-                    src.bank_stride = prob.bank_stride;
-                    src.num_banks = prob.banks ? prob.num_banks : 0u; /* without a table every bank constant reads zero */
-                    src.K = prob.num_constants;
-                    src.n_affine = hp->n_affine;
-                    src.affines = batch.affines + hp->affine_off;
-                    src.lits = batch.lits + hp->lit_off;
-                    __syncwarp();
-                    run_bank_part<RC, FAST>(exec, first_bg * RC, ngroups * RC, n_cst, table + j * ngroups * table_stride, slot_base, src, lane);
-                }
+            /* the constant tables of every permutation of the item, all in one run of the bank part; an
+             * item of one permutation is then patched for it, the others inside the row passes */
+            __syncwarp();
+            if (pre_off) {
+                BankSource src;
+                src.banks = prob.banks ? prob.banks + gp * prob.program_bank_stride : nullptr;
+                src.bank_stride = prob.bank_stride;
+                src.num_banks = prob.banks ? prob.num_banks : 0u; /* without a table every bank constant reads zero */
+                src.K = prob.num_constants;
+                src.n_affine = hp->n_affine;
+                src.affines = batch.affines + hp->affine_off;
+                src.lits = batch.lits + hp->lit_off;
+                run_bank_part<RC, FAST>(exec, first_bg * RC, ngroups * RC, ppi, perm0, patches, n_cst, table, slot_base, src, lane);
             }
+            if (ppi == 1u && n_patch) patch_for(perm0);
             __syncwarp();
             const bool has_shared = mid_off > pre_off, has_prelude = main_off > mid_off;
             const uint32_t eval_groups = (flags & SB_PROG_BANK_INDEPENDENT) ? 1u : ngroups;

@@ -150,6 +150,7 @@ SBT_EXPORT int sbt_eval(const SbtBatch* b, size_t program, const float* input, s
     std::vector<float> slots(std::max<unsigned>(1, std::max(p.n_slots, p.n_btmp)), std::nanf(""));
     std::vector<float> hoisted(p.n_hoisted ? p.n_hoisted : 1, std::nanf(""));
     float acc = std::nanf("");
+    uint64_t bank_permutation = permutation; /* the permutation the bank part's lanes select by */
     int part = 0; /* 0 bank, 1 prelude, 2 main */
     bool failed = false;
     auto operand = [&](unsigned kind, unsigned index, bool fma) -> float {
@@ -171,7 +172,15 @@ SBT_EXPORT int sbt_eval(const SbtBatch* b, size_t program, const float* input, s
     auto run_part = [&](size_t begin, int which) -> bool {
         part = which;
         for (size_t pc = begin; pc < code.size(); ++pc) {
-            const SbInsn ins = code[pc];
+            SbInsn ins = code[pc];
+            if (which == 0 && ins.w1 && (ins.w0 & 0xffu) != SB_CASE_FMA) { /* a toggle site of the bank part picks its own alternative */
+                if (ins.w1 > p.n_patch) return false;
+                const SbPatch& site = e.patches[p.patch_off + ins.w1 - 1];
+                unsigned choice = (unsigned)(bank_permutation >> site.bit0) & 1u;
+                if (site.bit1 != 0xff) choice |= ((unsigned)(bank_permutation >> site.bit1) & 1u) << 1;
+                if (site.insn != pc || (site.alt[choice].w0 & 0xffu) == SB_CASE_END) return false;
+                ins.w0 = site.alt[choice].w0;
+            }
             const unsigned cs = ins.w0 & 0xffu, index = ins.w0 >> 16;
             if (cs == SB_CASE_END) return !failed;
             if (cs >= SB_CASE_LOAD && cs < SB_CASE_LOAD + SB_NUM_KINDS) acc = operand(cs - SB_CASE_LOAD, index, false);
@@ -201,13 +210,17 @@ SBT_EXPORT int sbt_eval(const SbtBatch* b, size_t program, const float* input, s
      * complementary permutation, which differs in every toggle */
     if (p.mid_off > p.pre_off) {
         if (!patch_for(~permutation)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
+        bank_permutation = ~permutation;
         if (p.pre_off && !run_part(0, 0)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
         for (auto& v : slots) v = std::nanf("");
         if (!run_part(p.pre_off, 1)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
         for (auto& v : table) v = std::nanf("");
     }
-    if (!patch_for(permutation)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
+    /* the bank part selects by itself: run it on a copy patched for yet another permutation */
+    if (!patch_for(permutation ^ 0x5555555555555555ull)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
+    bank_permutation = permutation;
     if (p.pre_off && !run_part(0, 0)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
+    if (!patch_for(permutation)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
     if (p.main_off > p.mid_off) {
         for (auto& v : slots) v = std::nanf("");
         if (!run_part(p.mid_off, 1)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
