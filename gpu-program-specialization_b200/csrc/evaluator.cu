@@ -447,7 +447,7 @@ __device__ __noinline__ void stage_tile(float* tile, uint32_t tile_ld, const Eva
 
 /* 16 values per thread: 20 warps per CTA within 96 registers (32-value tiles were measured
  * slower at the 12 warps their 168 registers allow). */
-template <int RR, int RC, bool FAST>
+template <int RR, int RC, bool FAST, bool SPAN>
 __global__ void __launch_bounds__(640, 1)
 eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, float* __restrict__ partial) {
     using M = Machine<RR, RC, FAST>;
@@ -474,7 +474,7 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
     const uint32_t T = prob.num_targets;
     const uint32_t nq = prob.mode == EVAL_AFFINE_STATS ? T + 2 : T;
     const uint32_t gpi = geom.groups_per_item;
-    const uint32_t ppi = materialize ? 1u : geom.perms_per_item;
+    const uint32_t ppi = (!SPAN || materialize) ? 1u : geom.perms_per_item; /* SPAN: items may cover several permutations */
     const uint32_t wide = ppi * gpi; /* (permutation, bank group) pairs of an item: the partial sums' middle dimension */
     /* configuration groups of one program: permutation-major, RC banks per group */
     const uint32_t bank_groups = materialize ? 1u : (prob.num_banks + RC - 1) / RC;
@@ -573,21 +573,32 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
                 float* const hrowp = hoist + lane * 4;
                 const uint32_t row0 = pass * M::PASS + lane * 4; /* first row of this thread in the tile */
                 const bool full = (pass + 1) * M::PASS <= chunk_rows;
-                /* Permutation -1 (only when the program has a shared row prelude) evaluates, once for the
-                 * pass, the row-only sub-expressions no toggle reaches.  For every permutation of the item,
-                 * iteration -1 (only when the program has one) evaluates the row-only sub-expressions that
-                 * depend on it, and iterations 0.. the main part per bank group.  One call site: a second
-                 * inlined copy of the interpreter would not fit the instruction caches. */
+                /* One loop over the steps of a pass, so that the interpreter has one call site (a second
+                 * inlined copy would not fit the instruction caches).  First (only when the program has
+                 * one) the shared row prelude: the row-only sub-expressions no toggle reaches, once for the
+                 * pass.  Then, for every permutation of the item: the row-only sub-expressions that depend
+                 * on it (only when the program has any), and the main part once per bank group.  Without
+                 * SPAN an item has one permutation and the steps are -2 (shared prelude), -1 (prelude),
+                 * 0.. (bank groups); with it they are -1 (shared prelude) and then per_perm steps per
+                 * permutation. */
+                const int per_perm = (has_prelude ? 1 : 0) + (int)eval_groups;
+                const int first = SPAN ? (has_shared ? -1 : 0) : (has_shared ? -2 : has_prelude ? -1 : 0);
+                const int last = SPAN ? (int)ppi * per_perm : (int)eval_groups;
 #pragma unroll 1
-                for (int j = has_shared ? -1 : 0; j < (int)ppi; ++j) {
-                if (j >= 0 && ppi > 1u && n_patch) patch_for(perm0 + (uint32_t)j);
-                const int g_end = j < 0 ? 0 : (int)eval_groups;
-#pragma unroll 1
-                for (int g = (j < 0 || has_prelude) ? -1 : 0; g < g_end; ++g) {
-                    const bool prelude = g < 0;
-                    const uint32_t gi = (uint32_t)(j < 0 ? 0 : j) * ngroups + (uint32_t)(prelude ? 0 : g); /* this permutation's table, this group's */
-                    m.run(exec + (prelude ? (j < 0 ? pre_off : mid_off) : main_off), rowp, tile_ld, table + gi * table_stride, slots,
-                          geom.scratch_slot, hrowp);
+                for (int s = first; s < last; ++s) {
+                    int j = 0, g = s < 0 ? 0 : s;
+                    bool prelude = s < 0;
+                    uint32_t start = s == first && has_shared ? pre_off : s < 0 ? mid_off : main_off;
+                    if (SPAN) {
+                        j = s < 0 ? 0 : s / per_perm;
+                        const int w = s - j * per_perm; /* step inside the permutation */
+                        prelude = s < 0 || (has_prelude && w == 0);
+                        g = prelude ? 0 : w - (has_prelude ? 1 : 0);
+                        start = prelude ? (s < 0 ? pre_off : mid_off) : main_off;
+                        if (s >= 0 && w == 0 && ppi > 1u && n_patch) patch_for(perm0 + (uint32_t)j);
+                    } else if (s == -1 && !has_prelude) continue;
+                    const uint32_t gi = (uint32_t)j * ngroups + (uint32_t)g; /* this permutation's table, this group's */
+                    m.run(exec + start, rowp, tile_ld, table + gi * table_stride, slots, geom.scratch_slot, hrowp);
                     if (prelude) continue;
                     if (materialize) {
                         float* out = prob.output + gp * prob.out_program_stride + c0;
@@ -641,7 +652,6 @@ eval_kernel(const DeviceBatch batch, const EvalProblem prob, const Geom geom, fl
                         }
                     }
                 }
-                }
             }
             if (materialize) continue;
             __syncwarp();
@@ -688,10 +698,15 @@ __global__ void combine_kernel(const DeviceBatch batch, const EvalProblem prob, 
 template <int RR, int RC>
 cudaError_t launch_variant(const DeviceBatch& batch, const EvalProblem& prob, const Geom& geom, const LaunchPlan& plan,
                            float* partial, cudaStream_t stream) {
-    if (prob.fast_math)
-        eval_kernel<RR, RC, true><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom, partial);
+    const bool span = plan.perms_per_item > 1;
+    if (prob.fast_math && span)
+        eval_kernel<RR, RC, true, true><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom, partial);
+    else if (prob.fast_math)
+        eval_kernel<RR, RC, true, false><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom, partial);
+    else if (span)
+        eval_kernel<RR, RC, false, true><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom, partial);
     else
-        eval_kernel<RR, RC, false><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom, partial);
+        eval_kernel<RR, RC, false, false><<<plan.grid_x, plan.warps * 32, plan.smem_bytes, stream>>>(batch, prob, geom, partial);
     return cudaGetLastError();
 }
 
@@ -707,8 +722,10 @@ cudaError_t configure_kernels() {
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
     if ((e = cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return e;
 #define SB_CONFIGURE(RR, RC) \
-    if ((e = cudaFuncSetAttribute(eval_kernel<RR, RC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e; \
-    if ((e = cudaFuncSetAttribute(eval_kernel<RR, RC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(eval_kernel<RR, RC, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e; \
+    if ((e = cudaFuncSetAttribute(eval_kernel<RR, RC, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e; \
+    if ((e = cudaFuncSetAttribute(eval_kernel<RR, RC, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e; \
+    if ((e = cudaFuncSetAttribute(eval_kernel<RR, RC, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit)) != cudaSuccess) return e;
     SB_FOR_VARIANTS(SB_CONFIGURE)
 #undef SB_CONFIGURE
     return cudaSuccess;
