@@ -260,3 +260,44 @@ def test_reducer_and_gather_match_a_host_sort(cuda, systems, banks, bits, k):
         torch.cuda.synchronize()
         assert torch.equal(plain, winners) and torch.equal(plain_counts, counts)
     E.check(lib.odezza_score_reducer_destroy(reducer))
+
+
+# ---- the reference's own pools, run beside this library's -----------------------------------------
+
+def reference_engine():
+    """oracle/_ref/libodezza_engine_ref.so: the reference's o_philox.c (kernels compiled with NVRTC at
+    run time), built by `make -C oracle engine-ref`."""
+    path = os.path.join(REF, "libodezza_engine_ref.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref/libodezza_engine_ref.so is built only where the reference checkout exists")
+    lib = C.CDLL(path)
+    for name, (restype, argtypes) in E.EXPORTED.items():
+        if hasattr(lib, name):
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = restype, argtypes
+    return lib
+
+
+def pool_planes(lib, info):
+    pool, view = C.c_void_p(), E.RngPoolView()
+    code = lib.odezza_rng_pool_create(100, C.byref(info), C.byref(pool))
+    if code:
+        buf = C.create_string_buffer(2048)
+        lib.odezza_rng_pool_write_error(pool, buf, len(buf))
+        raise AssertionError((E.result_name(code), buf.value.decode()[-800:]))
+    E.check(lib.odezza_rng_pool_view(pool, C.byref(view)))
+    planes = download(view.uniform_device, info.size), download(view.normal_device, info.size)
+    E.check(lib.odezza_rng_pool_destroy(pool))
+    return planes
+
+
+def test_pools_equal_the_reference_pools_bit_for_bit(cuda):
+    """Both planes, sample for sample, against the reference's own pool kernels on the same device
+    (projects/odezza/core/o_philox.cu, compiled by the reference with --fmad=false): an odd sample
+    base, a size that is no multiple of four, and a second stream and seed."""
+    ref = reference_engine()
+    mine = E.load()
+    for info in (E.RngPoolInfo(20260906, 37, 7, 1048583, 3), E.RngPoolInfo(1, 0, 0, 4099, 3), E.RngPoolInfo((1 << 64) - 3, 12345, (1 << 40) + 2, 70001, 3)):
+        got, want = pool_planes(mine, info), pool_planes(ref, info)
+        for plane in range(2):
+            assert np.array_equal(got[plane].view(np.uint32), want[plane].view(np.uint32)), (info.seed, "uniform normal".split()[plane])
