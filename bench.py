@@ -193,6 +193,16 @@ def reference_arm(args, w):
     print(json.dumps(line))
 
 
+# What the evaluator kernel executes, from one multi-pass profiler capture of a reduced case of this
+# workload (4,096 programs x 131,072 rows, the summary is profiles/eval_kernel_configs1_reduced_ncu_full.md).
+# Not measured in this run: counters of that kind need a profiler and the full size is too large for it.
+EXECUTED_ON_REDUCED_CASE = {
+    "source": "profiler capture of a reduced case (4,096 programs x 131,072 rows), not this run",
+    "pipe_fma_pct": 32.9, "pipe_alu_pct": 37.0, "pipe_xu_pct": 13.7, "issue_active_pct": 68.7,
+    "instruction_cache_hit_pct": 97.8, "fp32_share_of_executed_instructions": 0.335,
+}
+
+
 # ------------------------------------------------------------------------ RK4 arm ----
 
 def rk4_arm(args, w):
@@ -645,7 +655,8 @@ def gpu_arm(args, w):
                          "note": "achieved = sum over programs of (ops + 2) x sets x rows / device time, one per "
                                  "algorithmic operation; peak = FFMA lane-instructions/s probed on this device in this "
                                  "run; DRAM traffic needs a multi-pass capture: measured on a reduced case only and not "
-                                 "proportional to the unit count"},
+                                 "proportional to the unit count",
+                         "executed": EXECUTED_ON_REDUCED_CASE},
             "cpu_baseline": cpu,
             "parity_spot": spot,
             "top1024_head": [int(i) for i in top_pin[:4].tolist()],

@@ -20,6 +20,7 @@
 #include <condition_variable>
 #include <cstddef>
 #include <cstring>
+#include <exception>
 #include <mutex>
 #include <system_error>
 #include <thread>
@@ -145,15 +146,13 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
     std::vector<std::thread> workers;
     const unsigned hardware = std::thread::hardware_concurrency();
     const size_t want_workers = std::min<size_t>(num_chunks > 1 ? num_chunks - 1 : 0, std::min<unsigned>(hardware ? hardware : 1u, 8u));
-    for (size_t w = 0; w < want_workers; ++w) {
-        try {
-            workers.emplace_back(encode_chunks);
-        } catch (const std::system_error&) {
-            break; /* fewer helpers, or none: the calling thread encodes whatever is left */
-        }
+    try {
+        workers.reserve(want_workers);
+        for (size_t w = 0; w < want_workers; ++w) workers.emplace_back(encode_chunks);
+    } catch (const std::exception&) {
+        /* no memory or no thread to be had: fewer helpers, or none; the calling thread encodes whatever is left */
     }
 
-    /* records travel on their own stream, so an upload never waits for the kernels of earlier chunks */
     /* records travel on their own stream, so an upload never waits for the kernels of earlier chunks;
      * the chunks' kernels go round the compute streams, so a chunk smaller than the GPU shares it
      * with its neighbours */
