@@ -163,6 +163,13 @@ struct Rk4Problem {
  * columns_are_slots and 5 * num_states reserved slots. */
 cudaError_t launch_rk4(const DeviceBatch& batch, const Rk4Problem& problem, size_t smem_limit, cudaStream_t stream);
 
+/* Adds the statistics of the static Gram shape for a batch of cohorts over `rows` rows of
+ * materialized predictions [program of the batch][prediction_ld] (gram.cu); statistics points at
+ * the batch's first cohort. */
+cudaError_t launch_gram(const float* predictions, size_t prediction_ld, uint32_t rows, const float* targets, size_t targets_ld,
+                        uint32_t num_targets, uint32_t cohort_size, uint32_t batch_programs, float* statistics, size_t statistics_ld,
+                        cudaStream_t stream);
+
 /* One-time per-device kernel attribute setup (dynamic shared memory opt-in). */
 cudaError_t configure_kernels();
 

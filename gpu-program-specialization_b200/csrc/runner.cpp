@@ -281,10 +281,6 @@ SecantResult options_validate(const SecantCubinRunnerOptions* options) {
 }
 
 SecantResult create_common(SecantCubinRunnerImpl* r, const SecantCubinRunnerOptions* options, SecantCubinRunner* out) {
-    if (r->plan->shape == SECANT_KERNEL_SHAPE_STATIC_GRAM_STATS_F32) { /* dense Gram cohorts are not evaluated here */
-        delete r;
-        return SECANT_ERROR_UNSUPPORTED_SHAPE;
-    }
     const SecantResult result = runner_init(r, options);
     if (result != SECANT_SUCCESS) {
         if (runner_teardown(r) != SECANT_SUCCESS) { /* keep ownership: destroy-only handle */
@@ -405,6 +401,8 @@ EvalProblem make_problem(const SecantCubinPlan& plan, const UnpackedRun& run, si
         p.mode = EVAL_SSE; p.out_program_stride = run.output.leading_dimension; p.out_target_stride = 1; break;
     case SECANT_KERNEL_SHAPE_STATIC_AFFINE_STATS_F32:
         p.mode = EVAL_AFFINE_STATS; p.out_program_stride = run.output.leading_dimension; p.out_target_stride = 1; break;
+    case SECANT_KERNEL_SHAPE_STATIC_GRAM_STATS_F32: /* predictions are materialized into scratch; launch_gram_batch() places them */
+        p.mode = EVAL_MATERIALIZE; p.output = nullptr; p.out_program_stride = 0; p.out_target_stride = 0; break;
     default:
         p.mode = EVAL_SSE;
         p.out_program_stride = run.num_targets * run.output.leading_dimension;
@@ -473,6 +471,59 @@ SecantResult launch_batch(SecantCubinRunnerImpl* r, const DeviceBatch& db, const
     return SECANT_SUCCESS;
 }
 
+/* The static Gram shape: the predictions of the batch's programs are materialized for a range of
+ * rows into the stream's scratch by the evaluator (every view of the batch), then reduced to the
+ * cohorts' statistics, range after range on one stream, so every statistic is added to in row
+ * order.  first_program is the batch's first program and a multiple of the cohort size. */
+SecantResult launch_gram_batch(SecantCubinRunnerImpl* r, const std::vector<DeviceBatch>& views, const std::vector<UnpackedRun>& runs,
+                               size_t first_program, size_t batch_programs, size_t* stream_cursor, cudaEvent_t after,
+                               std::vector<cudaEvent_t>* done, std::vector<char>* used) {
+    const SecantCubinPlan& plan = *r->plan;
+    const size_t cohort = plan.asts_per_kernel;
+    for (size_t e = 0; e < runs.size(); ++e) {
+        const UnpackedRun& run = runs[e];
+        const size_t k = (*stream_cursor)++ % r->streams.size();
+        cudaStream_t stream = r->streams[k];
+        /* rows per range: what the scratch limit leaves for this batch, between 128 and 16,384 */
+        const size_t fit = r->scratch_limit / batch_programs;
+        const size_t range = std::min<size_t>(run.rows, std::max<size_t>(128, std::min<size_t>(16384, fit)));
+        float* scratch = nullptr;
+        const SecantResult a = stream_scratch(r, k, batch_programs * range, &scratch);
+        if (a != SECANT_SUCCESS) return a;
+        cudaError_t ce = after ? cudaStreamWaitEvent(stream, after, 0) : cudaSuccess;
+        for (size_t r0 = 0; r0 < run.rows && ce == cudaSuccess; r0 += range) {
+            const size_t rows_now = std::min(range, run.rows - r0);
+            for (const DeviceBatch& db : views) {
+                EvalProblem prob = make_problem(plan, run, 0);
+                prob.fast_math = r->fast_math;
+                prob.input += r0;
+                prob.num_rows = rows_now;
+                /* SbProgram::index is the program's position in the run: shift the base so that the batch's first program lands on row 0 */
+                prob.output = reinterpret_cast<float*>(reinterpret_cast<uintptr_t>(scratch) - first_program * range * sizeof(float));
+                prob.out_program_stride = range;
+                const LaunchPlan lp = plan_launch(db, prob, r->sm_count, r->smem_limit, r->scratch_limit);
+                if (!lp.ok) {
+                    r->last_error = "program batch does not fit shared memory";
+                    return lp.overflow ? SECANT_ERROR_OVERFLOW : SECANT_ERROR_REGISTER_OVERFLOW;
+                }
+                unsigned launches = 0;
+                ce = launch_eval(db, prob, lp, nullptr, stream, &launches);
+                g_kernel_launches.fetch_add(launches);
+                if (ce != cudaSuccess) break;
+            }
+            if (ce == cudaSuccess)
+                ce = launch_gram(scratch, range, (uint32_t)rows_now, reinterpret_cast<const float*>(run.targets.address) + r0,
+                                 run.targets.leading_dimension, (uint32_t)run.num_targets, (uint32_t)cohort, (uint32_t)batch_programs,
+                                 reinterpret_cast<float*>(run.output.address) + (first_program / cohort) * run.output.leading_dimension,
+                                 run.output.leading_dimension, stream);
+        }
+        if (ce == cudaSuccess && done) ce = cudaEventRecord((*done)[k], stream);
+        if (ce != cudaSuccess) return cuda_fail(r, ce, "kernel launch");
+        if (used) (*used)[k] = 1;
+    }
+    return SECANT_SUCCESS;
+}
+
 /* Waits for everything the runner has enqueued; false (and a destroy-only handle) when a wait fails. */
 bool drain_streams(SecantCubinRunnerImpl* r) {
     bool ok = true;
@@ -507,6 +558,8 @@ SecantResult execute(SecantCubinRunnerImpl* r, const std::vector<UnpackedRun>& r
     const double t_begin = now_seconds();
     size_t batch_size = (P + 3) / 4;
     if (batch_size < 4096) batch_size = 4096;
+    const bool gram = plan.shape == SECANT_KERNEL_SHAPE_STATIC_GRAM_STATS_F32;
+    if (gram) batch_size = (batch_size + plan.asts_per_kernel - 1) / plan.asts_per_kernel * plan.asts_per_kernel; /* whole cohorts */
     if (batch_size > P) batch_size = P;
     const size_t num_batches = (P + batch_size - 1) / batch_size;
     const bool accumulate = plan.shape != SECANT_KERNEL_SHAPE_STATIC_MATERIALIZE_F32;
@@ -575,9 +628,15 @@ SecantResult execute(SecantCubinRunnerImpl* r, const std::vector<UnpackedRun>& r
         result = upload_batch(r, *slot, &views);
         upload_seconds += now_seconds() - t_up;
         if (result != SECANT_SUCCESS) break;
-        for (const DeviceBatch& db : views) {
-            result = launch_batch(r, db, runs, &stream_cursor, slot->uploaded, &slot->done, &slot->used);
-            if (result != SECANT_SUCCESS) break;
+        if (gram) {
+            const size_t first = b * batch_size;
+            result = launch_gram_batch(r, views, runs, first, std::min(batch_size, P - first), &stream_cursor, slot->uploaded, &slot->done,
+                                       &slot->used);
+        } else {
+            for (const DeviceBatch& db : views) {
+                result = launch_batch(r, db, runs, &stream_cursor, slot->uploaded, &slot->done, &slot->used);
+                if (result != SECANT_SUCCESS) break;
+            }
         }
         in_flight.push_back(slot);
         ++launched_batches;
@@ -855,6 +914,7 @@ SecantResult secant_b200_population_create(SecantCubinRunner r, const SecantAstP
     void* ctx = current_context(&ok);
     if (!ok || ctx != r->context) return SECANT_ERROR_INVALID_STATE;
     const SecantCubinPlan& plan = *r->plan;
+    if (plan.shape == SECANT_KERNEL_SHAPE_STATIC_GRAM_STATS_F32) return SECANT_ERROR_UNSUPPORTED_SHAPE; /* cohorts go through the run entry points */
     ProgramRules rules;
     rules.num_columns = plan.num_inputs;
     rules.num_constants = plan.num_constants;

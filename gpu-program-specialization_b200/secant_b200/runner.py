@@ -16,6 +16,7 @@ _SHAPE_RECIPE = {
     abi.SHAPE_MATERIALIZE: abi.MaterializeRecipe,
     abi.SHAPE_SSE: abi.TiledRecipe,
     abi.SHAPE_AFFINE_STATS: abi.TiledRecipe,
+    abi.SHAPE_GRAM_STATS: abi.TiledRecipe,
     abi.SHAPE_TOGGLE_SSE: abi.ToggleRecipe,
 }
 
@@ -152,6 +153,14 @@ class Runner:
 
     def affine_stats(self, packed, x, y):
         out = torch.empty((len(packed.asts), 2 + y.shape[0]), dtype=torch.float32, device=x.device)
+        self.run(self.static_request(packed, x, y, out))
+        return out
+
+    def gram_stats(self, packed, x, y):
+        """[cohort][A sums | A x A Gram matrix | A x T cross sums], A = the recipe's programs per kernel."""
+        cohort = self.recipe.asts_per_kernel
+        cohorts = (len(packed.asts) + cohort - 1) // cohort
+        out = torch.full((cohorts, cohort * (1 + cohort + y.shape[0])), float("nan"), dtype=torch.float32, device=x.device)
         self.run(self.static_request(packed, x, y, out))
         return out
 

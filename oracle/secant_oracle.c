@@ -385,6 +385,58 @@ SO_EXPORT SecantResult so_affine_stats(const uint8_t* routine_blob, const uint64
     return r;
 }
 
+/* ---- Gram statistics (s_cpu.c:724-848): programs in consecutive cohorts of `cohort`; per cohort
+ * [0, A) sums, [A, A + A*A) row-major Gram matrix, then [feature][target] cross sums, all added
+ * to the caller's values row after row in float32 (products rounded first) ---- */
+SO_EXPORT SecantResult so_gram_stats(const uint8_t* routine_blob, const uint64_t* routine_off, size_t num_routines,
+                                     const uint8_t* ast_blob, const uint64_t* ast_off, size_t num_asts, size_t cohort,
+                                     size_t num_inputs, size_t num_targets, const float* input, size_t input_ld,
+                                     const float* targets, size_t targets_ld, size_t num_rows, float* stats,
+                                     size_t stats_ld, double* stats64) {
+    SoPrograms p;
+    SoEnv env;
+    float features[32];
+    size_t c, i, j, t, row;
+    SecantResult r;
+    if (!cohort || cohort > 32 || !num_inputs || num_inputs > SECANT_AST_MAX_INPUTS || !num_targets || !num_asts || !input ||
+        !targets || !stats || !num_rows || input_ld < num_rows || targets_ld < num_rows ||
+        stats_ld < cohort * (1 + cohort + num_targets))
+        return SECANT_ERROR_INVALID_VALUE;
+    r = so_programs_open(&p, routine_blob, routine_off, num_routines, ast_blob, ast_off, num_asts);
+    memset(&env, 0, sizeof(env));
+    env.routines = p.routines; env.num_routines = num_routines; env.arity = p.arity;
+    env.num_columns = num_inputs; env.input = input; env.input_ld = input_ld;
+    for (c = 0; r == SECANT_SUCCESS && c * cohort < num_asts; ++c) {
+        const size_t first = c * cohort, active = num_asts - first < cohort ? num_asts - first : cohort;
+        float* out = stats + c * stats_ld;
+        double* out64 = stats64 ? stats64 + c * stats_ld : NULL;
+        for (row = 0; r == SECANT_SUCCESS && row < num_rows; ++row) {
+            env.row = row;
+            for (i = 0; i < active && r == SECANT_SUCCESS; ++i) {
+                r = so_frame(&env, p.asts[first + i], NULL, 0, 0, &features[i]);
+                if (r != SECANT_SUCCESS) break;
+                out[i] += features[i];
+                if (out64) out64[i] += features[i];
+            }
+            if (r != SECANT_SUCCESS) break;
+            for (i = 0; i < active; ++i) {
+                for (j = 0; j < active; ++j) {
+                    const float product = features[i] * features[j];
+                    out[cohort + i * cohort + j] += product;
+                    if (out64) out64[cohort + i * cohort + j] += product;
+                }
+                for (t = 0; t < num_targets; ++t) {
+                    const float cross = features[i] * targets[t * targets_ld + row];
+                    out[cohort + cohort * cohort + i * num_targets + t] += cross;
+                    if (out64) out64[cohort + cohort * cohort + i * num_targets + t] += cross;
+                }
+            }
+        }
+    }
+    so_programs_close(&p);
+    return r;
+}
+
 /* ---- toggle SSE (s_cpu.c:851-917) ------------------------------------------------
  * Output [ast][target][configuration], configuration = bank * 2^bits + permutation.
  * Order of checks: null/zero arguments -> layout -> leading dimensions -> span overflow ->

@@ -347,4 +347,18 @@ cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem&, const Laun
 
 cudaError_t launch_rk4(const DeviceBatch&, const Rk4Problem&, size_t, cudaStream_t) { return cudaErrorUnknown; }
 
+cudaError_t launch_gram(const float* predictions, size_t prediction_ld, uint32_t, const float*, size_t, uint32_t, uint32_t, uint32_t batch_programs,
+                        float*, size_t, cudaStream_t stream) {
+    std::lock_guard<std::mutex> lock(world.mutex);
+    if (failing("launch_gram")) return cudaErrorUnknown;
+    Allocation* scratch = owner_of(predictions);
+    if (!scratch || scratch->bytes < (size_t)batch_programs * prediction_ld * sizeof(float)) {
+        violation("statistics launch with too little scratch for its predictions");
+        return cudaErrorInvalidValue;
+    }
+    merge(scratch->busy, advance(stream));
+    ++world.launches;
+    return cudaSuccess;
+}
+
 }  // namespace sb

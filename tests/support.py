@@ -96,6 +96,35 @@ def oracle_sse(packed, x, y, want64=True):
     return r, out, out64
 
 
+def oracle_gram_stats(packed, x, y, cohort):
+    """Gram statistics [cohorts][A + A*A + A*T] of programs in consecutive cohorts of `cohort`
+    (accumulated from zero); returns (code, f32, f64)."""
+    F, N = x.shape
+    T = y.shape[0]
+    cohorts = (len(packed.asts) + cohort - 1) // cohort
+    width = cohort * (1 + cohort + T)
+    out = np.zeros((cohorts, width), dtype=np.float32)
+    out64 = np.zeros((cohorts, width), dtype=np.float64)
+    r = oracle().so_gram_stats(*blob_args(packed), C.c_size_t(cohort), C.c_size_t(F), C.c_size_t(T), fptr(x), C.c_size_t(N), fptr(y),
+                               C.c_size_t(N), C.c_size_t(N), fptr(out), C.c_size_t(width), out64.ctypes.data_as(F64P))
+    return r, out, out64
+
+
+def reference_gram_stats(lib, packed, x, y, cohort):
+    """The same through the reference's own host evaluator (secant_cpu_run, Gram-statistics shape)."""
+    from secant_b200 import abi
+    F, N = x.shape
+    T = y.shape[0]
+    cohorts = (len(packed.asts) + cohort - 1) // cohort
+    width = cohort * (1 + cohort + T)
+    out = np.zeros((cohorts, width), dtype=np.float32)
+    run = abi.init_header(abi.CpuGramRun(), abi.CPU_RUN_VERSION, abi.SHAPE_GRAM_STATS)
+    packed.fill(run.programs)
+    run.asts_per_cohort, run.num_inputs, run.num_targets, run.num_rows = cohort, F, T, N
+    run.input, run.targets, run.statistics = host_matrix(x, N), host_matrix(y, N), host_matrix(out, width)
+    return lib.secant_cpu_run(C.byref(run)), out
+
+
 def oracle_toggle_sse(packed, x, y, banks, num_constants, toggle_bits, bank_stride=None, program_bank_stride=0,
                       out=None, out_ld=None):
     """Toggle SSE [asts][targets][configs]; banks: [banks][stride] (or per program)."""

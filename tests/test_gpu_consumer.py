@@ -61,3 +61,31 @@ def test_reference_search_driver_runs_on_the_drop_in(cuda):
     refined, events = _search("cuda", ("--refine-rounds", "2", "--refine-budget", "32"))
     assert refined.returncode == 0, refined.stderr[-2000:]
     assert any(e.get("event") == "result" for e in events)
+
+
+REF = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "oracle", "_ref")
+
+
+@pytest.mark.gpu
+def test_reference_runner_test_passes_against_the_drop_in(cuda):
+    """The reference's own GPU test of the runner API (projects/secant/tests/toggle_cuda_test.c,
+    compiled unmodified with the reference host evaluator and linked against this library:
+    oracle/Makefile, target `secant-tests`; oracle/secant_runner_test_shim.c calls its parts): the
+    fixture toggles with 1 and 3 programs per kernel (partial batches, ties, repeated and batched
+    runs, a malformed program), seeded random programs with 1, 8 and 32 programs per kernel, and
+    the four static shapes (materialize, SSE, affine statistics, Gram statistics), each compared
+    with the reference host evaluator.  The edge part (no columns, no constants, no toggles, a
+    toggle inside a routine) compares its scores too and then looks for the machine-code bytes of one
+    instruction in what secant_cubin_specialize_into() wrote, which a library that patches no machine
+    code cannot show: the process must end exactly there."""
+    binary = os.path.join(REF, "secant_toggle_cuda_test")
+    if not os.path.exists(binary):
+        pytest.skip("oracle/_ref/secant_toggle_cuda_test is built only where the reference checkout exists")
+    env = dict(os.environ, CUDA_MODULE_LOADING="EAGER")
+    done = subprocess.run([binary], capture_output=True, text=True, timeout=600, env=env)
+    assert done.returncode == 0, (done.stdout[-1500:], done.stderr[-1500:])
+    assert "static shape 3 passed" in done.stdout and "random toggles (packed=32)" in done.stdout
+    assert "scores of the toggle, random and static parts agree" in done.stdout
+    edge = subprocess.run([binary, "edge"], capture_output=True, text=True, timeout=600, env=env)
+    assert edge.returncode == 1 and edge.stderr.strip().endswith("toggle_cuda_test.c:521: found"), (edge.stdout[-800:], edge.stderr[-800:])
+    assert "mismatch" not in edge.stderr

@@ -170,3 +170,20 @@ def test_grouped_topk_rule_on_a_hand_checked_grid():
     assert S.oracle().so_grouped_topk(S.fptr(grid), C.c_size_t(2), C.c_size_t(2), C.c_uint32(1), C.c_uint32(1), C.c_size_t(1),
                                       S.fptr(mse), idx.ctypes.data_as(S.U64P), counts.ctypes.data_as(S.U64P)) == 0
     assert idx[:, 0].tolist() == [2, 1, 6, 2 ** 64 - 1] and counts[:, 0].tolist() == [2, 2, 1, 0]
+
+
+def test_gram_statistics_restatement_matches_the_reference_library():
+    """so_gram_stats against the reference host evaluator's Gram-statistics run (projects/secant/
+    s_cpu.c:724-848) bit for bit: cohorts of 5 with a ragged last one, two targets, routines."""
+    ref = S.reference_lib()
+    if ref is None:
+        pytest.skip("oracle/_ref/libsecant_ref.so is built only where the reference checkout exists")
+    pop = P.random_population(61, 23, 15, 4)
+    x = np.stack([P.uniform(62, c, 301, -1, 1) for c in range(4)])
+    y = np.stack([P.normal(63, t, 301) for t in range(2)])
+    code, want = S.reference_gram_stats(ref, pop, x, y, 5)
+    assert code == 0
+    code, got, _ = S.oracle_gram_stats(pop, x, y, 5)
+    assert code == 0
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert np.all(got[-1].reshape(-1)[3:5] == 0)                       # the last cohort holds 3 programs: unused sums stay zero
