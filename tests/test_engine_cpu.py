@@ -237,3 +237,18 @@ def test_launches_are_rejected_before_any_work():
         assert p.run([[(0, constant_slope(1.0)), (1, constant_slope(1.0))]], sampled)[0] == E.ERROR_INVALID_ARGUMENT
         sampled = reference_launch(sampled_parameters_device=0x5004, rng_pool_size=16, uniform_pool_device=0x6000)
         assert p.run([[(0, constant_slope(1.0)), (1, constant_slope(1.0))]], sampled)[0] == E.ERROR_INVALID_ARGUMENT
+
+
+def test_reference_handle_contract_test_passes():
+    """projects/odezza/tests/o_scoring_pipeline_test.c (a failed creation keeps a diagnostic handle
+    with a message, refuses the workspace query, can be destroyed), compiled unmodified against the
+    reference header and linked against this library (oracle/Makefile, target engine-tests); it
+    needs no device."""
+    import subprocess
+    import pytest
+    binary = os.path.join(ROOT, "oracle", "_ref", "o_scoring_pipeline_test")
+    if not os.path.exists(binary):
+        pytest.skip("oracle/_ref/o_scoring_pipeline_test is built only where the reference checkout exists")
+    done = subprocess.run([binary], capture_output=True, text=True, timeout=60)
+    assert done.returncode == 0, (done.stdout, done.stderr)
+    assert "verified" in done.stdout
