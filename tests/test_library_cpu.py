@@ -202,3 +202,21 @@ def test_extension_fields_default_to_reference_behaviour():
     assert validate(recipe, ext) == abi.ERROR_INSUFFICIENT_BUFFER  # two tables no longer fit in 38 elements
     ext.base.constants.num_elements = 39 + 38
     assert validate(recipe, ext) == 0
+
+
+def test_reference_header_tests_pass_against_this_include_directory():
+    """projects/secant/tests/c_header_test.c and cpp_header_test.cpp (descriptor layouts and
+    initialisers, bytecode encoders, the entry points that need no device), compiled unmodified
+    against include/ of this repository - where secant.h and secant_instructions.h forward to
+    secant_b200.h - as C99 with -Wpedantic -Werror and as C++17, and linked against the library
+    (oracle/Makefile, target header-tests)."""
+    import subprocess
+    import pytest
+    ran = 0
+    for name in ("secant_c_header_test", "secant_cpp_header_test"):
+        binary = os.path.join(ROOT, "oracle", "_ref", name)
+        if os.path.exists(binary):
+            assert subprocess.run([binary], timeout=60).returncode == 0, name
+            ran += 1
+    if not ran:
+        pytest.skip("oracle/_ref/secant_*_header_test are built only where the reference checkout exists")
