@@ -11,9 +11,9 @@
  * other operand is a leaf costs one instruction, a node with two computed operands spills the
  * first through a slot.  The deeper operand is evaluated first (Sethi-Ullman order), which only
  * changes the order pure sub-expressions are computed in, never how values are rounded or
- * associated.  For the population evaluator the instructions go to three runs (record.h):
- * bank-only sub-expressions to the bank part, row-only ones to the row prelude, the rest to
- * the main part.
+ * associated.  For the population evaluator the instructions go to up to four runs (record.h):
+ * bank-only sub-expressions to the bank part, row-only ones to the shared row prelude (no toggle
+ * reaches them) or the row prelude, the rest to the main part.
  */
 #include "encoder.h"
 
