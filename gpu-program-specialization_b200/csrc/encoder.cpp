@@ -677,7 +677,7 @@ SecantResult encode_program(const SecantAstInstruction* program, const SecantAst
     Emitter em(nodes, rules, out, (unsigned)affines.size());
     em.slots_high = rules.reserved_slots;
     const ValueClass root_class = em.classify(root);
-    if (rules.split_parts && !rules.columns_are_slots) {
+    if (rules.split_parts) { /* rollout records (columns_are_slots) have no row-only class: only bank roots turn up */
         std::vector<int> bank_roots, row_roots;
         std::vector<uint8_t> seen(nodes.size(), 0);
         em.collect(root, false, bank_roots, row_roots, seen);

@@ -160,8 +160,9 @@ struct Rk4Problem {
     unsigned long long* integrated; /* optional device counter: (trajectory, observation interval) pairs integrated */
 };
 /* batch.programs holds num_systems * num_states records, system-major, encoded with
- * columns_are_slots and 5 * num_states reserved slots. */
-cudaError_t launch_rk4(const DeviceBatch& batch, const Rk4Problem& problem, size_t smem_limit, cudaStream_t stream);
+ * columns_are_slots, 4 * num_states reserved slots and a bank part.  `concurrent` = how many such
+ * launches share the device at a time (the launch takes that share of the resident CTAs). */
+cudaError_t launch_rk4(const DeviceBatch& batch, const Rk4Problem& problem, size_t smem_limit, unsigned concurrent, cudaStream_t stream);
 
 /* Adds the statistics of the static Gram shape for a batch of cohorts over `rows` rows of
  * materialized predictions [program of the batch][prediction_ld] (gram.cu); statistics points at

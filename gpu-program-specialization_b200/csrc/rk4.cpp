@@ -78,12 +78,10 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
     rules.toggle_bits = run->toggle_bits;
     rules.columns_are_slots = true;
     rules.reserved_slots = (unsigned)(4 * S); /* stage, next stage, sum, state vectors */
+    rules.split_parts = true;                 /* what depends on the constants only is computed once per candidate, */
+    rules.hoist_bank = true;                  /* not once per stage */
     for (size_t i = 0; i < programs.routines.count; ++i) {
         const SecantResult r = preflight(programs.routines.items[i], rules);
-        if (r != SECANT_SUCCESS) return r;
-    }
-    for (size_t i = 0; i < programs.asts.count; ++i) {
-        const SecantResult r = preflight(programs.asts.items[i], rules);
         if (r != SECANT_SUCCESS) return r;
     }
     uint8_t arity[SECANT_AST_MAX_ROUTINES];
@@ -95,40 +93,63 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
         cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess)
         return SECANT_ERROR_DRIVER_FAILED;
 
-    /* Systems are encoded in chunks by a few host threads while the calling thread uploads and
-     * launches the chunks in order on one stream, so encoding overlaps the kernels of earlier
-     * chunks.  A structural error found while encoding a later chunk ends the call with that code;
-     * scores of earlier chunks may already have been written. */
-    constexpr size_t kChunkSystems = 2048;
-    const size_t num_chunks = (run->num_systems + kChunkSystems - 1) / kChunkSystems;
-    struct Chunk {
+    /* Host threads work on pieces of 512 systems: first every piece is scanned (nothing is launched
+     * before every program has passed the scan, and the first failing program in order decides the
+     * result), then the pieces are encoded while the calling thread joins four encoded pieces into
+     * one launch, uploads it and starts its kernels, so encoding overlaps the kernels of earlier
+     * launches.  A structural error found while encoding a later piece ends the call with that
+     * code; scores of earlier launches may already have been written. */
+    constexpr size_t kPieceSystems = 512, kPiecesPerLaunch = 4;
+    const size_t num_pieces = (run->num_systems + kPieceSystems - 1) / kPieceSystems;
+    const size_t num_chunks = (num_pieces + kPiecesPerLaunch - 1) / kPiecesPerLaunch;
+    struct Piece {
         EncodedBatch enc;
         SecantResult status = SECANT_SUCCESS;
+    };
+    struct Chunk {
         std::vector<char> host;
         char* device = nullptr;
     };
+    std::vector<Piece> pieces;
     std::vector<Chunk> chunks;
     std::mutex mutex;
     std::condition_variable ready;
-    std::vector<char> done;
-    std::atomic<size_t> next_chunk{0};
+    std::vector<char> done;          /* piece encoded */
+    size_t scanned = 0;              /* pieces scanned */
+    bool encoding_open = false;      /* every piece passed the scan */
+    std::atomic<size_t> next_scan{0}, next_piece{0};
     std::atomic<bool> stop{false};
     try {
+        pieces.resize(num_pieces);
         chunks.resize(num_chunks);
-        done.assign(num_chunks, 0);
+        done.assign(num_pieces, 0);
     } catch (const std::bad_alloc&) {
         return SECANT_ERROR_ALLOCATION_FAILED;
     }
+    auto piece_range = [&](size_t c, size_t* first, size_t* count) {
+        *first = c * kPieceSystems * S;
+        *count = std::min(kPieceSystems, run->num_systems - c * kPieceSystems) * S;
+    };
+    auto scan_one = [&](size_t c) {
+        size_t first, count;
+        piece_range(c, &first, &count);
+        SecantResult r = SECANT_SUCCESS;
+        for (size_t i = 0; i < count && r == SECANT_SUCCESS; ++i) r = preflight(programs.asts.items[first + i], rules);
+        std::lock_guard<std::mutex> lock(mutex);
+        pieces[c].status = r;
+        ++scanned;
+        if (scanned == num_pieces) ready.notify_all();
+    };
     auto encode_one = [&](size_t c) {
-        Chunk& chunk = chunks[c];
-        const size_t first = c * kChunkSystems * S;
-        const size_t count = std::min(kChunkSystems, run->num_systems - c * kChunkSystems) * S;
+        Piece& piece = pieces[c];
+        size_t first, count;
+        piece_range(c, &first, &count);
         try {
-            chunk.enc.programs.reserve(count);
-            for (size_t i = 0; i < count && chunk.status == SECANT_SUCCESS; ++i)
-                chunk.status = encode_program(programs.asts.items[first + i], programs.routines, arity, rules, chunk.enc);
+            piece.enc.programs.reserve(count);
+            for (size_t i = 0; i < count && piece.status == SECANT_SUCCESS; ++i)
+                piece.status = encode_program(programs.asts.items[first + i], programs.routines, arity, rules, piece.enc);
         } catch (const std::bad_alloc&) {
-            chunk.status = SECANT_ERROR_ALLOCATION_FAILED;
+            piece.status = SECANT_ERROR_ALLOCATION_FAILED;
         }
         {
             std::lock_guard<std::mutex> lock(mutex);
@@ -136,28 +157,54 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
         }
         ready.notify_all();
     };
-    auto encode_chunks = [&]() {
+    auto scan_pieces = [&]() {
         for (;;) {
-            const size_t c = next_chunk.fetch_add(1);
-            if (c >= num_chunks || stop.load()) return;
+            const size_t c = next_scan.fetch_add(1);
+            if (c >= num_pieces) return;
+            scan_one(c);
+        }
+    };
+    auto worker = [&]() {
+        scan_pieces();
+        {
+            std::unique_lock<std::mutex> lock(mutex);
+            ready.wait(lock, [&] { return encoding_open || stop.load(); });
+        }
+        for (;;) {
+            const size_t c = next_piece.fetch_add(1);
+            if (c >= num_pieces || stop.load()) return;
             encode_one(c);
         }
     };
     std::vector<std::thread> workers;
     const unsigned hardware = std::thread::hardware_concurrency();
-    const size_t want_workers = std::min<size_t>(num_chunks > 1 ? num_chunks - 1 : 0, std::min<unsigned>(hardware ? hardware : 1u, 8u));
+    const size_t want_workers = std::min<size_t>(num_pieces > 1 ? num_pieces - 1 : 0, std::min<unsigned>(hardware ? hardware : 1u, 16u) - 1u);
     try {
         workers.reserve(want_workers);
-        for (size_t w = 0; w < want_workers; ++w) workers.emplace_back(encode_chunks);
+        for (size_t w = 0; w < want_workers; ++w) workers.emplace_back(worker);
     } catch (const std::exception&) {
-        /* no memory or no thread to be had: fewer helpers, or none; the calling thread encodes whatever is left */
+        /* no memory or no thread to be had: fewer helpers, or none; the calling thread does whatever is left */
+    }
+    scan_pieces();
+    {
+        std::unique_lock<std::mutex> lock(mutex);
+        ready.wait(lock, [&] { return scanned == num_pieces; });
+        for (size_t c = 0; c < num_pieces && result == SECANT_SUCCESS; ++c) result = pieces[c].status; /* the first failing program in order */
+        if (result == SECANT_SUCCESS) encoding_open = true;
+        else stop.store(true);
+    }
+    ready.notify_all();
+    if (result != SECANT_SUCCESS) {
+        for (std::thread& t : workers) t.join();
+        return result;
     }
 
     /* records travel on their own stream, so an upload never waits for the kernels of earlier chunks;
      * the chunks' kernels go round the compute streams, so a chunk smaller than the GPU shares it
      * with its neighbours */
-    constexpr int kComputeStreams = 4;
-    cudaStream_t compute[kComputeStreams] = {nullptr, nullptr, nullptr, nullptr}, copies = nullptr;
+    constexpr int kComputeStreams = 8;
+    cudaStream_t compute[kComputeStreams] = {}, copies = nullptr;
+    const unsigned concurrent = (unsigned)std::min<size_t>(num_chunks, kComputeStreams);
     cudaEvent_t uploaded = nullptr;
     cudaError_t e = cudaStreamCreateWithFlags(&copies, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&uploaded, cudaEventDisableTiming);
@@ -171,27 +218,41 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
     auto align256 = [](size_t v) { return (v + 255) / 256 * 256; };
     unsigned launches = 0;
     for (size_t c = 0; c < num_chunks && e == cudaSuccess && result == SECANT_SUCCESS; ++c) {
-        for (;;) { /* wait for chunk c; while it is in other hands, encode chunks nobody has taken */
-            {
-                std::lock_guard<std::mutex> lock(mutex);
-                if (done[c]) break;
+        const size_t piece0 = c * kPiecesPerLaunch, piece1 = std::min(num_pieces, piece0 + kPiecesPerLaunch);
+        for (size_t q = piece0; q < piece1; ++q)
+            for (;;) { /* wait for piece q; while it is in other hands, encode pieces nobody has taken */
+                {
+                    std::lock_guard<std::mutex> lock(mutex);
+                    if (done[q]) break;
+                }
+                const size_t mine = next_piece.fetch_add(1);
+                if (mine < num_pieces) {
+                    encode_one(mine);
+                } else {
+                    std::unique_lock<std::mutex> lock(mutex);
+                    ready.wait(lock, [&] { return done[q] != 0; });
+                }
             }
-            const size_t mine = next_chunk.fetch_add(1);
-            if (mine < num_chunks) {
-                encode_one(mine);
-            } else {
-                std::unique_lock<std::mutex> lock(mutex);
-                ready.wait(lock, [&] { return done[c] != 0; });
-            }
+        for (size_t q = piece0; q < piece1 && result == SECANT_SUCCESS; ++q) result = pieces[q].status;
+        if (result != SECANT_SUCCESS) break;
+        /* the pieces' arrays joined section by section; a program's offsets move by what lies before its piece */
+        EncodedBatch enc; /* totals and maxima only */
+        size_t n_programs = 0, n_insns = 0, n_patches = 0, n_affines = 0, n_lits = 0;
+        for (size_t q = piece0; q < piece1; ++q) {
+            const EncodedBatch& part = pieces[q].enc;
+            n_programs += part.programs.size(); n_insns += part.insns.size(); n_patches += part.patches.size();
+            n_affines += part.affines.size(); n_lits += part.lits.size();
+            enc.max_insn = std::max(enc.max_insn, part.max_insn); enc.max_extra = std::max(enc.max_extra, part.max_extra);
+            enc.max_slots = std::max(enc.max_slots, part.max_slots); enc.max_cst = std::max(enc.max_cst, part.max_cst);
+            enc.max_btmp = std::max(enc.max_btmp, part.max_btmp);
         }
+        if (n_insns > 0xffffffffull || n_patches > 0xffffffffull || n_affines > 0xffffffffull || n_lits > 0xffffffffull) { result = SECANT_ERROR_OVERFLOW; break; }
         Chunk& chunk = chunks[c];
-        if (chunk.status != SECANT_SUCCESS) { result = chunk.status; break; }
-        const EncodedBatch& enc = chunk.enc;
-        const size_t o_insn = align256(enc.programs.size() * sizeof(SbProgram));
-        const size_t o_patch = align256(o_insn + enc.insns.size() * sizeof(SbInsn));
-        const size_t o_aff = align256(o_patch + enc.patches.size() * sizeof(SbPatch));
-        const size_t o_lit = align256(o_aff + enc.affines.size() * sizeof(SbAffine));
-        const size_t o_flag = align256(o_lit + enc.lits.size() * sizeof(float) + 16); /* one word raised by the data validation */
+        const size_t o_insn = align256(n_programs * sizeof(SbProgram));
+        const size_t o_patch = align256(o_insn + n_insns * sizeof(SbInsn));
+        const size_t o_aff = align256(o_patch + n_patches * sizeof(SbPatch));
+        const size_t o_lit = align256(o_aff + n_affines * sizeof(SbAffine));
+        const size_t o_flag = align256(o_lit + n_lits * sizeof(float) + 16); /* one word raised by the data validation */
         const size_t total = o_flag + 256;
         try {
             chunk.host.assign(total, 0);
@@ -200,11 +261,26 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
             break;
         }
         char* host = chunk.host.data();
-        std::memcpy(host, enc.programs.data(), enc.programs.size() * sizeof(SbProgram));
-        std::memcpy(host + o_insn, enc.insns.data(), enc.insns.size() * sizeof(SbInsn));
-        if (!enc.patches.empty()) std::memcpy(host + o_patch, enc.patches.data(), enc.patches.size() * sizeof(SbPatch));
-        if (!enc.affines.empty()) std::memcpy(host + o_aff, enc.affines.data(), enc.affines.size() * sizeof(SbAffine));
-        if (!enc.lits.empty()) std::memcpy(host + o_lit, enc.lits.data(), enc.lits.size() * sizeof(float));
+        {
+            size_t at_program = 0, at_insn = 0, at_patch = 0, at_affine = 0, at_lit = 0;
+            for (size_t q = piece0; q < piece1; ++q) {
+                EncodedBatch& part = pieces[q].enc;
+                SbProgram* out = reinterpret_cast<SbProgram*>(host) + at_program;
+                for (size_t i = 0; i < part.programs.size(); ++i) {
+                    SbProgram pr = part.programs[i];
+                    pr.insn_off += (uint32_t)at_insn; pr.patch_off += (uint32_t)at_patch;
+                    pr.affine_off += (uint32_t)at_affine; pr.lit_off += (uint32_t)at_lit;
+                    out[i] = pr;
+                }
+                if (!part.insns.empty()) std::memcpy(host + o_insn + at_insn * sizeof(SbInsn), part.insns.data(), part.insns.size() * sizeof(SbInsn));
+                if (!part.patches.empty()) std::memcpy(host + o_patch + at_patch * sizeof(SbPatch), part.patches.data(), part.patches.size() * sizeof(SbPatch));
+                if (!part.affines.empty()) std::memcpy(host + o_aff + at_affine * sizeof(SbAffine), part.affines.data(), part.affines.size() * sizeof(SbAffine));
+                if (!part.lits.empty()) std::memcpy(host + o_lit + at_lit * sizeof(float), part.lits.data(), part.lits.size() * sizeof(float));
+                at_program += part.programs.size(); at_insn += part.insns.size(); at_patch += part.patches.size();
+                at_affine += part.affines.size(); at_lit += part.lits.size();
+                part = EncodedBatch(); /* the piece's own copy is not needed any more */
+            }
+        }
         if (cudaMalloc(&chunk.device, total) != cudaSuccess) { result = SECANT_ERROR_ALLOCATION_FAILED; break; }
         char* d = chunk.device;
         e = cudaMemcpyAsync(d, host, total, cudaMemcpyHostToDevice, copies);
@@ -212,8 +288,8 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
         cudaStream_t stream = compute[c % kComputeStreams];
         if (e == cudaSuccess) e = cudaStreamWaitEvent(stream, uploaded, 0);
         if (e != cudaSuccess) break;
-        const size_t first_system = c * kChunkSystems;
-        const size_t systems = enc.programs.size() / S;
+        const size_t first_system = piece0 * kPieceSystems;
+        const size_t systems = n_programs / S;
         DeviceBatch db;
         std::memset(&db, 0, sizeof(db));
         db.programs = reinterpret_cast<const SbProgram*>(d);
@@ -221,11 +297,13 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
         db.patches = reinterpret_cast<const SbPatch*>(d + o_patch);
         db.affines = reinterpret_cast<const SbAffine*>(d + o_aff);
         db.lits = reinterpret_cast<const float*>(d + o_lit);
-        db.num_programs = (uint32_t)enc.programs.size();
+        db.num_programs = (uint32_t)n_programs;
         db.max_insn = enc.max_insn;
         db.max_extra = enc.max_extra;
         db.max_slots = enc.max_slots > rules.reserved_slots ? enc.max_slots : rules.reserved_slots;
         db.max_hoisted = 0;
+        db.max_cst = enc.max_cst;
+        db.max_btmp = enc.max_btmp;
         Rk4Problem p;
         p.num_systems = (uint32_t)systems; p.num_states = (uint32_t)S; p.num_constants = (uint32_t)K;
         p.num_banks = (uint32_t)run->num_banks; p.toggle_bits = run->toggle_bits;
@@ -249,7 +327,7 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
         p.output = reinterpret_cast<float*>(run->output.address) + first_system * run->output.leading_dimension;
         p.output_ld = run->output.leading_dimension;
         p.integrated = reinterpret_cast<unsigned long long*>(run->integrated_intervals);
-        e = launch_rk4(db, p, (size_t)limit, stream);
+        e = launch_rk4(db, p, (size_t)limit, concurrent, stream);
         if (e == cudaErrorInvalidConfiguration) { result = SECANT_ERROR_REGISTER_OVERFLOW; e = cudaSuccess; break; }
         if (e == cudaSuccess) launches += 2;
     }

@@ -123,13 +123,51 @@ __device__ __noinline__ float2 unary2(float2 v, unsigned op) {
 }
 __device__ __noinline__ float2 div2(float2 a, float2 b) { return make_float2(__fdiv_rn(a.x, b.x), __fdiv_rn(a.y, b.y)); }
 
+/* ---- shared memory by 32-bit shared-window address ------------------------------------------
+ * The interpreter's operands, the integrator's vectors and the instruction stream itself are read
+ * through these, so address arithmetic stays 32 bits wide and an operand's address can be stored
+ * ready-made in the instruction word. */
+__device__ __forceinline__ uint32_t shared_address(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+template <int RR>
+__device__ __forceinline__ void lds(uint32_t a, float (&x)[RR]) {
+    if constexpr (RR == 4) asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x[0]), "=f"(x[1]), "=f"(x[2]), "=f"(x[3]) : "r"(a));
+    else if constexpr (RR == 2) asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(x[0]), "=f"(x[1]) : "r"(a));
+    else asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x[0]) : "r"(a));
+}
+template <int RR>
+__device__ __forceinline__ void sts(uint32_t a, const float (&x)[RR]) {
+    if constexpr (RR == 4) asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
+    else if constexpr (RR == 2) asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(a), "f"(x[0]), "f"(x[1]) : "memory");
+    else asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(x[0]) : "memory");
+}
+__device__ __forceinline__ void lds_pair(uint32_t a, uint32_t& lo, uint32_t& hi) {
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(a));
+}
+__device__ __forceinline__ uint32_t lds_word(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+
+/* Handlers of the rollout machine.  A warp rewrites the main part of its private copy of a record
+ * once per item into this form: word 0 = handler (bits 0..7) and, for H_UNARY, the function (bits
+ * 8..15); word 1 = the operand's shared-window address, with bit 31 set when every lane reads its own
+ * RR floats of a slot (the lane's offset is added) and clear when all lanes read one table entry.
+ * H_FMA keeps the record's form (operand kinds in bits 8..13 of word 0, three 10-bit indices in
+ * word 1).  One item runs its right-hand sides states x 4 stages x steps times, so the rewrite is free
+ * and the dispatch per instruction is an address add, one load and one dense switch. */
+enum { H_END = 0, H_STORE, H_LOAD, H_ADD, H_SUB, H_RSUB, H_MUL, H_DIV, H_RDIV, H_MIN, H_MAX, H_NEG, H_ABS, H_UNARY, H_FMA };
+constexpr uint32_t kPerLane = 0x80000000u;
+
 template <int RR>
 struct Rollout {
     float acc[RR];
-    float* slots; /* this lane's RR floats of slot 0; slot s lies s * 32 * RR floats further */
+    uint32_t lane_off; /* byte offset of this lane's RR floats inside a slot */
+    uint32_t slot0;    /* shared address of slot 0; slot s lies s * 32 * RR floats further */
 
-    __device__ __forceinline__ void get(uint32_t s, float (&x)[RR]) const { load_lanes<RR>(slots + (size_t)s * (32 * RR), x); }
-    __device__ __forceinline__ void put(uint32_t s, const float (&x)[RR]) const { store_lanes<RR>(slots + (size_t)s * (32 * RR), x); }
+    __device__ __forceinline__ uint32_t slot_address(uint32_t s) const { return slot0 + s * (uint32_t)(RR * 128) + lane_off; }
+    __device__ __forceinline__ void get(uint32_t s, float (&x)[RR]) const { lds<RR>(slot_address(s), x); }
+    __device__ __forceinline__ void put(uint32_t s, const float (&x)[RR]) const { sts<RR>(slot_address(s), x); }
 
     __device__ __forceinline__ void apply_unary(unsigned op) {
         if constexpr (RR == 4) {
@@ -155,97 +193,156 @@ struct Rollout {
         }
     }
 
-    /* acc = value of the record at `exec` with constants `cst` */
-    __device__ __forceinline__ void run(const SbInsn* exec, const float* cst) {
-        const uint2* ip = reinterpret_cast<const uint2*>(exec);
-        uint2 next = *ip++; /* the buffer holds one padding entry after the END */
+    /* acc = value of the rewritten main part that starts at shared address `ip`; `table` is the
+     * shared address of the program's constant table (RR copies of every entry) */
+    __device__ __forceinline__ void run(uint32_t ip, uint32_t table) {
+        uint32_t n0, n1;
+        lds_pair(ip, n0, n1); /* the buffer holds one padding entry after the END */
+        ip += 8;
 #pragma unroll 1
         for (;;) {
-            const uint2 ins = next;
-            next = *ip++;
-            const unsigned cs = ins.x & 0xffu;
-            const uint32_t idx = ins.x >> 16;
-            if (cs == SB_CASE_END) return;
-            if (cs == SB_CASE_STORE) { put(idx, acc); continue; }
-            if (cs >= SB_CASE_UN) {
-                if (cs == SB_CASE_FMA) { fused(ins); continue; }
-                const unsigned op = cs - SB_CASE_UN;
-                if (op == SB_UN_NEG) {
-#pragma unroll
-                    for (int q = 0; q < RR; ++q) acc[q] = -acc[q];
-                } else if (op == SB_UN_ABS) {
-#pragma unroll
-                    for (int q = 0; q < RR; ++q) acc[q] = fabsf(acc[q]);
-                } else apply_unary(op);
-                continue;
-            }
-            /* a load or a binary operation: fetch the operand, then apply */
-            const unsigned rel = cs < SB_CASE_BIN ? cs - SB_CASE_LOAD : (cs - SB_CASE_BIN) % SB_NUM_KINDS;
+            const uint32_t w0 = n0, w1 = n1;
+            lds_pair(ip, n0, n1);
+            ip += 8;
+            const unsigned handler = w0 & 0xffu;
             float x[RR];
-            if (rel == SB_KIND_CST) {
-                const float c = cst[idx];
-#pragma unroll
-                for (int q = 0; q < RR; ++q) x[q] = c;
-            } else get(idx, x);
-            if (cs < SB_CASE_BIN) {
+            if (handler != H_FMA) lds<RR>((w1 & 0x00ffffffu) + ((uint32_t)((int32_t)w1 >> 31) & lane_off), x);
+            switch (handler) {
+            case H_END: return;
+            case H_STORE: sts<RR>((w1 & 0x00ffffffu) + lane_off, acc); break;
+            case H_LOAD:
 #pragma unroll
                 for (int q = 0; q < RR; ++q) acc[q] = x[q];
-                continue;
-            }
-            switch ((cs - SB_CASE_BIN) / SB_NUM_KINDS) {
-            case SB_BIN_ADD:
+                break;
+            case H_ADD:
 #pragma unroll
                 for (int q = 0; q < RR; ++q) acc[q] = __fadd_rn(acc[q], x[q]);
                 break;
-            case SB_BIN_SUB:
+            case H_SUB:
 #pragma unroll
                 for (int q = 0; q < RR; ++q) acc[q] = __fsub_rn(acc[q], x[q]);
                 break;
-            case SB_BIN_RSUB:
+            case H_RSUB:
 #pragma unroll
                 for (int q = 0; q < RR; ++q) acc[q] = __fsub_rn(x[q], acc[q]);
                 break;
-            case SB_BIN_MUL:
+            case H_MUL:
 #pragma unroll
                 for (int q = 0; q < RR; ++q) acc[q] = __fmul_rn(acc[q], x[q]);
                 break;
-            case SB_BIN_DIV: divide(acc, x); break;
-            case SB_BIN_RDIV: divide(x, acc); break;
-            case SB_BIN_MIN:
+            case H_DIV: divide(acc, x); break;
+            case H_RDIV: divide(x, acc); break;
+            case H_MIN:
 #pragma unroll
                 for (int q = 0; q < RR; ++q) acc[q] = fminf(acc[q], x[q]);
                 break;
-            default:
+            case H_MAX:
 #pragma unroll
                 for (int q = 0; q < RR; ++q) acc[q] = fmaxf(acc[q], x[q]);
                 break;
+            case H_NEG:
+#pragma unroll
+                for (int q = 0; q < RR; ++q) acc[q] = -acc[q];
+                break;
+            case H_ABS:
+#pragma unroll
+                for (int q = 0; q < RR; ++q) acc[q] = fabsf(acc[q]);
+                break;
+            case H_UNARY: apply_unary((w0 >> 8) & 0xffu); break;
+            case H_FMA: fused(w0, w1, table); break;
+            default: return; /* unreachable for records produced by the encoder */
             }
         }
     }
 
-    const float* cst_of_run = nullptr;
-
-    /* FMA_F32 over three operands of any kind (constant, slot, or the accumulator) */
-    __device__ __forceinline__ void fused(uint2 ins) {
-        const unsigned kinds = (ins.x >> 8) & 0x3fu;
+    /* FMA_F32 over three operands of any kind (table entry, slot, or the accumulator) */
+    __device__ __forceinline__ void fused(uint32_t w0, uint32_t w1, uint32_t table) {
+        const unsigned kinds = (w0 >> 8) & 0x3fu;
         float v[3][RR];
 #pragma unroll
         for (int i = 0; i < 3; ++i) {
             const unsigned kind = (kinds >> (2 * i)) & 3u;
-            const uint32_t index = (ins.y >> (10 * i)) & 1023u;
-            if (kind == SB_KIND_CST) {
-                const float c = cst_of_run[index];
-#pragma unroll
-                for (int q = 0; q < RR; ++q) v[i][q] = c;
-            } else if (kind == SB_FMA_ACC) {
+            const uint32_t index = (w1 >> (10 * i)) & 1023u;
+            if (kind == SB_FMA_ACC) {
 #pragma unroll
                 for (int q = 0; q < RR; ++q) v[i][q] = acc[q];
-            } else get(index, v[i]);
+            } else if (kind == SB_KIND_CST) lds<RR>(table + index * (uint32_t)(RR * 4), v[i]);
+            else get(index, v[i]);
         }
 #pragma unroll
         for (int q = 0; q < RR; ++q) acc[q] = __fmaf_rn(v[0][q], v[1][q], v[2][q]);
     }
 };
+
+/* Rewrites instruction `in` of a record's main part for the machine above. */
+template <int RR>
+__device__ __forceinline__ SbInsn rewritten(SbInsn in, uint32_t table, uint32_t slot0) {
+    const unsigned cs = in.w0 & 0xffu;
+    const uint32_t idx = in.w0 >> 16;
+    unsigned handler = H_END, aux = 0, kind = SB_NUM_KINDS; /* SB_NUM_KINDS: no operand */
+    if (cs >= SB_CASE_LOAD && cs < SB_CASE_STORE) { handler = H_LOAD; kind = cs - SB_CASE_LOAD; }
+    else if (cs == SB_CASE_STORE) { handler = H_STORE; kind = SB_KIND_SLOT; }
+    else if (cs >= SB_CASE_BIN && cs < SB_CASE_UN) { handler = H_ADD + (cs - SB_CASE_BIN) / SB_NUM_KINDS; kind = (cs - SB_CASE_BIN) % SB_NUM_KINDS; }
+    else if (cs >= SB_CASE_UN && cs < SB_CASE_FMA) {
+        aux = cs - SB_CASE_UN;
+        handler = aux == SB_UN_NEG ? H_NEG : aux == SB_UN_ABS ? H_ABS : H_UNARY;
+    } else if (cs == SB_CASE_FMA) return SbInsn{(in.w0 & 0xffffff00u) | H_FMA, in.w1};
+    if (kind == SB_KIND_ROW) handler = H_END; /* rollout records have no per-row operands */
+    uint32_t operand = table; /* instructions without an operand read (and ignore) the table's first entry */
+    if (kind == SB_KIND_CST) operand = table + idx * (uint32_t)(RR * 4);
+    if (kind == SB_KIND_SLOT) operand = (slot0 + idx * (uint32_t)(RR * 128)) | kPerLane;
+    return SbInsn{handler | (aux << 8), operand};
+}
+
+/* The bank part of a record (record.h): sub-expressions that depend on the candidate's constants
+ * only, computed once per item instead of once per stage.  Every lane runs it on the same values
+ * (no divergence, no exchange) and stores the same results: table entry e as RR adjacent copies, so
+ * the main part reads a constant with the load it uses for a lane's slot values.  Operand kinds of
+ * the bank part: CST = source constant (bank slots, affine entries, literals), ROW = table entry
+ * written earlier, SLOT = scalar temporary.  The functions are the scalar pieces the wider
+ * machines use, so a value has the bits it would have had in the main part. */
+__device__ __noinline__ void rollout_bank_part(const SbInsn* code, const float* source, float* tmp, float* table, int copies) {
+    float acc = 0.0f;
+    auto operand = [&](unsigned kind, uint32_t idx) -> float {
+        return kind == SB_KIND_ROW ? table[idx * copies] : kind == SB_KIND_SLOT ? tmp[idx] : source[idx];
+    };
+#pragma unroll 1
+    for (;; ++code) {
+        const SbInsn ins = *code;
+        const unsigned cs = ins.w0 & 0xffu;
+        const uint32_t idx = ins.w0 >> 16;
+        if (cs == SB_CASE_END || cs > SB_CASE_FMA) return;
+        if (cs < SB_CASE_STORE) acc = operand(cs - SB_CASE_LOAD, idx);
+        else if (cs == SB_CASE_STORE) tmp[idx] = acc;
+        else if (cs == SB_CASE_STOREH) {
+            for (int q = 0; q < copies; ++q) table[idx * copies + q] = acc;
+        } else if (cs < SB_CASE_UN) {
+            const float x = operand((cs - SB_CASE_BIN) % SB_NUM_KINDS, idx);
+            switch ((cs - SB_CASE_BIN) / SB_NUM_KINDS) {
+            case SB_BIN_ADD: acc = __fadd_rn(acc, x); break;
+            case SB_BIN_SUB: acc = __fsub_rn(acc, x); break;
+            case SB_BIN_RSUB: acc = __fsub_rn(x, acc); break;
+            case SB_BIN_MUL: acc = __fmul_rn(acc, x); break;
+            case SB_BIN_DIV: acc = div1(acc, x); break;
+            case SB_BIN_RDIV: acc = div1(x, acc); break;
+            case SB_BIN_MIN: acc = fminf(acc, x); break;
+            default: acc = fmaxf(acc, x); break;
+            }
+        } else if (cs < SB_CASE_FMA) {
+            const unsigned op = cs - SB_CASE_UN;
+            acc = op == SB_UN_NEG ? -acc : op == SB_UN_ABS ? fabsf(acc) : unary1(acc, op);
+        } else {
+            const unsigned kinds = (ins.w0 >> 8) & 0x3fu;
+            float v[3];
+#pragma unroll
+            for (int i = 0; i < 3; ++i) {
+                const unsigned kind = (kinds >> (2 * i)) & 3u;
+                v[i] = kind == SB_FMA_ACC ? acc : operand(kind, (ins.w1 >> (10 * i)) & 1023u);
+            }
+            acc = __fmaf_rn(v[0], v[1], v[2]);
+        }
+    }
+}
 
 /* projects/odezza/core/o_sampled_constants_source.h:32-44 */
 __device__ __forceinline__ float sampled_constant(const Rk4Problem& prob, unsigned long long index, uint32_t bank) {
@@ -259,14 +356,27 @@ __device__ __forceinline__ float sampled_constant(const Rk4Problem& prob, unsign
     return fminf(p.upper, fmaxf(p.lower, value));
 }
 
+/* Shared memory of one warp, in this order: per state the record (exec_bytes) and the constant
+ * table (table_bytes); then one area for the source constants of the record being set up and the
+ * bank part's temporaries (source_bytes), the main parts' start addresses (16 words), the slots. */
+struct RolloutLayout {
+    uint32_t exec_bytes, table_bytes, source_bytes, warp_bytes;
+};
+
 template <int RR>
 __global__ void __launch_bounds__(kRolloutMaxWarps * 32, RR == 4 ? 1 : 2)
-rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, uint32_t cst_bytes, uint32_t warp_bytes) {
+rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, const RolloutLayout lay) {
     constexpr uint32_t PASS = 32 * RR; /* trajectories of one pass */
     extern __shared__ __align__(16) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t S = prob.num_states, K = prob.num_constants;
-    unsigned char* const warea = smem + (size_t)warp * warp_bytes;
+    unsigned char* const warea = smem + (size_t)warp * lay.warp_bytes;
+    unsigned char* const tables = warea + (size_t)S * lay.exec_bytes;
+    float* const source = reinterpret_cast<float*>(tables + (size_t)S * lay.table_bytes);
+    float* const tmp = source + K + batch.max_extra;
+    uint32_t* const starts = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(source) + lay.source_bytes);
+    float* const slot_area = reinterpret_cast<float*>(starts + 16);
+    const uint32_t slot0 = shared_address(slot_area);
     const unsigned long long configs = (unsigned long long)prob.num_banks << prob.toggle_bits;
     const unsigned long long num_items = configs * prob.num_systems;
     unsigned int integrated = 0; /* (trajectory, observation interval) pairs this lane carried out */
@@ -283,10 +393,12 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, 
     const uint32_t bank = (uint32_t)(cfg >> prob.toggle_bits);
     const float* bank_ptr = prob.banks ? prob.banks + (size_t)sys * prob.system_bank_stride + (size_t)bank * prob.bank_stride : nullptr;
 
-    for (uint32_t s = 0; s < S; ++s) { /* private copy of every right-hand side, toggles resolved, constants staged */
+    /* private copy of every right-hand side: toggles resolved, the bank part run once, the main
+     * part rewritten for the machine */
+    for (uint32_t s = 0; s < S; ++s) {
         const SbProgram pr = batch.programs[sys * S + s];
-        SbInsn* exec = reinterpret_cast<SbInsn*>(warea + (size_t)s * exec_bytes);
-        float* cst = reinterpret_cast<float*>(warea + (size_t)S * exec_bytes + (size_t)s * cst_bytes);
+        SbInsn* exec = reinterpret_cast<SbInsn*>(warea + (size_t)s * lay.exec_bytes);
+        float* table = reinterpret_cast<float*>(tables + (size_t)s * lay.table_bytes);
         for (uint32_t i = lane; i < pr.n_insn; i += 32) exec[i] = batch.insns[pr.insn_off + i];
         if (lane == 0) exec[pr.n_insn] = SbInsn{0u, 0u};
         __syncwarp();
@@ -304,15 +416,23 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, 
                 const float slot = prob.sampled ? sampled_constant(prob, (unsigned long long)sys * K + a.slot, bank) : bank_ptr[a.slot];
                 v = __fadd_rn(__fmul_rn(slot, a.scale), a.offset);
             } else v = batch.lits[pr.lit_off + e - K - pr.n_affine];
-            cst[e] = v;
+            source[e] = v;
         }
+        __syncwarp();
+        if (pr.main_off) rollout_bank_part(exec, source, tmp, table, RR);
+        __syncwarp(); /* the next record's constants overwrite `source` */
+        const uint32_t table_address = shared_address(table);
+        for (uint32_t i = pr.main_off + lane; i < pr.n_insn; i += 32) exec[i] = rewritten<RR>(exec[i], table_address, slot0);
+        if (lane == 0) starts[s] = shared_address(exec + pr.main_off);
     }
     __syncwarp();
 
     const uint32_t STAGE = 0, NEXT = S, SUM = 2 * S, STATE = 3 * S, BASE = STATE;
     const bool ragged = prob.offsets != nullptr;
     Rollout<RR> m;
-    m.slots = reinterpret_cast<float*>(warea + (size_t)S * (exec_bytes + cst_bytes)) + lane * RR;
+    m.slot0 = slot0;
+    m.lane_off = (uint32_t)lane * (uint32_t)(RR * 4);
+    const uint32_t starts_address = shared_address(starts), tables_address = shared_address(tables);
     float sq = 0.0f;
     unsigned long long residuals = 0;
     /* any non-finite time or reference value (NaN excepted where it means "unobserved"), found
@@ -378,9 +498,7 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, uint32_t exec_bytes, 
                 for (int stage = 0; stage < 4; ++stage) {
                     const float weight = (stage == 0 || stage == 3) ? 1.0f : 2.0f;
                     for (uint32_t s = 0; s < S; ++s) {
-                        const SbInsn* exec = reinterpret_cast<const SbInsn*>(warea + (size_t)s * exec_bytes);
-                        m.cst_of_run = reinterpret_cast<const float*>(warea + (size_t)S * exec_bytes + (size_t)s * cst_bytes);
-                        m.run(exec, m.cst_of_run); /* acc = rhs of state s at the stage values */
+                        m.run(lds_word(starts_address + 4u * s), tables_address + s * lay.table_bytes); /* acc = rhs of state s at the stage values */
                         float v[RR];
                         m.get(SUM + s, v);
 #pragma unroll
@@ -478,11 +596,14 @@ __global__ void rk4_validate_kernel(const Rk4Problem prob) {
 uint32_t round16(size_t v) { return (uint32_t)((v + 15) / 16 * 16); }
 
 template <int RR>
-cudaError_t launch_width(const DeviceBatch& batch, const Rk4Problem& prob, size_t smem_limit, cudaStream_t stream) {
-    const uint32_t exec_bytes = round16(((size_t)batch.max_insn + 1) * sizeof(SbInsn));
-    const uint32_t cst_bytes = round16(((size_t)prob.num_constants + batch.max_extra) * 4 + 16);
+cudaError_t launch_width(const DeviceBatch& batch, const Rk4Problem& prob, size_t smem_limit, unsigned concurrent, cudaStream_t stream) {
+    RolloutLayout lay;
+    lay.exec_bytes = round16(((size_t)batch.max_insn + 1) * sizeof(SbInsn));
+    lay.table_bytes = round16(((size_t)batch.max_cst + 1) * RR * 4); /* one entry at least: instructions without an operand read it */
+    lay.source_bytes = round16(((size_t)prob.num_constants + batch.max_extra + batch.max_btmp) * 4 + 16);
     /* max_slots already includes the integrator's reserved slots */
-    const uint32_t warp_bytes = prob.num_states * (exec_bytes + cst_bytes) + batch.max_slots * (uint32_t)RR * 128u;
+    lay.warp_bytes = prob.num_states * (lay.exec_bytes + lay.table_bytes) + lay.source_bytes + 64u + batch.max_slots * (uint32_t)RR * 128u;
+    const uint32_t warp_bytes = lay.warp_bytes;
     /* warps per CTA: the count that puts most warps on an SM (shared memory per SM is the CTA limit
      * plus 1 KB reserved per resident CTA; the register file bounds the narrow machines at two full
      * CTAs and the wide one at about 24 warps) */
@@ -503,20 +624,24 @@ cudaError_t launch_width(const DeviceBatch& batch, const Rk4Problem& prob, size_
     /* warps draw items from the queue until it is empty, so the grid only has to fill the device */
     int device = 0, sms = 0;
     if ((e = cudaGetDevice(&device)) != cudaSuccess || (e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return e;
+    /* a launch that shares the device with `concurrent` - 1 others takes its share of the resident
+     * CTAs: its warps then work through several items each, and one that drew a short item (an
+     * invalid candidate) goes on with the next instead of idling until its CTA's longest item ends */
     const unsigned long long resident = (unsigned long long)sms * (unsigned)std::max(1, best / warps);
-    const unsigned long long blocks = std::min<unsigned long long>((items + warps - 1) / warps, resident);
+    const unsigned long long share = std::max<unsigned long long>(1, (resident + concurrent - 1) / std::max(1u, concurrent));
+    const unsigned long long blocks = std::min<unsigned long long>((items + warps - 1) / warps, share);
     const size_t values = (size_t)prob.total_points * (prob.num_states + 1);
     rk4_validate_kernel<<<(unsigned)std::min<size_t>(1024, (values + 255) / 256), 256, 0, stream>>>(prob);
-    rk4_kernel<RR><<<(unsigned)blocks, warps * 32, smem, stream>>>(batch, prob, exec_bytes, cst_bytes, warp_bytes);
+    rk4_kernel<RR><<<(unsigned)blocks, warps * 32, smem, stream>>>(batch, prob, lay);
     return cudaGetLastError();
 }
 
 }  // namespace
 
-cudaError_t launch_rk4(const DeviceBatch& batch, const Rk4Problem& prob, size_t smem_limit, cudaStream_t stream) {
-    if (prob.num_trajectories <= 32) return launch_width<1>(batch, prob, smem_limit, stream);
-    if (prob.num_trajectories <= 64) return launch_width<2>(batch, prob, smem_limit, stream);
-    return launch_width<4>(batch, prob, smem_limit, stream);
+cudaError_t launch_rk4(const DeviceBatch& batch, const Rk4Problem& prob, size_t smem_limit, unsigned concurrent, cudaStream_t stream) {
+    if (prob.num_trajectories <= 32) return launch_width<1>(batch, prob, smem_limit, concurrent, stream);
+    if (prob.num_trajectories <= 64) return launch_width<2>(batch, prob, smem_limit, concurrent, stream);
+    return launch_width<4>(batch, prob, smem_limit, concurrent, stream);
 }
 
 }  // namespace sb

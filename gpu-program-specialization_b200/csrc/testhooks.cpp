@@ -32,7 +32,9 @@ SBT_EXPORT int sbt_encode(const uint8_t* routine_blob, const uint64_t* routine_o
     /* flags: bit 0 run the preflight scan first; bit 1 hoist bank-only and row-only sub-expressions; bit 3 only
      * row-only sub-expressions that no toggle reaches;
      * bit 2 one-part records with direct constant addressing (the rollout kernel's form);
-     * bits 8.. cap on hoisted row values (0 = default) */
+     * bit 4 the rollout kernel's split form: columns are the first spill slots (four vectors of them are
+     * reserved for the integrator), bank-only sub-expressions move to the bank part, nothing else is hoisted;
+     * bits 8..15 cap on hoisted row values (0 = default) */
     const bool run_preflight = (flags & 1) != 0, hoist = (flags & 2) != 0, flat = (flags & 4) != 0;
     std::vector<const SecantAstInstruction*> routines(num_routines), asts(num_asts);
     for (size_t i = 0; i < num_routines; ++i) routines[i] = routine_blob + routine_off[i];
@@ -50,7 +52,14 @@ SBT_EXPORT int sbt_encode(const uint8_t* routine_blob, const uint64_t* routine_o
     b->rules.hoist_bank = hoist && !flat;
     b->rules.hoist_row = hoist && !flat;
     b->rules.hoist_toggled = !(flags & 8u);
-    if (flags >> 8) b->rules.max_hoisted = (unsigned)(flags >> 8);
+    if (flags & 16u) {
+        b->rules.columns_are_slots = true;
+        b->rules.reserved_slots = (unsigned)(4 * num_columns);
+        b->rules.split_parts = true;
+        b->rules.hoist_bank = true;
+        b->rules.hoist_row = false;
+    }
+    if ((flags >> 8) & 0xff) b->rules.max_hoisted = (unsigned)((flags >> 8) & 0xff);
     SecantResult r = SECANT_SUCCESS;
     if (run_preflight) {
         for (size_t i = 0; i < num_routines && r == SECANT_SUCCESS; ++i) r = preflight(routines[i], b->rules);
@@ -227,6 +236,8 @@ SBT_EXPORT int sbt_eval(const SbtBatch* b, size_t program, const float* input, s
     }
     for (int round = 0; round < 2; ++round) {
         for (auto& v : slots) v = std::nanf("");
+        if (b->rules.columns_are_slots) /* the integrator keeps state i in slot i */
+            for (size_t c = 0; c < b->rules.num_columns && c < slots.size(); ++c) slots[c] = input[c * input_ld + row];
         acc = std::nanf("");
         if (!run_part(p.main_off, 2)) return SECANT_ERROR_UNEXPECTED_INSTRUCTION;
     }

@@ -345,7 +345,7 @@ cudaError_t launch_eval(const DeviceBatch& batch, const EvalProblem&, const Laun
     return cudaSuccess;
 }
 
-cudaError_t launch_rk4(const DeviceBatch&, const Rk4Problem&, size_t, cudaStream_t) { return cudaErrorUnknown; }
+cudaError_t launch_rk4(const DeviceBatch&, const Rk4Problem&, size_t, unsigned, cudaStream_t) { return cudaErrorUnknown; }
 
 cudaError_t launch_gram(const float* predictions, size_t prediction_ld, uint32_t, const float*, size_t, uint32_t, uint32_t, uint32_t batch_programs,
                         float*, size_t, cudaStream_t stream) {

@@ -12,11 +12,13 @@ from secant_b200 import abi, programs as P
 
 
 def encode(packed, columns, constants, banks_allowed=True, toggle_bits=0, preflight=True, hoist=False, flat=False,
-           max_hoisted=0):
+           max_hoisted=0, rollout=False):
     """hoist: bank-only and row-only sub-expressions move to the bank part and the row prelude;
-    flat: one-part records with direct constant addressing (the rollout kernel's form)."""
+    flat: one-part records with direct constant addressing;
+    rollout: the rollout kernel's form (columns are the integrator's state slots, bank-only
+    sub-expressions in the bank part, nothing else hoisted)."""
     handle = C.c_void_p()
-    flags = int(preflight) | (2 if hoist else 0) | (4 if flat else 0) | (max_hoisted << 8)
+    flags = int(preflight) | (2 if hoist else 0) | (4 if flat else 0) | (16 if rollout else 0) | (max_hoisted << 8)
     code = S.hooks().sbt_encode(*S.blob_args(packed), C.c_size_t(columns), C.c_size_t(constants), int(banks_allowed),
                                 toggle_bits, flags, C.byref(handle))
     return code, handle
@@ -42,10 +44,10 @@ def same(a, b):
     return (np.isnan(a) and np.isnan(b)) or a.view(np.uint32) == b.view(np.uint32)
 
 
-MODES = [dict(), dict(hoist=True), dict(hoist=True, max_hoisted=1), dict(flat=True)]
+MODES = [dict(), dict(hoist=True), dict(hoist=True, max_hoisted=1), dict(flat=True), dict(rollout=True)]
 
 
-@pytest.mark.parametrize("mode", MODES, ids=["split", "hoisted", "hoisted-one-row-value", "flat"])
+@pytest.mark.parametrize("mode", MODES, ids=["split", "hoisted", "hoisted-one-row-value", "flat", "rollout"])
 @pytest.mark.parametrize("seed,max_tokens,bits", [(3, 15, 0), (4, 32, 3), (5, 48, 8)])
 def test_records_evaluate_like_the_oracle(seed, max_tokens, bits, mode):
     pop = P.random_population(seed, 150, max_tokens, 6, 8, 2.0, toggle_bits=bits)
