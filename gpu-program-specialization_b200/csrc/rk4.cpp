@@ -7,10 +7,10 @@
  * policy (projects/odezza/core/o_generate_scoring_cuda.c:494-588,
  * projects/odezza/core/odezza.h:285-289).  Right-hand sides are ordinary Secant programs:
  * COLUMN s reads state s, BANK_CONSTANT k reads coefficient k of the system's bank.
- * This call is blocking and self-contained: it validates the programs, encodes them in chunks on
- * a few host threads while earlier chunks are already being uploaded and scored on the call's own
- * stream (ordered after whatever the caller queued on the default stream), waits, and releases its
- * temporary device buffers.
+ * This call is blocking and self-contained: host threads scan the programs and encode them in
+ * pieces while the calling thread joins encoded pieces into launches, uploads them and starts their
+ * kernels on the call's own streams (ordered after whatever the caller queued on the default
+ * stream); it waits for all of them and hands its record buffers back to the library's memory pool.
  */
 #include "evaluator.cuh"
 #include "internal.h"
@@ -27,6 +27,46 @@
 #include <vector>
 
 using namespace sb;
+
+namespace {
+
+/* Record buffers live for one call; the pool keeps their memory between calls. */
+constexpr int kMaxPoolDevices = 64;
+std::mutex g_pool_mutex;
+cudaMemPool_t g_pools[kMaxPoolDevices] = {};
+
+cudaMemPool_t record_pool(int device) {
+    if (device < 0 || device >= kMaxPoolDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(g_pool_mutex);
+    if (!g_pools[device]) {
+        cudaMemPoolProps props;
+        std::memset(&props, 0, sizeof(props));
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = device;
+        cudaMemPool_t pool = nullptr;
+        if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        unsigned long long keep = ~0ull; /* nothing goes back to the driver until it is asked for */
+        if (cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep) != cudaSuccess) {
+            cudaGetLastError();
+            cudaMemPoolDestroy(pool);
+            return nullptr;
+        }
+        g_pools[device] = pool;
+    }
+    return g_pools[device];
+}
+
+}  // namespace
+
+extern "C" SecantResult secant_b200_release_cached_memory(void) {
+    std::lock_guard<std::mutex> lock(g_pool_mutex);
+    SecantResult result = SECANT_SUCCESS;
+    for (cudaMemPool_t pool : g_pools)
+        if (pool && cudaMemPoolTrimTo(pool, 0) != cudaSuccess) result = SECANT_ERROR_DRIVER_FAILED;
+    return result;
+}
 
 extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
     /* the uniform form ends before trajectory_offsets; shorter structs are extended with zeros */
@@ -109,7 +149,9 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
     struct Chunk {
         std::vector<char> host;
         char* device = nullptr;
+        bool pooled = false;
     };
+    const cudaMemPool_t pool = record_pool(device); /* null: plain allocations */
     std::vector<Piece> pieces;
     std::vector<Chunk> chunks;
     std::mutex mutex;
@@ -281,7 +323,13 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
                 part = EncodedBatch(); /* the piece's own copy is not needed any more */
             }
         }
-        if (cudaMalloc(&chunk.device, total) != cudaSuccess) { result = SECANT_ERROR_ALLOCATION_FAILED; break; }
+        if (pool && cudaMallocFromPoolAsync(reinterpret_cast<void**>(&chunk.device), total, pool, copies) == cudaSuccess) {
+            chunk.pooled = true;
+        } else {
+            cudaGetLastError();
+            chunk.device = nullptr;
+            if (cudaMalloc(&chunk.device, total) != cudaSuccess) { result = SECANT_ERROR_ALLOCATION_FAILED; break; }
+        }
         char* d = chunk.device;
         e = cudaMemcpyAsync(d, host, total, cudaMemcpyHostToDevice, copies);
         if (e == cudaSuccess) e = cudaEventRecord(uploaded, copies);
@@ -341,11 +389,15 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
             const cudaError_t f = cudaStreamSynchronize(q);
             if (e == cudaSuccess) e = f;
         }
-    for (Chunk& chunk : chunks)
+    for (Chunk& chunk : chunks) /* every stream has been waited for: nothing reads the buffers any more */
         if (chunk.device) {
-            const cudaError_t f = cudaFree(chunk.device);
+            const cudaError_t f = chunk.pooled ? cudaFreeAsync(chunk.device, copies) : cudaFree(chunk.device);
             if (e == cudaSuccess) e = f;
         }
+    if (copies) { /* the pool may hand the memory to the next call once the frees have been reached */
+        const cudaError_t f = cudaStreamSynchronize(copies);
+        if (e == cudaSuccess) e = f;
+    }
     if (uploaded) cudaEventDestroy(uploaded);
     for (cudaStream_t q : all_streams)
         if (q) {

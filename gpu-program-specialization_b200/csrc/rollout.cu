@@ -193,31 +193,38 @@ struct Rollout {
         }
     }
 
-    /* acc = value of the rewritten main part that starts at shared address `ip`; `table` is the
-     * shared address of the program's constant table (RR copies of every entry) */
-    __device__ __forceinline__ void run(uint32_t ip, uint32_t table) {
+    /* acc = value of the rewritten main part: `count` instructions (the closing END not counted)
+     * starting at shared address `ip`; `table` is the shared address of the program's constant
+     * table (RR copies of every entry) */
+    __device__ __forceinline__ void run(uint32_t ip, uint32_t count, uint32_t table) {
         uint32_t n0, n1;
-        lds_pair(ip, n0, n1); /* the buffer holds one padding entry after the END */
+        lds_pair(ip, n0, n1); /* the record ends with END and one padding entry, so reading ahead is safe */
         ip += 8;
 #pragma unroll 1
-        for (;;) {
+        for (; count; --count) {
             const uint32_t w0 = n0, w1 = n1;
             lds_pair(ip, n0, n1);
             ip += 8;
             const unsigned handler = w0 & 0xffu;
             float x[RR];
             if (handler != H_FMA) lds<RR>((w1 & 0x00ffffffu) + ((uint32_t)((int32_t)w1 >> 31) & lane_off), x);
-            switch (handler) {
-            case H_END: return;
-            case H_STORE: sts<RR>((w1 & 0x00ffffffu) + lane_off, acc); break;
-            case H_LOAD:
+            if (handler == H_MUL) {
 #pragma unroll
-                for (int q = 0; q < RR; ++q) acc[q] = x[q];
-                break;
-            case H_ADD:
+                for (int q = 0; q < RR; ++q) acc[q] = __fmul_rn(acc[q], x[q]);
+                continue;
+            }
+            if (handler == H_ADD) {
 #pragma unroll
                 for (int q = 0; q < RR; ++q) acc[q] = __fadd_rn(acc[q], x[q]);
-                break;
+                continue;
+            }
+            if (handler == H_LOAD) {
+#pragma unroll
+                for (int q = 0; q < RR; ++q) acc[q] = x[q];
+                continue;
+            }
+            if (handler == H_STORE) { sts<RR>((w1 & 0x00ffffffu) + lane_off, acc); continue; }
+            switch (handler) {
             case H_SUB:
 #pragma unroll
                 for (int q = 0; q < RR; ++q) acc[q] = __fsub_rn(acc[q], x[q]);
@@ -225,10 +232,6 @@ struct Rollout {
             case H_RSUB:
 #pragma unroll
                 for (int q = 0; q < RR; ++q) acc[q] = __fsub_rn(x[q], acc[q]);
-                break;
-            case H_MUL:
-#pragma unroll
-                for (int q = 0; q < RR; ++q) acc[q] = __fmul_rn(acc[q], x[q]);
                 break;
             case H_DIV: divide(acc, x); break;
             case H_RDIV: divide(x, acc); break;
@@ -250,7 +253,7 @@ struct Rollout {
                 break;
             case H_UNARY: apply_unary((w0 >> 8) & 0xffu); break;
             case H_FMA: fused(w0, w1, table); break;
-            default: return; /* unreachable for records produced by the encoder */
+            default: break; /* H_END inside the counted range: unreachable for records produced by the encoder */
             }
         }
     }
@@ -423,7 +426,8 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, const RolloutLayout l
         __syncwarp(); /* the next record's constants overwrite `source` */
         const uint32_t table_address = shared_address(table);
         for (uint32_t i = pr.main_off + lane; i < pr.n_insn; i += 32) exec[i] = rewritten<RR>(exec[i], table_address, slot0);
-        if (lane == 0) starts[s] = shared_address(exec + pr.main_off);
+        /* start address and length of the main part in one word (shared addresses fit 18 bits) */
+        if (lane == 0) starts[s] = shared_address(exec + pr.main_off) | ((uint32_t)(pr.n_insn - pr.main_off - 1u) << 18);
     }
     __syncwarp();
 
@@ -498,7 +502,8 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, const RolloutLayout l
                 for (int stage = 0; stage < 4; ++stage) {
                     const float weight = (stage == 0 || stage == 3) ? 1.0f : 2.0f;
                     for (uint32_t s = 0; s < S; ++s) {
-                        m.run(lds_word(starts_address + 4u * s), tables_address + s * lay.table_bytes); /* acc = rhs of state s at the stage values */
+                        const uint32_t start = lds_word(starts_address + 4u * s);
+                        m.run(start & 0x3ffffu, start >> 18, tables_address + s * lay.table_bytes); /* acc = rhs of state s at the stage values */
                         float v[RR];
                         m.get(SUM + s, v);
 #pragma unroll
@@ -616,7 +621,7 @@ cudaError_t launch_width(const DeviceBatch& batch, const Rk4Problem& prob, size_
         if (ctas * w > register_warps) ctas = register_warps / w;
         if (ctas * w >= best) { best = ctas * w; warps = w; }
     }
-    if (!warps) return cudaErrorInvalidConfiguration;
+    if (!warps || batch.max_insn > 16383u) return cudaErrorInvalidConfiguration; /* a main part's length travels in 14 bits */
     const size_t smem = (size_t)warp_bytes * warps;
     cudaError_t e = cudaFuncSetAttribute(rk4_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
     if (e != cudaSuccess) return e;

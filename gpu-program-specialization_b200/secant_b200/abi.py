@@ -212,6 +212,7 @@ EXPORTED = {
     "secant_b200_grouped_topk": (C.c_int32, [C.c_size_t, _sz, _sz, C.c_uint32, C.c_uint32, C.c_uint32, C.c_size_t, C.c_size_t,
                                  C.c_void_p]),
     "secant_b200_rk4_score": (C.c_int32, [C.c_void_p]),
+    "secant_b200_release_cached_memory": (C.c_int32, []),
     "secant_b200_best_config": (C.c_int32, [C.c_size_t, _sz, _sz, _sz, C.c_size_t, C.c_void_p]),
     "secant_b200_topk": (C.c_int32, [C.c_size_t, _sz, _sz, C.c_size_t, C.c_size_t, C.c_void_p]),
     "secant_b200_topk_scratch_elements": (_sz, [_sz, _sz]),

@@ -169,6 +169,11 @@ typedef struct SecantB200Rk4Run {
     uintptr_t integrated_intervals;
 } SecantB200Rk4Run;
 SECANT_DEC SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* run);
+/* The call's record buffers come from a stream-ordered memory pool of the library's own (one per
+ * device, created on first use), which keeps what the largest call so far needed: allocating and
+ * freeing them with cudaMalloc/cudaFree cost 2 to 300 ms per call.  This returns the cached memory of
+ * every device to the driver; buffers of calls in flight are not touched. */
+SECANT_DEC SecantResult secant_b200_release_cached_memory(void);
 
 /*
  * Grouped top-k over a score grid [system][configuration] (contiguous, configuration = bank *

@@ -57,6 +57,11 @@ def test_constant_slope_closed_form_and_invalid_policy(cuda):
     assert np.all(got == FLT_MAX)
     blow = P.PackedPrograms([P.col(0) + P.col(0) + P.op("MUL") + P.lit(1e30) + P.op("MUL") + P.RET])
     assert rk4_score(blow, 1, dev(reference), dev(times)).cpu().numpy()[0, 0] == FLT_MAX
+    # the record buffers' memory pool can be emptied between calls; the next call fills it again
+    from secant_b200 import abi
+    assert abi.load().secant_b200_release_cached_memory() == 0
+    again = rk4_score(systems, 1, dev(reference), dev(times), dev(constants[:, None, :]), 1, 1, 0, 4).cpu().numpy()[:, 0]
+    assert np.allclose(again, [0.53125 * e * e for e in range(4)], atol=2e-6)
 
 
 def test_lorenz_candidates_match_oracle_over_a_chaotic_horizon(cuda):
@@ -186,3 +191,38 @@ def test_sampled_parameter_pools_match_explicit_banks(cuda):
         assert np.array_equal(got[:, b] == FLT_MAX, want == FLT_MAX)
         fin = want != FLT_MAX
         assert np.allclose(got[fin, b], want64[fin], rtol=1e-4, atol=1e-7)
+
+
+@pytest.mark.parametrize("ntraj", [20, 50, 130], ids=["one-per-lane", "two-per-lane", "four-per-lane"])
+def test_constant_only_sub_expressions_in_every_form(cuda, ntraj):
+    """Right-hand sides whose constant-only parts take every form the bank part knows — a product
+    and a quotient of coefficients, an affine leaf, a toggle between two coefficients and between a
+    coefficient and a state, a fused multiply-add over constants, a function of a constant, a
+    right-hand side that is a constant altogether — on each of the three machine widths.  All
+    operations but the exponential round identically on both sides, the systems contract, so the
+    scores agree to summation order."""
+    col, bank, lit, op = P.col, P.bank, P.lit, P.op
+    damp = lambda s: col(s) + op("SUB") + P.RET                           # ... - state_s
+    forms = [
+        [bank(0) + bank(1) + op("MUL") + col(1) + op("MUL") + damp(0),                     # (c0 c1) y - x
+         bank(2) + lit(4.0) + op("DIV") + col(0) + op("MUL") + damp(1)],                   # (c2 / 4) x - y
+        [P.affine(1, 0.5, 0.25) + col(1) + op("MUL") + damp(0),                            # (c1/2 + 1/4) y - x
+         bank(0) + bank(2) + P.tog2(0) + col(0) + op("MUL") + damp(1)],                    # {c0|c2} x - y
+        [bank(0) + col(1) + P.tog2(1) + lit(0.5) + op("MUL") + damp(0),                    # {c0|y}/2 - x
+         bank(0) + bank(1) + bank(2) + op("FMA") + col(0) + op("MUL") + damp(1)],          # fma(c0,c1,c2) x - y
+        [bank(1) + op("NEG") + op("EXP") + col(1) + op("MUL") + damp(0),                   # exp(-c1) y - x
+         bank(2) + bank(0) + op("SUB") + P.RET],                                           # c2 - c0: no state at all
+        [col(0) + bank(1) + bank(2) + op("MUL") + lit(0.125) + op("FMA") + damp(0),        # fma(x, c1 c2, 1/8) - x
+         bank(0) + op("ABS") + op("SQRT") + col(0) + col(1) + op("MIN") + op("MUL") + damp(1)],
+    ]
+    pop = P.PackedPrograms([p for system in forms for p in system])
+    n_sys, K, nb, bits, points = len(forms), 3, 2, 2, 25
+    times = (np.arange(points, dtype=np.float32) * np.float32(0.04)).astype(np.float32)
+    ref = np.stack([P.uniform(31, s, ntraj * points, -1, 1) for s in range(2)])
+    banks = np.stack([np.stack([P.uniform(32, sy * 7 + b, K, 0.2, 1.5) for b in range(nb)]) for sy in range(n_sys)])
+    got = rk4_score(pop, 2, dev(ref), dev(times), dev(banks), K, nb, bits, 2).cpu().numpy()
+    for cfg in range(nb << bits):
+        code, want, want64 = S.oracle_rk4(pop, 2, ref, ntraj, times, np.ascontiguousarray(banks[:, cfg >> bits, :]), 2, bits,
+                                          cfg & 3, want64=True)
+        assert code == 0 and np.all(want != FLT_MAX)
+        assert np.allclose(got[:, cfg], want64, rtol=1e-4, atol=1e-7), cfg
