@@ -157,6 +157,7 @@ struct Rk4Problem {
     float* output;                 /* [system][configuration] */
     size_t output_ld;
     unsigned long long* queue;      /* device counter, zero at launch: the next item to be taken */
+    const uint32_t* order;          /* optional [num_systems]: the system whose items are taken k-th (costliest first) */
     unsigned long long* integrated; /* optional device counter: (trajectory, observation interval) pairs integrated */
 };
 /* batch.programs holds num_systems * num_states records, system-major, encoded with

@@ -295,7 +295,8 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
         const size_t o_aff = align256(o_patch + n_patches * sizeof(SbPatch));
         const size_t o_lit = align256(o_aff + n_affines * sizeof(SbAffine));
         const size_t o_flag = align256(o_lit + n_lits * sizeof(float) + 16); /* one word raised by the data validation */
-        const size_t total = o_flag + 256;
+        const size_t o_order = o_flag + 256;
+        const size_t total = align256(o_order + n_programs / S * sizeof(uint32_t));
         try {
             chunk.host.assign(total, 0);
         } catch (const std::bad_alloc&) {
@@ -321,6 +322,30 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
                 at_program += part.programs.size(); at_insn += part.insns.size(); at_patch += part.patches.size();
                 at_affine += part.affines.size(); at_lit += part.lits.size();
                 part = EncodedBatch(); /* the piece's own copy is not needed any more */
+            }
+            /* Warps take the launch's systems costliest first (by the instructions of their main parts):
+             * a candidate that stays valid runs for its full length, and the long ones should not be
+             * the last to start. */
+            const size_t n_systems = n_programs / S;
+            const SbProgram* recs = reinterpret_cast<const SbProgram*>(host);
+            uint32_t* order = reinterpret_cast<uint32_t*>(host + o_order);
+            for (size_t i = 0; i < n_systems; ++i) order[i] = (uint32_t)i;
+            try {
+                std::vector<uint32_t> cost(n_systems, 0);
+                const SbInsn* insns = reinterpret_cast<const SbInsn*>(host + o_insn);
+                for (size_t i = 0; i < n_systems; ++i)
+                    for (size_t k = 0; k < S; ++k) { /* the rollout machine's own weights: about 25 issue slots per instruction, 45 more for a function or a division */
+                        const SbProgram& pr = recs[i * S + k];
+                        for (uint32_t at = pr.main_off; at < pr.n_insn; ++at) {
+                            const unsigned cs = insns[pr.insn_off + at].w0 & 0xffu;
+                            const bool division = cs >= SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS && cs < SB_CASE_BIN + (SB_BIN_RDIV + 1) * SB_NUM_KINDS;
+                            const bool function = cs >= SB_CASE_UN && cs < SB_CASE_FMA && cs != SB_CASE_UN + SB_UN_NEG && cs != SB_CASE_UN + SB_UN_ABS;
+                            cost[i] += division || function ? 70u : 25u;
+                        }
+                    }
+                std::stable_sort(order, order + n_systems, [&](uint32_t a, uint32_t b) { return cost[a] > cost[b]; });
+            } catch (const std::bad_alloc&) {
+                /* no memory for the sort: the systems are taken in their own order */
             }
         }
         if (pool && cudaMallocFromPoolAsync(reinterpret_cast<void**>(&chunk.device), total, pool, copies) == cudaSuccess) {
@@ -368,6 +393,7 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
         p.allow_missing = run->allow_missing_observations;
         p.invalid_flag = reinterpret_cast<int*>(d + o_flag);
         p.queue = reinterpret_cast<unsigned long long*>(d + o_flag + 8); /* uploaded as zeros with the records */
+        p.order = reinterpret_cast<const uint32_t*>(d + o_order);
         p.sampled = sampled ? reinterpret_cast<const SecantB200SampledParameter*>(run->sampled_parameters) + first_system * K : nullptr;
         p.uniform_pool = reinterpret_cast<const float*>(run->uniform_pool);
         p.normal_pool = reinterpret_cast<const float*>(run->normal_pool);

@@ -390,7 +390,8 @@ rk4_kernel(const DeviceBatch batch, const Rk4Problem prob, const RolloutLayout l
     if (lane == 0) item = atomicAdd(prob.queue, 1ull);
     item = __shfl_sync(0xffffffffu, item, 0);
     if (item >= num_items) break;
-    const uint32_t sys = (uint32_t)(item / configs);
+    const uint32_t turn = (uint32_t)(item / configs);
+    const uint32_t sys = prob.order ? prob.order[turn] : turn;
     const unsigned long long cfg = item % configs;
     const unsigned long long perm = cfg & ((1ull << prob.toggle_bits) - 1ull);
     const uint32_t bank = (uint32_t)(cfg >> prob.toggle_bits);
