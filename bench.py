@@ -216,10 +216,11 @@ def rk4_arm(args, w):
         raise RuntimeError("bench.py needs a CUDA device")
     dev = torch.device("cuda", 0)
     systems, S, ics, steps, K = (args.programs or 16384), 3, 64, 1000, 8
+    banks = max(1, args.banks)                      # development only: several coefficient sets per system
     pop = P.random_population(4, systems * S, 24, S, K, 1.0)
     ops = P.count_ops(pop).reshape(systems, S).sum(axis=1)
     rng = np.random.Generator(np.random.Philox(key=4))
-    coeffs = rng.standard_normal((systems, 1, K), dtype=np.float32)
+    coeffs = rng.standard_normal((systems, banks, K), dtype=np.float32)
     h = np.float32(0.01)
     state = rng.uniform(-10, 10, size=(3, ics)).astype(np.float32)
     ref = np.empty((3, ics, steps + 1), dtype=np.float32)
@@ -243,7 +244,7 @@ def rk4_arm(args, w):
         launches0 = lib.secant_b200_kernel_launch_count()
         integrated.zero_()
         start.record()
-        scores = rk4_score(pop, S, ref_d, times_d, coeffs_d, K, integrated=integrated)   # encodes, uploads, integrates, blocks
+        scores = rk4_score(pop, S, ref_d, times_d, coeffs_d, K, banks, integrated=integrated)   # encodes, uploads, integrates, blocks
         stop.record()
         stop.synchronize()
         if it >= args.warmup:
@@ -252,17 +253,17 @@ def rk4_arm(args, w):
     # A candidate is integrated until one of its states stops being finite (its score is FLT_MAX from
     # then on), so the work done is what the device counted, not systems x conditions x steps.
     done = float(integrated.item())                                   # (trajectory, step) pairs integrated
-    share = done / (float(systems) * ics * steps)
+    share = done / (float(systems) * banks * ics * steps)
     stage_evals = done * 4
     per_system_step = (4 * ops + 4 * 2 * S + S + 2 * S).astype(np.float64)          # lane operations per (system, IC, step)
     lane_ops = float(per_system_step.mean()) * done                   # weighted by the mean: the counter is not per system
     peak = C.c_double()
     abi.check(lib.secant_b200_fp32_peak_probe(0.5, C.byref(peak)), "fp32 peak probe")
     valid = float((scores < 3.0e38).float().mean().item())
-    print(json.dumps({"impl": "rk4", "metric": "candidate systems scored/sec", "value": systems / dt, "unit": "systems/s",
+    print(json.dumps({"impl": "rk4", "metric": "candidate systems scored/sec", "value": systems * banks / dt, "unit": "systems/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
                       "dtype": "f32", "data": "synthetic",
-                      "config": {"workload": "configs[3] RK4 rollout scoring", "systems": systems, "states": S, "coefficients": K,
+                      "config": {"workload": "configs[3] RK4 rollout scoring", "systems": systems, "coefficient_sets": banks, "states": S, "coefficients": K,
                                  "initial_conditions": ics, "rk4_steps": steps, "max_tokens_per_state": 24,
                                  "mean_ops_per_system": float(ops.mean()), "valid_fraction": valid,
                                  "integrated_share": share, "ms_per_call": [round(x * 1e3, 1) for x in seconds],
@@ -677,6 +678,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "comparator", "rk4", "toggles", "box"])
     ap.add_argument("--programs", type=int, default=None, help="development only: shrink the population")
     ap.add_argument("--rows", type=int, default=None, help="development only: shrink the dataset")
+    ap.add_argument("--banks", type=int, default=1, help="development only (--impl rk4): coefficient sets per system")
     ap.add_argument("--no-cpu", action="store_true", help="development only: skip the CPU baseline and the parity spot check")
     args = ap.parse_args()
     w = dict(WORKLOAD)

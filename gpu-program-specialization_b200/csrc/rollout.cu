@@ -611,20 +611,23 @@ cudaError_t launch_width(const DeviceBatch& batch, const Rk4Problem& prob, size_
     lay.warp_bytes = prob.num_states * (lay.exec_bytes + lay.table_bytes) + lay.source_bytes + 64u + batch.max_slots * (uint32_t)RR * 128u;
     const uint32_t warp_bytes = lay.warp_bytes;
     /* warps per CTA: the count that puts most warps on an SM (shared memory per SM is the CTA limit
-     * plus 1 KB reserved per resident CTA; the register file bounds the narrow machines at two full
-     * CTAs and the wide one at about 24 warps) */
-    const int register_warps = RR == 4 ? 24 : 2 * kRolloutMaxWarps;
+     * plus 1 KB reserved per resident CTA; the register file holds 64 K registers, allocated per warp
+     * in units of 256) */
+    cudaFuncAttributes attributes;
+    cudaError_t e = cudaFuncGetAttributes(&attributes, rk4_kernel<RR>);
+    if (e != cudaSuccess) return e;
+    const int warp_registers = (attributes.numRegs * 32 + 255) / 256 * 256;
+    const int register_warps = std::min(64, 65536 / std::max(256, warp_registers));
     int warps = 0, best = 0;
     for (int w = 2; w <= kRolloutMaxWarps; ++w) {
         const size_t cta = (size_t)warp_bytes * w;
         if (cta > smem_limit) break;
-        int ctas = (int)((smem_limit + 1024) / (cta + 1024));
-        if (ctas * w > register_warps) ctas = register_warps / w;
-        if (ctas * w >= best) { best = ctas * w; warps = w; }
+        const int ctas = std::min((int)((smem_limit + 1024) / (cta + 1024)), register_warps / w);
+        if (ctas && ctas * w >= best) { best = ctas * w; warps = w; }
     }
     if (!warps || batch.max_insn > 16383u) return cudaErrorInvalidConfiguration; /* a main part's length travels in 14 bits */
     const size_t smem = (size_t)warp_bytes * warps;
-    cudaError_t e = cudaFuncSetAttribute(rk4_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
+    e = cudaFuncSetAttribute(rk4_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
     if (e != cudaSuccess) return e;
     const unsigned long long items = ((unsigned long long)prob.num_banks << prob.toggle_bits) * prob.num_systems;
     /* warps draw items from the queue until it is empty, so the grid only has to fill the device */

@@ -193,14 +193,15 @@ def test_sampled_parameter_pools_match_explicit_banks(cuda):
         assert np.allclose(got[fin, b], want64[fin], rtol=1e-4, atol=1e-7)
 
 
-@pytest.mark.parametrize("ntraj", [20, 50, 130], ids=["one-per-lane", "two-per-lane", "four-per-lane"])
-def test_constant_only_sub_expressions_in_every_form(cuda, ntraj):
+@pytest.mark.parametrize("ntraj,nb", [(20, 1), (20, 2), (20, 3), (20, 5), (50, 1), (50, 2), (50, 3), (130, 2)],
+                         ids=["20x1", "20x2", "20x3", "20x5", "50x1", "50x2", "50x3", "130x2"])
+def test_constant_only_sub_expressions_in_every_form(cuda, ntraj, nb):
     """Right-hand sides whose constant-only parts take every form the bank part knows — a product
     and a quotient of coefficients, an affine leaf, a toggle between two coefficients and between a
     coefficient and a state, a fused multiply-add over constants, a function of a constant, a
-    right-hand side that is a constant altogether — on each of the three machine widths.  All
-    operations but the exponential round identically on both sides, the systems contract, so the
-    scores agree to summation order."""
+    right-hand side that is a constant altogether — with one, two and four trajectories per lane and
+    one to five coefficient sets per system.  All operations but the exponential round identically
+    on both sides, the systems contract, so the scores agree to summation order."""
     col, bank, lit, op = P.col, P.bank, P.lit, P.op
     damp = lambda s: col(s) + op("SUB") + P.RET                           # ... - state_s
     forms = [
@@ -216,7 +217,7 @@ def test_constant_only_sub_expressions_in_every_form(cuda, ntraj):
          bank(0) + op("ABS") + op("SQRT") + col(0) + col(1) + op("MIN") + op("MUL") + damp(1)],
     ]
     pop = P.PackedPrograms([p for system in forms for p in system])
-    n_sys, K, nb, bits, points = len(forms), 3, 2, 2, 25
+    n_sys, K, bits, points = len(forms), 3, 2, 25
     times = (np.arange(points, dtype=np.float32) * np.float32(0.04)).astype(np.float32)
     ref = np.stack([P.uniform(31, s, ntraj * points, -1, 1) for s in range(2)])
     banks = np.stack([np.stack([P.uniform(32, sy * 7 + b, K, 0.2, 1.5) for b in range(nb)]) for sy in range(n_sys)])
@@ -226,3 +227,26 @@ def test_constant_only_sub_expressions_in_every_form(cuda, ntraj):
                                           cfg & 3, want64=True)
         assert code == 0 and np.all(want != FLT_MAX)
         assert np.allclose(got[:, cfg], want64, rtol=1e-4, atol=1e-7), cfg
+
+
+@pytest.mark.parametrize("ntraj", [20, 50])
+def test_an_exploding_coefficient_set_does_not_touch_its_neighbours(cuda, ntraj):
+    """Coefficient sets of one system are scored independently: x' = c0 x^2 - x blows up for the
+    large c0 of every second set (score FLT_MAX, whenever it happens) while the sets beside it
+    stay finite and keep the oracle's scores."""
+    col, bank, op = P.col, P.bank, P.op
+    pop = P.PackedPrograms([bank(0) + col(0) + op("MUL") + col(0) + op("MUL") + col(0) + op("SUB") + P.RET] * 3)
+    nb, points = 4, 40
+    times = (np.arange(points, dtype=np.float32) * np.float32(0.05)).astype(np.float32)
+    ref = P.uniform(41, 0, ntraj * points, 0.5, 1.5)[None, :]
+    banks = np.zeros((3, nb, 1), dtype=np.float32)
+    banks[:, 0::2, 0] = [[-0.5, 0.25], [0.1, -1.0], [0.3, 0.2]]         # tame
+    banks[:, 1::2, 0] = [[3.0e4, 1.0e6], [5.0e3, 2.0e5], [1.0e30, 4.0e4]]  # explosive, sooner or later
+    got = rk4_score(pop, 1, dev(ref), dev(times), dev(banks), 1, nb).cpu().numpy()
+    for b in range(nb):
+        code, want, want64 = S.oracle_rk4(pop, 1, ref, ntraj, times, np.ascontiguousarray(banks[:, b, :]), want64=True)
+        assert code == 0
+        assert np.array_equal(got[:, b] == FLT_MAX, want == FLT_MAX), b
+        assert np.all((want == FLT_MAX) == (b % 2 == 1))
+        fin = want != FLT_MAX
+        assert np.allclose(got[fin, b], want64[fin], rtol=1e-4, atol=1e-7), b
