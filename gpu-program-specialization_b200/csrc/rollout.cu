@@ -625,7 +625,8 @@ cudaError_t launch_width(const DeviceBatch& batch, const Rk4Problem& prob, size_
         const int ctas = std::min((int)((smem_limit + 1024) / (cta + 1024)), register_warps / w);
         if (ctas && ctas * w >= best) { best = ctas * w; warps = w; }
     }
-    if (!warps || batch.max_insn > 16383u) return cudaErrorInvalidConfiguration; /* a main part's length travels in 14 bits */
+    /* a main part's length travels in 14 bits; the start words of the states' main parts have 16 places */
+    if (!warps || batch.max_insn > 16383u || prob.num_states > 16u) return cudaErrorInvalidConfiguration;
     const size_t smem = (size_t)warp_bytes * warps;
     e = cudaFuncSetAttribute(rk4_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
     if (e != cudaSuccess) return e;
