@@ -195,13 +195,14 @@ SecantResult runs_validate(const SecantCubinPlan& plan, const UnpackedRun* runs,
     rules.banks_allowed = plan.shape == SECANT_KERNEL_SHAPE_TOGGLE_SSE_F32;
     rules.toggle_bits = rules.banks_allowed ? smallest_bits : 0;
     /* records in parts; row-only sub-expressions are worth a prelude as soon as a program is
-     * evaluated for more than one group of four banks, and those no toggle reaches as soon as there
-     * are toggles (an item then covers several permutations and computes them once) */
+     * evaluated for more than one bank group (more than two banks: three or four are two groups of
+     * the 8 x 2 tile, more are groups of four), and those no toggle reaches as soon as there are
+     * toggles (an item then covers several permutations and computes them once) */
     rules.split_parts = true;
     rules.hoist_bank = true;
     rules.hoist_toggled = false;
     if (rules.banks_allowed)
-        for (size_t i = 0; i < count; ++i) rules.hoist_toggled = rules.hoist_toggled || runs[i].num_banks > 4;
+        for (size_t i = 0; i < count; ++i) rules.hoist_toggled = rules.hoist_toggled || runs[i].num_banks > 2;
     rules.hoist_row = rules.hoist_toggled || rules.toggle_bits > 0;
     if (!skip_preflight) {
         const SecantAstProgramList* lists[2] = {&programs.routines, &programs.asts};

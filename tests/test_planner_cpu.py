@@ -31,12 +31,14 @@ def test_headline_shape_fills_the_machine():
 
 
 def test_items_span_permutations_when_one_item_holds_every_bank():
-    """Four coefficient sets are one bank group of the 4 x 4 tile, so an item goes on over sixteen
+    """Four coefficient sets are two bank groups of the 8 x 2 tile, so an item goes on over eight
     permutations (the program is fetched once for them); with sixteen bank groups per item there
     is no room, and the tables of long programs shrink the span."""
     code, p = plan(16384, 1 << 18, banks=4, bits=8, inputs=6, table=8)
-    assert code == 1 and p["gpi"] == 1 and p["ppi"] == 16
-    assert p["items"] == -(-16384 // p["groups"]) * (256 // 16)
+    assert code == 1 and p["variant"] == 1 and p["gpi"] == 2 and p["ppi"] == 8
+    assert p["items"] == -(-16384 // p["groups"]) * (256 // 8)
+    code, p = plan(16384, 1 << 18, banks=2, bits=8, inputs=6, table=8)          # one group of the 8 x 2 tile
+    assert code == 1 and p["variant"] == 1 and p["gpi"] == 1 and p["ppi"] == 16
     assert plan(16384, 1 << 18, banks=64, bits=8)[1]["ppi"] == 1
     assert plan(16384, 1 << 18, banks=8, bits=8)[1]["ppi"] == 8                # two bank groups per permutation
     assert plan(16384, 1 << 18, banks=4, bits=2)[1]["ppi"] == 4                # no more permutations than there are
@@ -59,7 +61,9 @@ def test_item_index_stays_inside_32_bits():
     (permutation, bank group) pairs, so the bound is reached with many banks."""
     assert plan(1, 1000, banks=64, bits=32)[0] == -1           # 2^32 items of sixteen bank groups
     assert plan(1, 1000, banks=128, bits=31)[0] == -1
-    code, p = plan(1, 1000, banks=4, bits=32)                  # one bank group: sixteen permutations per item
+    code, p = plan(1, 1000, banks=4, bits=32)                  # two bank groups: eight permutations per item
+    assert code == 1 and p["ppi"] == 8 and p["items"] == 1 << 29
+    code, p = plan(1, 1000, banks=2, bits=32)                  # one bank group: sixteen permutations per item
     assert code == 1 and p["ppi"] == 16 and p["items"] == 1 << 28
     code, p = plan(1, 1000, banks=64, bits=31)
     assert code == 1 and p["ppi"] == 1 and p["items"] == 1 << 31 and p["items"] + 20 < 1 << 32
