@@ -128,11 +128,6 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
     SecantResult result = routine_arities(programs.routines, arity);
     if (result != SECANT_SUCCESS) return result;
 
-    int device = 0, limit = 0;
-    if (cudaGetDevice(&device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess)
-        return SECANT_ERROR_DRIVER_FAILED;
-
     /* Host threads work on pieces of 512 systems: first every piece is scanned (nothing is launched
      * before every program has passed the scan, and the first failing program in order decides the
      * result), then the pieces are encoded while the calling thread joins four encoded pieces into
@@ -151,7 +146,6 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
         char* device = nullptr;
         bool pooled = false;
     };
-    const cudaMemPool_t pool = record_pool(device); /* null: plain allocations */
     std::vector<Piece> pieces;
     std::vector<Chunk> chunks;
     std::mutex mutex;
@@ -236,10 +230,24 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
         else stop.store(true);
     }
     ready.notify_all();
+    /* the device is asked for only now: a request with a malformed program is answered with that
+     * program's code whether or not a device can be had */
+    int device = 0, limit = 0;
+    if (result == SECANT_SUCCESS && (cudaGetDevice(&device) != cudaSuccess ||
+                                     cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess)) {
+        cudaGetLastError();
+        result = SECANT_ERROR_DRIVER_FAILED;
+        {
+            std::lock_guard<std::mutex> lock(mutex);
+            stop.store(true);
+        }
+        ready.notify_all();
+    }
     if (result != SECANT_SUCCESS) {
         for (std::thread& t : workers) t.join();
         return result;
     }
+    const cudaMemPool_t pool = record_pool(device); /* null: plain allocations */
 
     /* records travel on their own stream, so an upload never waits for the kernels of earlier chunks;
      * the chunks' kernels go round the compute streams, so a chunk smaller than the GPU shares it

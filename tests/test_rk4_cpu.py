@@ -186,3 +186,47 @@ def test_oracle_against_the_reference_host_scorer_on_its_fixed_shape():
     finally:
         S.oracle().so_rk4_set_fixed_interval(C.c_float(0.0))
     assert checked == 360 and finite > 100       # both valid scores and the FLT_MAX policy were exercised
+
+
+def _host_only_run(packed, num_states, systems, points=5, trajectories=2):
+    """A request whose device addresses are placeholders: validation and the program scan come
+    before anything is read, allocated or launched, so nothing may touch them.  The request
+    points into `packed`, which the caller keeps alive."""
+    import ctypes as C
+    from secant_b200 import abi
+    run = abi.Rk4Run()
+    run.struct_size, run.version = C.sizeof(run), abi.RUN_VERSION
+    packed.fill(run.programs)
+    run.num_systems, run.num_states, run.num_constants, run.num_banks = systems, num_states, 0, 1
+    total = points * trajectories
+    run.reference.address, run.reference.num_elements, run.reference.leading_dimension = 0x1000, num_states * total, total
+    run.num_trajectories, run.points_per_trajectory, run.times, run.steps_per_observation = trajectories, points, 0x2000, 1
+    run.output.address, run.output.num_elements, run.output.leading_dimension = 0x3000, systems, 1
+    return run
+
+
+def test_the_first_malformed_program_in_order_decides_the_result():
+    """Programs are scanned by several threads in pieces of 512 systems; whichever thread finds an
+    error first, the call answers with the error of the first malformed program in program order,
+    before any device is asked for (the reference validates every program before it launches,
+    projects/odezza/core/o_scoring_pipeline.c:1541-1594)."""
+    import ctypes as C
+    from secant_b200 import abi, programs as P
+    lib = abi.load()
+    good = P.col(0) + P.lit(0.5) + P.op("MUL") + P.RET
+    bad_column = P.col(7) + P.RET                                                # one state only
+    bad_opcode = P.col(0) + bytes([0x9b]) + P.RET                                # an integer addition: not evaluable
+    alone = []
+    for bad in (bad_column, bad_opcode):
+        one = P.PackedPrograms([bad])
+        single = _host_only_run(one, 1, 1)
+        alone.append(lib.secant_b200_rk4_score(C.byref(single)))
+    assert alone[0] != alone[1] and abi.SUCCESS not in alone and abi.ERROR_DRIVER_FAILED not in alone
+    systems = 3000                                                               # six pieces
+    for where_column, where_opcode in ((40, 2900), (2900, 40), (700, 1400), (1400, 700), (511, 512), (512, 511)):
+        asts = [good] * systems
+        asts[where_column], asts[where_opcode] = bad_column, bad_opcode
+        packed = P.PackedPrograms(asts)
+        run = _host_only_run(packed, 1, systems)
+        code = lib.secant_b200_rk4_score(C.byref(run))
+        assert code == (alone[0] if where_column < where_opcode else alone[1]), (where_column, where_opcode, code)
