@@ -250,3 +250,20 @@ def test_an_exploding_coefficient_set_does_not_touch_its_neighbours(cuda, ntraj)
         assert np.all((want == FLT_MAX) == (b % 2 == 1))
         fin = want != FLT_MAX
         assert np.allclose(got[fin, b], want64[fin], rtol=1e-4, atol=1e-7), b
+
+
+def test_a_structural_error_in_a_later_piece_ends_the_call_with_its_code(cuda):
+    """Errors a token scan cannot see (here a stack underflow) are found while a piece of 512
+    systems is being encoded, possibly after earlier launches have started: the call waits for
+    what it launched and answers with that code."""
+    from secant_b200 import abi
+    systems, reference, times, constants = slope_case()
+    good = systems.asts[0]
+    asts = [good] * 2600
+    asts[2300] = P.col(0) + P.op("ADD") + P.RET
+    coeffs = np.tile(constants[:1], (len(asts), 1))
+    with pytest.raises(abi.SecantError) as failure:
+        rk4_score(P.PackedPrograms(asts, systems.routines), 1, dev(reference), dev(times), dev(coeffs[:, None, :]), 1, 1, 0, 4)
+    assert failure.value.code == abi.ERROR_STACK_UNDERFLOW
+    again = rk4_score(systems, 1, dev(reference), dev(times), dev(constants[:, None, :]), 1, 1, 0, 4).cpu().numpy()[:, 0]
+    assert np.allclose(again, [0.53125 * e * e for e in range(4)], atol=2e-6)          # the library is usable afterwards
