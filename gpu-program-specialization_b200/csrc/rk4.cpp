@@ -128,17 +128,18 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
     SecantResult result = routine_arities(programs.routines, arity);
     if (result != SECANT_SUCCESS) return result;
 
-    /* Host threads work on pieces of 512 systems: first every piece is scanned (nothing is launched
+    /* Host threads work on pieces of 128 systems: first every piece is scanned (nothing is launched
      * before every program has passed the scan, and the first failing program in order decides the
-     * result), then the pieces are encoded while the calling thread joins four encoded pieces into
+     * result), then the pieces are encoded while the calling thread joins sixteen encoded pieces into
      * one launch, uploads it and starts its kernels, so encoding overlaps the kernels of earlier
      * launches.  A structural error found while encoding a later piece ends the call with that
      * code; scores of earlier launches may already have been written. */
-    constexpr size_t kPieceSystems = 512, kPiecesPerLaunch = 4;
+    constexpr size_t kPieceSystems = 128, kPiecesPerLaunch = 16;
     const size_t num_pieces = (run->num_systems + kPieceSystems - 1) / kPieceSystems;
     const size_t num_chunks = (num_pieces + kPiecesPerLaunch - 1) / kPiecesPerLaunch;
     struct Piece {
         EncodedBatch enc;
+        std::vector<uint32_t> cost; /* per system: its main parts' instructions, weighted as the rollout machine executes them */
         SecantResult status = SECANT_SUCCESS;
     };
     struct Chunk {
@@ -184,6 +185,20 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
             piece.enc.programs.reserve(count);
             for (size_t i = 0; i < count && piece.status == SECANT_SUCCESS; ++i)
                 piece.status = encode_program(programs.asts.items[first + i], programs.routines, arity, rules, piece.enc);
+            if (piece.status == SECANT_SUCCESS) { /* about 25 issue slots per instruction, 45 more for a function or a division */
+                piece.cost.assign(count / S, 0);
+                for (size_t i = 0; i < count; ++i) {
+                    const SbProgram& pr = piece.enc.programs[i];
+                    uint32_t cost = 0;
+                    for (uint32_t at = pr.main_off; at < pr.n_insn; ++at) {
+                        const unsigned cs = piece.enc.insns[pr.insn_off + at].w0 & 0xffu;
+                        const bool division = cs >= SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS && cs < SB_CASE_BIN + (SB_BIN_RDIV + 1) * SB_NUM_KINDS;
+                        const bool function = cs >= SB_CASE_UN && cs < SB_CASE_FMA && cs != SB_CASE_UN + SB_UN_NEG && cs != SB_CASE_UN + SB_UN_ABS;
+                        cost += division || function ? 70u : 25u;
+                    }
+                    piece.cost[i / S] += cost;
+                }
+            }
         } catch (const std::bad_alloc&) {
             piece.status = SECANT_ERROR_ALLOCATION_FAILED;
         }
@@ -331,27 +346,17 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
                 at_affine += part.affines.size(); at_lit += part.lits.size();
                 part = EncodedBatch(); /* the piece's own copy is not needed any more */
             }
-            /* Warps take the launch's systems costliest first (by the instructions of their main parts):
-             * a candidate that stays valid runs for its full length, and the long ones should not be
-             * the last to start. */
+            /* Warps take the launch's systems costliest first: a candidate that stays valid runs for its
+             * full length, and the long ones should not be the last to start. */
             const size_t n_systems = n_programs / S;
-            const SbProgram* recs = reinterpret_cast<const SbProgram*>(host);
             uint32_t* order = reinterpret_cast<uint32_t*>(host + o_order);
             for (size_t i = 0; i < n_systems; ++i) order[i] = (uint32_t)i;
             try {
-                std::vector<uint32_t> cost(n_systems, 0);
-                const SbInsn* insns = reinterpret_cast<const SbInsn*>(host + o_insn);
-                for (size_t i = 0; i < n_systems; ++i)
-                    for (size_t k = 0; k < S; ++k) { /* the rollout machine's own weights: about 25 issue slots per instruction, 45 more for a function or a division */
-                        const SbProgram& pr = recs[i * S + k];
-                        for (uint32_t at = pr.main_off; at < pr.n_insn; ++at) {
-                            const unsigned cs = insns[pr.insn_off + at].w0 & 0xffu;
-                            const bool division = cs >= SB_CASE_BIN + SB_BIN_DIV * SB_NUM_KINDS && cs < SB_CASE_BIN + (SB_BIN_RDIV + 1) * SB_NUM_KINDS;
-                            const bool function = cs >= SB_CASE_UN && cs < SB_CASE_FMA && cs != SB_CASE_UN + SB_UN_NEG && cs != SB_CASE_UN + SB_UN_ABS;
-                            cost[i] += division || function ? 70u : 25u;
-                        }
-                    }
-                std::stable_sort(order, order + n_systems, [&](uint32_t a, uint32_t b) { return cost[a] > cost[b]; });
+                std::vector<uint32_t> cost;
+                cost.reserve(n_systems);
+                for (size_t q = piece0; q < piece1; ++q) cost.insert(cost.end(), pieces[q].cost.begin(), pieces[q].cost.end());
+                if (cost.size() == n_systems)
+                    std::stable_sort(order, order + n_systems, [&](uint32_t a, uint32_t b) { return cost[a] > cost[b]; });
             } catch (const std::bad_alloc&) {
                 /* no memory for the sort: the systems are taken in their own order */
             }

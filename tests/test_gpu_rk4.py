@@ -253,7 +253,7 @@ def test_an_exploding_coefficient_set_does_not_touch_its_neighbours(cuda, ntraj)
 
 
 def test_a_structural_error_in_a_later_piece_ends_the_call_with_its_code(cuda):
-    """Errors a token scan cannot see (here a stack underflow) are found while a piece of 512
+    """Errors a token scan cannot see (here a stack underflow) are found while a piece of 128
     systems is being encoded, possibly after earlier launches have started: the call waits for
     what it launched and answers with that code."""
     from secant_b200 import abi

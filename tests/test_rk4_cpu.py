@@ -206,7 +206,7 @@ def _host_only_run(packed, num_states, systems, points=5, trajectories=2):
 
 
 def test_the_first_malformed_program_in_order_decides_the_result():
-    """Programs are scanned by several threads in pieces of 512 systems; whichever thread finds an
+    """Programs are scanned by several threads in pieces of 128 systems; whichever thread finds an
     error first, the call answers with the error of the first malformed program in program order,
     before any device is asked for (the reference validates every program before it launches,
     projects/odezza/core/o_scoring_pipeline.c:1541-1594)."""
@@ -222,8 +222,8 @@ def test_the_first_malformed_program_in_order_decides_the_result():
         single = _host_only_run(one, 1, 1)
         alone.append(lib.secant_b200_rk4_score(C.byref(single)))
     assert alone[0] != alone[1] and abi.SUCCESS not in alone and abi.ERROR_DRIVER_FAILED not in alone
-    systems = 3000                                                               # six pieces
-    for where_column, where_opcode in ((40, 2900), (2900, 40), (700, 1400), (1400, 700), (511, 512), (512, 511)):
+    systems = 3000                                                               # 24 pieces
+    for where_column, where_opcode in ((40, 2900), (2900, 40), (700, 1400), (1400, 700), (127, 128), (128, 127), (2943, 2944), (2944, 2943)):
         asts = [good] * systems
         asts[where_column], asts[where_opcode] = bad_column, bad_opcode
         packed = P.PackedPrograms(asts)
