@@ -710,6 +710,33 @@ SecantResult encode_program(const SecantAstInstruction* program, const SecantAst
     if (em.error != SECANT_SUCCESS) return em.error;
     em.consume(root);
 
+    if (rules.fuse_store_load) { /* a toggle site keeps its own instruction: its alternatives are whole instructions */
+        std::vector<SbInsn>& code = em.code[RUN_MAIN];
+        std::vector<uint8_t> is_site(code.size(), 0);
+        for (const SbPatch& p : em.sites[RUN_MAIN]) is_site[p.insn] = 1;
+        std::vector<SbInsn> fused;
+        std::vector<uint32_t> moved(code.size(), 0);
+        fused.reserve(code.size());
+        for (size_t i = 0; i < code.size(); ++i) {
+            const unsigned cs = code[i].w0 & 0xffu;
+            moved[i] = (uint32_t)fused.size();
+            if (cs == SB_CASE_STORE && i + 1 < code.size() && !is_site[i + 1]) {
+                const unsigned next = code[i + 1].w0 & 0xffu;
+                if (next >= SB_CASE_LOAD && next < SB_CASE_LOAD + SB_NUM_KINDS) {
+                    SbInsn both = code[i];
+                    both.w1 = SB_STORE_THEN_LOAD | ((uint32_t)(next - SB_CASE_LOAD) << 16) | (code[i + 1].w0 >> 16);
+                    fused.push_back(both);
+                    moved[i + 1] = moved[i]; /* a site never sits on the absorbed load */
+                    ++i;
+                    continue;
+                }
+            }
+            fused.push_back(code[i]);
+        }
+        for (SbPatch& p : em.sites[RUN_MAIN]) p.insn = (uint16_t)moved[p.insn];
+        code.swap(fused);
+    }
+
     /* assemble: bank part | shared row prelude | row prelude | main part, each closed by END; patch
      * sites become positions inside the whole record */
     size_t offset[NUM_RUNS] = {0, 0, 0, 0}, total = 0;

@@ -29,6 +29,9 @@ struct ProgramRules {
      * belong to the integrator and program temporaries start after them. */
     bool columns_are_slots = false;
     unsigned reserved_slots = 0;
+    /* main part: "STORE slot; LOAD x" becomes one instruction (record.h, SB_STORE_THEN_LOAD); only the
+     * rollout kernel understands it */
+    bool fuse_store_load = false;
     /* Records for the population evaluator are split into a bank part, a row prelude and a main
      * part (record.h, SbProgram) and address constants through a per-program table the bank part
      * fills.  Without split_parts (the rollout kernel) a record is one main part that addresses

@@ -15,7 +15,10 @@
  *     never manipulates a stack.
  *
  * Instruction word 0:  bits 0..7 case id (SB_CASE_*), bits 8..15 aux, bits 16..31 operand index.
- * Instruction word 1:  packed FMA operand indices (unused by the other instructions).
+ * Instruction word 1:  packed FMA operand indices.  In records made for the rollout kernel a STORE
+ *                      may carry SB_STORE_THEN_LOAD | kind << 16 | index there: "slot = acc, then
+ *                      acc = X" (a parked value is nearly always followed by the load that starts
+ *                      the next sub-expression; one dispatch instead of two).  Zero otherwise.
  */
 #ifndef SECANT_B200_RECORD_H
 #define SECANT_B200_RECORD_H
@@ -36,6 +39,7 @@ enum { SB_KIND_ROW = 0, SB_KIND_CST = 1, SB_KIND_SLOT = 2, SB_NUM_KINDS = 3 };
 enum { SB_ROW_HOISTED = 0x8000 };
 /* FMA operand descriptors: kind 3 means "the accumulator"; 10-bit indices, bit 9 = hoisted row value. */
 enum { SB_FMA_ACC = 3, SB_FMA_ROW_HOISTED = 0x200 };
+enum { SB_STORE_THEN_LOAD = 0x80000000u };
 
 /* Binary operations; R* = operand on the left, accumulator on the right. */
 enum { SB_BIN_ADD = 0, SB_BIN_SUB, SB_BIN_RSUB, SB_BIN_MUL, SB_BIN_DIV, SB_BIN_RDIV, SB_BIN_MIN, SB_BIN_MAX, SB_NUM_BIN };

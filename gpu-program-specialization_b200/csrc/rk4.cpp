@@ -120,6 +120,7 @@ extern "C" SecantResult secant_b200_rk4_score(const SecantB200Rk4Run* given) {
     rules.reserved_slots = (unsigned)(4 * S); /* stage, next stage, sum, state vectors */
     rules.split_parts = true;                 /* what depends on the constants only is computed once per candidate, */
     rules.hoist_bank = true;                  /* not once per stage */
+    rules.fuse_store_load = true;
     for (size_t i = 0; i < programs.routines.count; ++i) {
         const SecantResult r = preflight(programs.routines.items[i], rules);
         if (r != SECANT_SUCCESS) return r;

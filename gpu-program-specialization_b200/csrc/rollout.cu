@@ -153,10 +153,11 @@ __device__ __forceinline__ uint32_t lds_word(uint32_t a) {
  * once per item into this form: word 0 = handler (bits 0..7) and, for H_UNARY, the function (bits
  * 8..15); word 1 = the operand's shared-window address, with bit 31 set when every lane reads its own
  * RR floats of a slot (the lane's offset is added) and clear when all lanes read one table entry.
+ * H_STORE_LOAD (slot = acc, then acc = operand) carries the slot's address in bits 8..31 of word 0.
  * H_FMA keeps the record's form (operand kinds in bits 8..13 of word 0, three 10-bit indices in
  * word 1).  One item runs its right-hand sides states x 4 stages x steps times, so the rewrite is free
  * and the dispatch per instruction is an address add, one load and one dense switch. */
-enum { H_END = 0, H_STORE, H_LOAD, H_ADD, H_SUB, H_RSUB, H_MUL, H_DIV, H_RDIV, H_MIN, H_MAX, H_NEG, H_ABS, H_UNARY, H_FMA };
+enum { H_END = 0, H_STORE, H_LOAD, H_ADD, H_SUB, H_RSUB, H_MUL, H_DIV, H_RDIV, H_MIN, H_MAX, H_NEG, H_ABS, H_UNARY, H_STORE_LOAD, H_FMA };
 constexpr uint32_t kPerLane = 0x80000000u;
 
 template <int RR>
@@ -223,8 +224,14 @@ struct Rollout {
                 for (int q = 0; q < RR; ++q) acc[q] = x[q];
                 continue;
             }
-            if (handler == H_STORE) { sts<RR>((w1 & 0x00ffffffu) + lane_off, acc); continue; }
+            if (handler == H_STORE_LOAD) {
+                sts<RR>((w0 >> 8) + lane_off, acc);
+#pragma unroll
+                for (int q = 0; q < RR; ++q) acc[q] = x[q];
+                continue;
+            }
             switch (handler) {
+            case H_STORE: sts<RR>((w1 & 0x00ffffffu) + lane_off, acc); break;
             case H_SUB:
 #pragma unroll
                 for (int q = 0; q < RR; ++q) acc[q] = __fsub_rn(acc[q], x[q]);
@@ -284,7 +291,13 @@ __device__ __forceinline__ SbInsn rewritten(SbInsn in, uint32_t table, uint32_t 
     const uint32_t idx = in.w0 >> 16;
     unsigned handler = H_END, aux = 0, kind = SB_NUM_KINDS; /* SB_NUM_KINDS: no operand */
     if (cs >= SB_CASE_LOAD && cs < SB_CASE_STORE) { handler = H_LOAD; kind = cs - SB_CASE_LOAD; }
-    else if (cs == SB_CASE_STORE) { handler = H_STORE; kind = SB_KIND_SLOT; }
+    else if (cs == SB_CASE_STORE && (in.w1 & SB_STORE_THEN_LOAD)) {
+        const unsigned loaded = (in.w1 >> 16) & 3u;
+        const uint32_t from = in.w1 & 0xffffu;
+        if (loaded == SB_KIND_ROW) return SbInsn{H_END, table};
+        const uint32_t operand = loaded == SB_KIND_CST ? table + from * (uint32_t)(RR * 4) : ((slot0 + from * (uint32_t)(RR * 128)) | kPerLane);
+        return SbInsn{H_STORE_LOAD | ((slot0 + idx * (uint32_t)(RR * 128)) << 8), operand};
+    } else if (cs == SB_CASE_STORE) { handler = H_STORE; kind = SB_KIND_SLOT; }
     else if (cs >= SB_CASE_BIN && cs < SB_CASE_UN) { handler = H_ADD + (cs - SB_CASE_BIN) / SB_NUM_KINDS; kind = (cs - SB_CASE_BIN) % SB_NUM_KINDS; }
     else if (cs >= SB_CASE_UN && cs < SB_CASE_FMA) {
         aux = cs - SB_CASE_UN;
@@ -629,6 +642,11 @@ cudaError_t launch_width(const DeviceBatch& batch, const Rk4Problem& prob, size_
     if (!warps || batch.max_insn > 16383u || prob.num_states > 16u) return cudaErrorInvalidConfiguration;
     const size_t smem = (size_t)warp_bytes * warps;
     e = cudaFuncSetAttribute(rk4_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
+    if (e != cudaSuccess) return e;
+    /* the largest shared-memory carve-out, always: left to itself the driver gave a CTA that fits the
+     * 100 KB configuration that one, and only one CTA per SM became resident where two were planned
+     * (measured: a call took 169 ms instead of 117 when its CTAs shrank from 101 KB to 98.8 KB) */
+    e = cudaFuncSetAttribute(rk4_kernel<RR>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
     const unsigned long long items = ((unsigned long long)prob.num_banks << prob.toggle_bits) * prob.num_systems;
     /* warps draw items from the queue until it is empty, so the grid only has to fill the device */

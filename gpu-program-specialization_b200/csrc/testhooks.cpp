@@ -58,6 +58,7 @@ SBT_EXPORT int sbt_encode(const uint8_t* routine_blob, const uint64_t* routine_o
         b->rules.split_parts = true;
         b->rules.hoist_bank = true;
         b->rules.hoist_row = false;
+        b->rules.fuse_store_load = true;
     }
     if ((flags >> 8) & 0xff) b->rules.max_hoisted = (unsigned)((flags >> 8) & 0xff);
     SecantResult r = SECANT_SUCCESS;
@@ -193,7 +194,14 @@ SBT_EXPORT int sbt_eval(const SbtBatch* b, size_t program, const float* input, s
             const unsigned cs = ins.w0 & 0xffu, index = ins.w0 >> 16;
             if (cs == SB_CASE_END) return !failed;
             if (cs >= SB_CASE_LOAD && cs < SB_CASE_LOAD + SB_NUM_KINDS) acc = operand(cs - SB_CASE_LOAD, index, false);
-            else if (cs == SB_CASE_STORE) { if (index >= slots.size()) return false; slots[index] = acc; }
+            else if (cs == SB_CASE_STORE) {
+                if (index >= slots.size()) return false;
+                slots[index] = acc;
+                if (ins.w1 & SB_STORE_THEN_LOAD) { /* the rollout records' fused form: then acc = X */
+                    if (which == 0) return false;
+                    acc = operand((ins.w1 >> 16) & 3u, ins.w1 & 0xffffu, false);
+                }
+            }
             else if (cs == SB_CASE_STOREH) {
                 std::vector<float>& dst = which == 0 ? table : hoisted;
                 if (which == 2 || index >= dst.size()) return false;
