@@ -205,6 +205,14 @@ EXECUTED_ON_REDUCED_CASE = {
 
 # ------------------------------------------------------------------------ RK4 arm ----
 
+# The same kind of figures for the rollout kernel: one launch of 2,048 systems of the configs[3]
+# population under a profiler (profiles/rk4_kernel_configs3.md), not this run.
+RK4_EXECUTED_ON_REDUCED_CASE = {
+    "source": "profiler capture of one launch of 2,048 systems, not this run",
+    "warp_instructions_per_interpreted_instruction": 50, "fp32_share_of_executed_instructions": 0.138,
+    "issue_active_pct_at_2_warps_per_scheduler": 35.7,
+}
+
 def rk4_arm(args, w):
     """`--impl rk4`: the rollout-scoring variant (16,384 candidate systems of
     3 right-hand sides with at most 24 tokens over 3 states and 8 coefficients, 64 initial
@@ -274,7 +282,8 @@ def rk4_arm(args, w):
                       "roofline": {"bound": "fp32", "achieved": lane_ops / dt / 1e12, "peak": peak.value / 1e12, "unit": "TFLOP/s",
                                    "frac": lane_ops / dt / peak.value, "traffic": None,
                                    "note": "operations of the integrations that were carried out (device counter), mean operation "
-                                           "count per system"}}))
+                                           "count per system",
+                                   "executed": RK4_EXECUTED_ON_REDUCED_CASE}}))
 
 
 # ------------------------------------------------------ the other benchmark shapes ----
